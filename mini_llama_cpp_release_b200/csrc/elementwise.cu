@@ -1,0 +1,267 @@
+// Row-wise kernels around the matrix products: embedding gather, residual add fused with
+// RMSNorm, the rotation table, the Q/K/V epilogue (bias, rotate-half RoPE, scatter of keys
+// and values into the paged cache), SiLU(gate)·up, and row gather.
+//
+// The arithmetic follows the reference's scalar code and stays in float32 wherever the
+// reference's does: the sum of squares and 1/sqrt(ss/d + eps) with the multiply order
+// x·scale·w (src/ops.cpp:19-41), cos/sin of a float32 angle p·f_i and the pairing
+// (i, i + hd/2) (src/ops.cpp:125-141), gate·(1/(1+exp(-gate)))·up (src/ops.cpp:94-107),
+// the residual sum (src/forward.cpp:772, 779).  What is new is the fusion and the layout.
+#include "common.cuh"
+
+namespace mlc {
+
+// ------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, int d,
+                             float* __restrict__ out) {
+    const int n = blockIdx.x;
+    const T* row = table + (long long)ids[n] * d;
+    float* o = out + (long long)n * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm
+// x (float32, the residual stream) += delta when delta is given; out = x·scale·gain.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                   const float* __restrict__ gain, float eps, int d,
+                                   T* __restrict__ out) {
+    __shared__ float scratch[32];
+    const long long base = (long long)blockIdx.x * d;
+    float ss = 0.0f;
+    if (delta != nullptr) {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = x[base + i] + delta[base + i];
+            x[base + i] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = x[base + i];
+            ss += v * v;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        out[base + i] = from_float<T>(x[base + i] * scale * gain[i]);
+    }
+}
+
+// ------------------------------------------------------------------ rotation table
+// table[p][i] = (cos(p·f_i), sin(p·f_i)), the angle formed in float32 from an integer
+// position and a float32 frequency, as src/ops.cpp:132-134 does for each token.
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, int n_pos, int half,
+                                  float2* __restrict__ table) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_pos * half) return;
+    const int p = (int)(idx / half), i = (int)(idx % half);
+    const float angle = (float)p * inv_freq[i];
+    table[idx] = make_float2(cosf(angle), sinf(angle));
+}
+
+// ------------------------------------------------------------------ Q/K/V epilogue
+// One block per token.  Input row: [q heads | k heads | v heads] in float32 straight from
+// the projection.  Adds the bias, rotates q and k by the token's position, writes q as
+// [token][head][hd] in the activation type and k, v into the token's place in the cache.
+// With kv_heads_in_row == 0 the row holds q only (a layer that reads another's cache).
+template <typename T>
+__global__ void qkv_post_kernel(const float* __restrict__ qkv, const float* __restrict__ bias,
+                                const int* __restrict__ positions, const int* __restrict__ tok_seq,
+                                const float2* __restrict__ rope, int rope_positions, int q_heads,
+                                int kv_heads_in_row, int hd, T* __restrict__ q_out, PagedKV cache) {
+    const int n = blockIdx.x;
+    const int half = hd >> 1;
+    const int row_width = (q_heads + 2 * kv_heads_in_row) * hd;
+    const float* row = qkv + (long long)n * row_width;
+    const int p = positions[n];
+    const int seq = tok_seq[n];
+    const float2* cs = (rope != nullptr) ? rope + (long long)min(p, rope_positions - 1) * half : nullptr;
+
+    // q and k heads: one thread per rotation pair
+    const int rot_heads = q_heads + kv_heads_in_row;
+    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+        const int head = idx / half, i = idx % half;
+        const int c0 = head * hd + i, c1 = c0 + half;
+        float x0 = row[c0], x1 = row[c1];
+        if (bias != nullptr) {
+            x0 += bias[c0];
+            x1 += bias[c1];
+        }
+        float y0 = x0, y1 = x1;
+        if (cs != nullptr) {
+            const float2 t = cs[i];
+            y0 = x0 * t.x - x1 * t.y;
+            y1 = x0 * t.y + x1 * t.x;
+        }
+        if (head < q_heads) {
+            T* dst = q_out + ((long long)n * q_heads + head) * hd;
+            dst[i] = from_float<T>(y0);
+            dst[i + half] = from_float<T>(y1);
+        } else {
+            T* dst = (T*)cache.k_pool + paged_offset(cache, seq, p, head - q_heads);
+            dst[i] = from_float<T>(y0);
+            dst[i + half] = from_float<T>(y1);
+        }
+    }
+    // v heads: bias only
+    const int v_start = (q_heads + kv_heads_in_row) * hd;
+    for (int idx = threadIdx.x; idx < kv_heads_in_row * hd; idx += blockDim.x) {
+        const int head = idx / hd, i = idx % hd;
+        float v = row[v_start + idx];
+        if (bias != nullptr) v += bias[v_start + idx];
+        T* dst = (T*)cache.v_pool + paged_offset(cache, seq, p, head);
+        dst[i] = from_float<T>(v);
+    }
+}
+
+// ------------------------------------------------------------------ SiLU(gate)·up
+// Input row [gate (I) | up (I)], output [I].
+template <typename TIn, typename TOut>
+__global__ void silu_mul_kernel(const TIn* __restrict__ gu, int inter, long long total,
+                                TOut* __restrict__ out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long n = idx / inter;
+    const int i = (int)(idx % inter);
+    const float g = to_float(gu[n * 2 * inter + i]);
+    const float u = to_float(gu[n * 2 * inter + inter + i]);
+    const float sig = 1.0f / (1.0f + expf(-g));
+    out[idx] = from_float<TOut>(g * sig * u);
+}
+
+// ------------------------------------------------------------------ row gather
+__global__ void gather_rows_kernel(const float* __restrict__ x, const float* __restrict__ delta,
+                                   const int* __restrict__ rows, int d, float* __restrict__ out_x,
+                                   float* __restrict__ out_delta) {
+    const long long src = (long long)rows[blockIdx.x] * d, dst = (long long)blockIdx.x * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        out_x[dst + i] = x[src + i];
+        if (delta != nullptr) out_delta[dst + i] = delta[src + i];
+    }
+}
+
+// ------------------------------------------------------------------ dtype conversion
+template <typename TIn, typename TOut>
+__global__ void convert_kernel(const TIn* __restrict__ in, long long total, TOut* __restrict__ out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) out[idx] = from_float<TOut>(to_float(in[idx]));
+}
+
+static inline int row_threads(int d) {
+    int t = 32;
+    while (t < d && t < 256) t <<= 1;
+    return t;
+}
+
+}  // namespace mlc
+
+using namespace mlc;
+
+extern "C" int mlc_embed(const void* table, int table_dtype, const int* ids, int n, int d, float* out,
+                         void* stream) {
+    if (n <= 0) return 0;
+    if (d <= 0) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == MLC_DTYPE_F32)
+        embed_kernel<float><<<n, row_threads(d), 0, s>>>((const float*)table, ids, d, out);
+    else if (table_dtype == MLC_DTYPE_BF16)
+        embed_kernel<bf16><<<n, row_threads(d), 0, s>>>((const bf16*)table, ids, d, out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_add_rmsnorm(float* x, const float* delta, const float* gain, float eps, int n, int d,
+                               void* out, int out_dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d <= 0) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == MLC_DTYPE_F32)
+        add_rmsnorm_kernel<float><<<n, row_threads(d), 0, s>>>(x, delta, gain, eps, d, (float*)out);
+    else if (out_dtype == MLC_DTYPE_BF16)
+        add_rmsnorm_kernel<bf16><<<n, row_threads(d), 0, s>>>(x, delta, gain, eps, d, (bf16*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_rope_table(const float* inv_freq, int n_pos, int half, void* table, void* stream) {
+    if (n_pos <= 0 || half <= 0) return MLC_ERR_BAD_SIZE;
+    const long long total = (long long)n_pos * half;
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(inv_freq, n_pos, half,
+                                                                                         (float2*)table);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_qkv_post(const float* qkv, const float* bias, const int* positions, const int* tok_seq,
+                            const void* rope_table, int rope_positions, int n, int q_heads,
+                            int kv_heads_in_row, int hd, void* q_out, int dtype, void* k_pool, void* v_pool,
+                            const int* page_table, long long entry_offset, int pages_per_seq, int page_size,
+                            int cache_kv_heads, void* stream) {
+    if (n <= 0) return 0;
+    if (hd <= 0 || (hd & 1) || q_heads <= 0 || kv_heads_in_row < 0) return MLC_ERR_BAD_SIZE;
+    if (kv_heads_in_row != 0 && kv_heads_in_row != cache_kv_heads) return MLC_ERR_BAD_SIZE;
+    PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, cache_kv_heads, hd};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = row_threads((q_heads + kv_heads_in_row) * hd / 2);
+    if (dtype == MLC_DTYPE_F32)
+        qkv_post_kernel<float><<<n, threads, 0, s>>>(qkv, bias, positions, tok_seq, (const float2*)rope_table,
+                                                     rope_positions, q_heads, kv_heads_in_row, hd,
+                                                     (float*)q_out, c);
+    else if (dtype == MLC_DTYPE_BF16)
+        qkv_post_kernel<bf16><<<n, threads, 0, s>>>(qkv, bias, positions, tok_seq, (const float2*)rope_table,
+                                                    rope_positions, q_heads, kv_heads_in_row, hd, (bf16*)q_out,
+                                                    c);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_silu_mul(const void* gate_up, int in_dtype, int n, int inter, void* out, int out_dtype,
+                            void* stream) {
+    if (n <= 0) return 0;
+    if (inter <= 0) return MLC_ERR_BAD_SIZE;
+    const long long total = (long long)n * inter;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (in_dtype == MLC_DTYPE_F32 && out_dtype == MLC_DTYPE_F32)
+        silu_mul_kernel<float, float><<<blocks, 256, 0, s>>>((const float*)gate_up, inter, total, (float*)out);
+    else if (in_dtype == MLC_DTYPE_F32 && out_dtype == MLC_DTYPE_BF16)
+        silu_mul_kernel<float, bf16><<<blocks, 256, 0, s>>>((const float*)gate_up, inter, total, (bf16*)out);
+    else if (in_dtype == MLC_DTYPE_BF16 && out_dtype == MLC_DTYPE_BF16)
+        silu_mul_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((const bf16*)gate_up, inter, total, (bf16*)out);
+    else if (in_dtype == MLC_DTYPE_BF16 && out_dtype == MLC_DTYPE_F32)
+        silu_mul_kernel<bf16, float><<<blocks, 256, 0, s>>>((const bf16*)gate_up, inter, total, (float*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_gather_rows(const float* x, const float* delta, const int* rows, int n_rows, int d,
+                               float* out_x, float* out_delta, void* stream) {
+    if (n_rows <= 0) return 0;
+    gather_rows_kernel<<<n_rows, row_threads(d), 0, (cudaStream_t)stream>>>(x, delta, rows, d, out_x, out_delta);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_convert(const void* in, int in_dtype, long long total, void* out, int out_dtype, void* stream) {
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (in_dtype == MLC_DTYPE_F32 && out_dtype == MLC_DTYPE_BF16)
+        convert_kernel<float, bf16><<<blocks, 256, 0, s>>>((const float*)in, total, (bf16*)out);
+    else if (in_dtype == MLC_DTYPE_BF16 && out_dtype == MLC_DTYPE_F32)
+        convert_kernel<bf16, float><<<blocks, 256, 0, s>>>((const bf16*)in, total, (float*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,74 @@
+"""The unit of work of the step function: for each sequence of the batch, its next tokens.
+
+The reference's `MiniBatch` is the tokens and positions of one sequence, and its
+`forward_batch` walks them one by one and returns the last token's logits
+(include/mini_llama/batch.h:9-23; src/batch.cpp:33-52).  Here a batch holds several
+sequences, each bound to a cache slot, each continuing at the slot's current length; the
+positions follow from that and are not given twice.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+
+@dataclass
+class SequenceChunk:
+    slot: int
+    tokens: List[int]
+    want: List[int] = field(default_factory=list)      # indices into `tokens` whose logits are asked for
+
+
+@dataclass
+class MiniBatch:
+    chunks: List[SequenceChunk]
+
+    @property
+    def n_tokens(self) -> int:
+        return sum(len(c.tokens) for c in self.chunks)
+
+    @staticmethod
+    def single(slot: int, token: int, want: bool = True) -> "MiniBatch":
+        """One token of one sequence (include/mini_llama/batch.h:18-19)."""
+        return MiniBatch([SequenceChunk(slot, [int(token)], [0] if want else [])])
+
+    @staticmethod
+    def from_tokens(slot: int, tokens: Sequence[int], want: Optional[Sequence[int]] = None) -> "MiniBatch":
+        """Several tokens of one sequence, continuing where the slot stands
+        (include/mini_llama/batch.h:21-23); by default the last token's logits are wanted."""
+        toks = [int(t) for t in tokens]
+        return MiniBatch([SequenceChunk(slot, toks, list(want) if want is not None else [len(toks) - 1])])
+
+    @staticmethod
+    def prefill(slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> "MiniBatch":
+        """Whole prompts of several sequences in one step; each one's last position is wanted."""
+        if len(slots) != len(prompts):
+            raise ValueError("one slot per prompt")
+        return MiniBatch([SequenceChunk(s, [int(t) for t in p], [len(p) - 1]) for s, p in zip(slots, prompts)])
+
+    @staticmethod
+    def decode(slots: Sequence[int], tokens: Sequence[int]) -> "MiniBatch":
+        """One token for each of several sequences."""
+        if len(slots) != len(tokens):
+            raise ValueError("one token per slot")
+        return MiniBatch([SequenceChunk(s, [int(t)], [0]) for s, t in zip(slots, tokens)])
+
+    def validate(self, vocab_size: int) -> None:
+        """Empty batches, empty sequences, a slot named twice, token ids outside the
+        vocabulary and wanted places outside a sequence are errors
+        (src/batch.cpp:38-43; src/forward.cpp:20-22)."""
+        if not self.chunks:
+            raise ValueError("forward_batch: the batch is empty")
+        seen = set()
+        for c in self.chunks:
+            if not c.tokens:
+                raise ValueError(f"forward_batch: slot {c.slot} brings no tokens")
+            if c.slot in seen:
+                raise ValueError(f"forward_batch: slot {c.slot} appears twice in one batch")
+            seen.add(c.slot)
+            for t in c.tokens:
+                if not 0 <= t < vocab_size:
+                    raise IndexError(f"forward_batch: token id {t} is outside the vocabulary [0, {vocab_size})")
+            for w in c.want:
+                if not 0 <= w < len(c.tokens):
+                    raise IndexError(f"forward_batch: wanted place {w} is outside the {len(c.tokens)} tokens of slot {c.slot}")

@@ -1,0 +1,135 @@
+"""A context: one model's cache on one device, and the step function over it.
+
+The reference's context is one sequence: its cache, its position, its token history
+(include/mini_llama/context.h:11-30), and `forward_batch(model, ctx, batch)` feeds it
+(src/batch.cpp:33-52).  Here a context holds many sequences, each in a slot; a step
+brings the next tokens of some of them, runs exactly those tokens as one batch against
+the cache, and returns logits at the places asked for.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.paged import PAGE_SIZE, PagedCache
+from .batch import MiniBatch, SequenceChunk
+from .model import Model
+from .step_info import StepInfo
+
+
+class ContextOverflow(ValueError):
+    """A sequence would pass the model's largest position."""
+
+
+class Context:
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = PAGE_SIZE):
+        """`max_tokens`: the most tokens live sequences hold at any time, each sequence's
+        count rounded up to whole pages of `page_size` tokens."""
+        self.model = model
+        rt = model.runtime
+        if max_seqs is None:
+            max_seqs = min((max_tokens + page_size - 1) // page_size, 4096)
+        with torch.cuda.device(rt.device):
+            self.cache = PagedCache(model.cache_needs(), model.reads_cache_of(), model.state_specs(), max_tokens,
+                                    max_seqs, rt.dtype, rt.device, page_size)
+        self.max_position = model.config.max_position_embeddings
+        self.token_history: Dict[int, List[int]] = {}
+        self.n_steps = 0
+
+    # ------------------------------------------------------------------ slots
+    def acquire(self) -> int:
+        slot = self.cache.acquire()
+        self.token_history[slot] = []
+        return slot
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+        self.token_history.pop(slot, None)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length[slot]
+
+    # ------------------------------------------------------------------ the step
+    def describe(self, batch: MiniBatch) -> StepInfo:
+        """Reserve pages for the batch's tokens and put its description on the device."""
+        cache = self.cache
+        tokens: List[int] = []
+        positions: List[int] = []
+        tok_seq: List[int] = []
+        cu = [0]
+        start_pos: List[int] = []
+        slots: List[int] = []
+        want_rows: List[int] = []
+        max_q = max_kv = 0
+        for c in batch.chunks:
+            if c.slot not in cache.length:
+                raise ValueError(f"forward_batch: slot {c.slot} is not held")
+            start = cache.length[c.slot]
+            if start + len(c.tokens) > self.max_position:
+                raise ContextOverflow(
+                    f"slot {c.slot}: {start} cached + {len(c.tokens)} new tokens pass max_position_embeddings "
+                    f"{self.max_position}")                                          # src/forward.cpp:23-25
+        for c in batch.chunks:
+            cache.reserve(c.slot, len(c.tokens))
+        for b, c in enumerate(batch.chunks):
+            start = cache.length[c.slot]
+            n = len(c.tokens)
+            base = len(tokens)
+            tokens.extend(c.tokens)
+            positions.extend(range(start, start + n))
+            tok_seq.extend([b] * n)
+            cu.append(base + n)
+            start_pos.append(start)
+            slots.append(c.slot)
+            want_rows.extend(base + w for w in c.want)
+            max_q = max(max_q, n)
+            max_kv = max(max_kv, start + n)
+        n_groups = len(cache.groups)
+        tables: List[List[int]] = []
+        widths: List[int] = []
+        for g in range(n_groups):
+            width = max(1, max(len(cache.page_lists[s][g]) for s in slots))
+            widths.append(width)
+            flat: List[int] = []
+            for s in slots:
+                pl = cache.page_lists[s][g]
+                flat.extend(pl)
+                flat.extend([-1] * (width - len(pl)))
+            tables.append(flat)
+        # one host buffer, one copy
+        segments = [tokens, positions, tok_seq, cu, start_pos, slots, want_rows, *tables]
+        offsets = []
+        flat_all: List[int] = []
+        for seg in segments:
+            offsets.append(len(flat_all))
+            flat_all.extend(seg)
+            flat_all.extend([0] * ((-len(flat_all)) % 4))        # keep every segment 16-byte aligned
+        host = torch.tensor(flat_all, dtype=torch.int32).pin_memory()
+        dev = host.to(self.model.runtime.device, non_blocking=True)
+
+        def seg(i: int, n: int) -> torch.Tensor:
+            return dev[offsets[i]: offsets[i] + n]
+
+        B = len(slots)
+        page_tables = [seg(7 + g, B * widths[g]).view(B, widths[g]) for g in range(n_groups)]
+        slots_dev = seg(5, B)
+        return StepInfo(
+            n_tokens=len(tokens), n_seqs=B, max_q_len=max_q, max_kv_len=max_kv,
+            tokens=seg(0, len(tokens)), positions=seg(1, len(tokens)), tok_seq=seg(2, len(tokens)),
+            cu_seqlens=seg(3, B + 1), start_pos=seg(4, B), slots=slots_dev, want_rows=seg(6, len(want_rows)),
+            page_tables=page_tables, slots_long=slots_dev.long(),
+        )
+
+    def forward_batch(self, batch: MiniBatch) -> torch.Tensor:
+        """Run the batch's tokens; returns float32 logits [number of wanted places, vocab], in
+        the order of the batch's sequences and of each one's `want`."""
+        batch.validate(self.model.config.vocab_size)
+        with torch.cuda.device(self.model.runtime.device):
+            step = self.describe(batch)
+            logits = self.model.forward(step, self.cache)
+        for c in batch.chunks:
+            self.cache.commit(c.slot, len(c.tokens))
+            self.token_history[c.slot].extend(c.tokens)                      # src/batch.cpp:49
+        self.n_steps += 1
+        return logits

@@ -1,0 +1,249 @@
+"""ctypes bindings of the core kernel library (see csrc/*.cu for what each kernel computes)."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+__all__ = [
+    "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
+    "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
+    "launch_count", "reset_launch_count",
+]
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_ERRORS = {-1: "unsupported element type", -2: "a size the kernel does not take", -3: "an option the kernel does not support"}
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches issued through these bindings since the last reset (a captured
+    graph's replays are counted by the engine, which knows how many launches it holds)."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def dtype_code(t: torch.dtype) -> int:
+    try:
+        return _DT[t]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16, not {t}") from None
+
+
+def require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("this engine runs on a CUDA device only: got a tensor on " + str(t.device))
+        if not t.is_contiguous():
+            raise KernelError("kernels take dense row-major tensors; got strides " + str(t.stride()))
+
+
+_core = None
+
+
+def core() -> ctypes.CDLL:
+    """The core library, built on first use."""
+    global _core
+    if _core is None:
+        lib = _build.core_library()
+        P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+        sigs = {
+            "mlc_embed": [P, I, P, I, I, P, P],
+            "mlc_add_rmsnorm": [P, P, P, F, I, I, P, I, P],
+            "mlc_rope_table": [P, I, I, P, P],
+            "mlc_qkv_post": [P, P, P, P, P, I, I, I, I, I, P, I, P, P, P, LL, I, I, I, P],
+            "mlc_silu_mul": [P, I, I, I, P, I, P],
+            "mlc_gather_rows": [P, P, P, I, I, P, P, P],
+            "mlc_convert": [P, I, LL, P, I, P],
+            "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
+            "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
+            "mlc_argmax": [P, I, I, P, P],
+            "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        lib.mlc_uniform_of.argtypes = [c_ulonglong, c_int, c_int]
+        lib.mlc_uniform_of.restype = c_float
+        _core = lib
+    return _core
+
+
+def _check(rc: int, what: str) -> None:
+    global _launches
+    if rc == 0:
+        _launches += 1
+        return
+    if rc < 0:
+        raise KernelError(f"{what}: {_ERRORS.get(rc, 'error ' + str(rc))}")
+    raise KernelError(f"{what}: CUDA error {rc} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+@dataclass
+class KVView:
+    """Where one cache entry's keys and values are: the group's pools
+    [entries][pages][kv_heads][page_size][head_dim], the entry's offset in elements, and the
+    page lists [n_seqs][pages_per_seq] of the sequences of this step."""
+    k_pool: torch.Tensor
+    v_pool: torch.Tensor
+    entry_offset: int
+    page_table: torch.Tensor
+    page_size: int
+    kv_heads: int
+    head_dim: int
+
+    @property
+    def pages_per_seq(self) -> int:
+        return self.page_table.shape[1]
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    require_cuda(table, ids, out)
+    n, d = out.shape
+    assert ids.dtype == torch.int32 and ids.numel() == n and table.shape[1] == d and out.dtype == torch.float32
+    _check(core().mlc_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), n, d, out.data_ptr(), _stream()),
+           "embedding")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                out: torch.Tensor) -> None:
+    """x (float32) += delta if given; out = x * 1/sqrt(mean(x^2) + eps) * gain."""
+    require_cuda(x, delta, gain, out)
+    n, d = x.shape
+    assert x.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == d and out.shape == x.shape
+    assert delta is None or (delta.dtype == torch.float32 and delta.shape == x.shape)
+    _check(core().mlc_add_rmsnorm(x.data_ptr(), _ptr(delta), gain.data_ptr(), float(eps), n, d, out.data_ptr(),
+                                  dtype_code(out.dtype), _stream()), "rmsnorm")
+
+
+def rope_table(inv_freq: torch.Tensor, n_pos: int) -> torch.Tensor:
+    """[n_pos][half][2] float32: cos and sin of position * inv_freq, the angle in float32."""
+    require_cuda(inv_freq)
+    assert inv_freq.dtype == torch.float32
+    half = inv_freq.numel()
+    table = torch.empty((n_pos, half, 2), dtype=torch.float32, device=inv_freq.device)
+    _check(core().mlc_rope_table(inv_freq.data_ptr(), n_pos, half, table.data_ptr(), _stream()), "rope table")
+    return table
+
+
+def qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor, tok_seq: torch.Tensor,
+             rope: Optional[torch.Tensor], q_heads: int, kv_heads_in_row: int, head_dim: int, q_out: torch.Tensor,
+             kv: Optional[KVView]) -> None:
+    """Bias, rotation and cache write for the rows [q | k | v] (float32) of a projection."""
+    require_cuda(qkv, bias, positions, tok_seq, rope, q_out)
+    n = qkv.shape[0]
+    width = (q_heads + 2 * kv_heads_in_row) * head_dim
+    assert qkv.dtype == torch.float32 and qkv.shape[1] == width
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == width)
+    assert q_out.numel() == n * q_heads * head_dim
+    if kv_heads_in_row:
+        assert kv is not None and kv.k_pool.dtype == q_out.dtype and kv.head_dim == head_dim
+        args = (kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset,
+                kv.pages_per_seq, kv.page_size, kv.kv_heads)
+    else:
+        args = (None, None, None, 0, 0, 1, 0)
+    rope_positions = rope.shape[0] if rope is not None else 0
+    _check(core().mlc_qkv_post(qkv.data_ptr(), _ptr(bias), positions.data_ptr(), tok_seq.data_ptr(), _ptr(rope),
+                               rope_positions, n, q_heads, kv_heads_in_row, head_dim, q_out.data_ptr(),
+                               dtype_code(q_out.dtype), *args, _stream()), "qkv epilogue")
+
+
+def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
+                   n_seqs: int, max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int = 0,
+                   n_splits: int = 1, part_ml: Optional[torch.Tensor] = None,
+                   part_o: Optional[torch.Tensor] = None) -> None:
+    require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o)
+    n_tokens = q.shape[0]
+    assert q.dtype == out.dtype == kv.k_pool.dtype
+    if n_splits > 1:
+        assert part_ml is not None and part_ml.numel() >= n_tokens * q_heads * n_splits * 2
+        assert part_o is not None and part_o.numel() >= n_tokens * q_heads * n_splits * kv.head_dim
+    _check(core().mlc_attention_simt(q.data_ptr(), out.data_ptr(), dtype_code(q.dtype), cu_seqlens.data_ptr(),
+                                     start_pos.data_ptr(), n_seqs, n_tokens, max_q_len, q_heads, kv.kv_heads,
+                                     kv.head_dim, float(scale), int(window), n_splits, _ptr(part_ml), _ptr(part_o),
+                                     kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
+                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, _stream()), "attention")
+    if n_splits > 1:
+        count_launches(1)
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """rows [gate | up] → gate * sigmoid(gate) * up."""
+    require_cuda(gate_up, out)
+    n, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (n, two_i // 2)
+    _check(core().mlc_silu_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n, two_i // 2, out.data_ptr(),
+                               dtype_code(out.dtype), _stream()), "silu_mul")
+
+
+def gather_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, out_x: torch.Tensor,
+                out_delta: Optional[torch.Tensor]) -> None:
+    require_cuda(x, delta, rows, out_x, out_delta)
+    assert x.dtype == torch.float32 and rows.dtype == torch.int32
+    assert (delta is None) == (out_delta is None)
+    _check(core().mlc_gather_rows(x.data_ptr(), _ptr(delta), rows.data_ptr(), rows.numel(), x.shape[1],
+                                  out_x.data_ptr(), _ptr(out_delta), _stream()), "gather")
+
+
+def linear_simt(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y = x @ w.T with float32 multiply-adds on the CUDA cores."""
+    require_cuda(x, w, y)
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and y.shape == (m, n)
+    _check(core().mlc_linear_simt(x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype), y.data_ptr(),
+                                  dtype_code(y.dtype), m, n, k, _stream()), "linear")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    require_cuda(logits, out)
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == logits.shape[0]
+    _check(core().mlc_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, seq_ids: torch.Tensor,
+           positions: torch.Tensor, out: torch.Tensor) -> None:
+    require_cuda(logits, seq_ids, positions, out)
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32
+    rows, vocab = logits.shape
+    if top_k > 1 and min(top_k, vocab) > 1024:
+        raise KernelError(f"top-k sampling on the device keeps at most 1024 candidates; got top_k={top_k}")
+    _check(core().mlc_sample(logits.data_ptr(), rows, vocab, float(temperature), int(top_k), int(seed) & (2**64 - 1),
+                             seq_ids.data_ptr(), positions.data_ptr(), out.data_ptr(), _stream()), "sampling")
+
+
+def uniform_of(seed: int, seq_id: int, position: int) -> float:
+    """The uniform number the device sampler draws for (seed, sequence id, position)."""
+    return float(core().mlc_uniform_of(int(seed) & (2**64 - 1), int(seq_id), int(position)))
