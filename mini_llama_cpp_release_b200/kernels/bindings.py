@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count",
+    "launch_count", "reset_launch_count", "attention_mma_available", "attention_mma",
 ]
 
 
@@ -247,3 +247,13 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, seq_
 def uniform_of(seed: int, seq_id: int, position: int) -> float:
     """The uniform number the device sampler draws for (seed, sequence id, position)."""
     return float(core().mlc_uniform_of(int(seed) & (2**64 - 1), int(seq_id), int(position)))
+
+
+def attention_mma_available() -> bool:
+    """Whether the tensor-core attention kernels exist in this build."""
+    import os
+    return os.path.exists(os.path.join(os.path.dirname(_build.__file__), "attention_mma.cu"))
+
+
+def attention_mma(q, o, step, q_heads, kv, scale, window, runtime) -> None:
+    raise KernelError("the tensor-core attention kernels are not part of this build")

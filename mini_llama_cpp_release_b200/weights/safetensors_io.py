@@ -127,7 +127,7 @@ class SafetensorsFile:
         if e.numel == 0:
             return torch.empty(e.shape, dtype=dtype)
         buf = memoryview(self._mm)[self.data_start + e.begin: self.data_start + e.end]
-        t = torch.frombuffer(buf, dtype=dtype).reshape(e.shape).clone()
+        t = torch.frombuffer(bytearray(buf), dtype=dtype).reshape(e.shape)      # one copy, off the map
         buf.release()
         return t
 
