@@ -1,0 +1,248 @@
+"""Each kernel alone against a plain float32 PyTorch restatement of the same operation, at
+sizes other than the engine's tests use: widths and vocabularies that are no power of two,
+head sizes in steps of 16, group sizes 1 to 20, pages handed out in shuffled order."""
+import math
+
+import pytest
+import torch
+
+import plain_impl
+from mini_llama_cpp_release_b200 import kernels
+from mini_llama_cpp_release_b200.kernels import KVView
+from mini_llama_cpp_release_b200.parts.rotary import neox_inv_freq
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def close(got, want, tol):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+    assert err <= tol, err
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_gathers_rows(dtype):
+    table = torch.randn(333, 72).to(DT[dtype])
+    ids = torch.tensor([0, 332, 5, 5, 17], dtype=torch.int32)
+    out = torch.empty(5, 72, device=DEV)
+    kernels.embed(table.to(DEV), ids.to(DEV), out)
+    assert torch.equal(out.cpu(), table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("d", [72, 896, 1000, 3584])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_add_rmsnorm(d, dtype):
+    torch.manual_seed(d)
+    x, delta, gain = torch.randn(5, d) * 3, torch.randn(5, d), 1 + 0.1 * torch.randn(d)
+    for use_delta in (False, True):
+        xd = x.clone().to(DEV)
+        out = torch.empty(5, d, dtype=DT[dtype], device=DEV)
+        kernels.add_rmsnorm(xd, delta.to(DEV) if use_delta else None, gain.to(DEV), 1e-5, out)
+        s = x + delta if use_delta else x
+        assert torch.allclose(xd.cpu(), s, atol=1e-6)                                   # the stream holds the sum, in float32
+        close(out.float(), plain_impl.rmsnorm(s, gain, 1e-5), 2e-6 if dtype == "float32" else 5e-3)
+
+
+def test_eps_sits_inside_the_square_root():
+    x = torch.zeros(1, 64, device=DEV)
+    x[0, 0] = 1e-3
+    out = torch.empty(1, 64, device=DEV)
+    kernels.add_rmsnorm(x, None, torch.ones(64, device=DEV), 1e-2, out)
+    assert math.isclose(float(out[0, 0]), 1e-3 / math.sqrt(1e-6 / 64 + 1e-2), rel_tol=1e-5)
+
+
+@pytest.mark.parametrize("hd,theta", [(16, 1e4), (64, 1e6), (80, 5e5)])
+def test_rotation_table_uses_float32_angles(hd, theta):
+    inv = neox_inv_freq(hd, theta)
+    i = torch.arange(hd // 2, dtype=torch.float32)
+    assert torch.allclose(inv, 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), 2 * i / hd), rtol=2e-7)
+    table = kernels.rope_table(inv.to(DEV), 5000).cpu()
+    angle = torch.arange(5000, dtype=torch.float32)[:, None] * inv[None, :]          # float32 product, as src/ops.cpp:133
+    assert torch.allclose(table[..., 0], torch.cos(angle), atol=2e-6)
+    assert torch.allclose(table[..., 1], torch.sin(angle), atol=2e-6)
+
+
+def make_paged(ks, vs, dtype, page_size=64, entries=2, entry=1, spare=3, seed=0):
+    """A cache holding the given sequences' keys and values ([len, KV, hd] each) in pages
+    handed out in shuffled order, as entry `entry` of `entries`."""
+    KV, hd = ks[0].shape[1], ks[0].shape[2]
+    n_pages = sum((len(k) + page_size - 1) // page_size for k in ks) + spare
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    k_pool = torch.full((entries, n_pages, KV, page_size, hd), float("nan"), dtype=dtype)
+    v_pool = torch.full_like(k_pool, float("nan"))
+    width = max((len(k) + page_size - 1) // page_size for k in ks)
+    table = torch.full((len(ks), width), -1, dtype=torch.int32)
+    nxt = 0
+    for b, (k, v) in enumerate(zip(ks, vs)):
+        for p in range((len(k) + page_size - 1) // page_size):
+            page = perm[nxt]; nxt += 1
+            table[b, p] = page
+            chunk = slice(p * page_size, min(len(k), (p + 1) * page_size))
+            n = chunk.stop - chunk.start
+            k_pool[entry, page, :, :n] = k[chunk].transpose(0, 1).to(dtype)
+            v_pool[entry, page, :, :n] = v[chunk].transpose(0, 1).to(dtype)
+    return KVView(k_pool.to(DEV), v_pool.to(DEV), entry * n_pages * KV * page_size * hd, table.to(DEV), page_size, KV, hd)
+
+
+def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0, scale_up=None):
+    """Sequences of `lens` cached tokens of which the last `q_lens` are this step's; compare
+    with the plain attention of each whole sequence."""
+    g = torch.Generator().manual_seed(seed)
+    t = DT[dtype]
+    ks = [torch.randn(n, KV, hd, generator=g).to(t).float() for n in lens]
+    vs = [torch.randn(n, KV, hd, generator=g).to(t).float() for n in lens]
+    qs = [torch.randn(n, H, hd, generator=g).to(t).float() for n in lens]
+    if scale_up is not None:
+        scale_up(qs, ks, vs)
+        qs = [q.to(t).float() for q in qs]; ks = [k.to(t).float() for k in ks]; vs = [v.to(t).float() for v in vs]
+    kv = make_paged(ks, vs, t, seed=seed)
+    q = torch.cat([qq[n - m:] for qq, n, m in zip(qs, lens, q_lens)]).to(t).to(DEV)
+    out = torch.empty_like(q)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    start = torch.tensor([n - m for n, m in zip(lens, q_lens)], dtype=torch.int32, device=DEV)
+    N = q.shape[0]
+    part_ml = torch.empty(N * H * n_splits * 2, device=DEV) if n_splits > 1 else None
+    part_o = torch.empty(N * H * n_splits * hd, device=DEV) if n_splits > 1 else None
+    kernels.attention_simt(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
+                           1.0 / math.sqrt(hd), window, n_splits, part_ml, part_o)
+    want = torch.cat([plain_impl.attention(qq, k, v, window or None)[n - m:] for qq, k, v, n, m in zip(qs, ks, vs, lens, q_lens)])
+    return out.float().cpu(), want, (qs, ks, vs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (14, 2, 64), (8, 1, 32), (6, 6, 80), (20, 1, 48), (3, 1, 256), (2, 2, 24)])
+def test_attention_prompts_chunks_and_single_tokens(H, KV, hd, dtype):
+    tol = 3e-6 if dtype == "float32" else 1e-2
+    got, want, _ = attention_case([7, 1, 130, 64], [7, 1, 130, 64], H, KV, hd, dtype)          # whole prompts
+    close(got, want, tol)
+    got, want, _ = attention_case([200, 65, 3], [1, 1, 1], H, KV, hd, dtype, seed=1)           # one token each
+    close(got, want, tol)
+    got, want, _ = attention_case([150, 90], [22, 90], H, KV, hd, dtype, seed=2)               # a chunk after a prefix
+    close(got, want, tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_splits", [2, 5, 32])
+def test_attention_key_splits_merge_to_the_same_result(n_splits, dtype):
+    tol = 3e-6 if dtype == "float32" else 1e-2
+    got, want, _ = attention_case([700, 33, 1], [1, 1, 1], 14, 2, 64, dtype, n_splits=n_splits)
+    close(got, want, tol)
+    got, want, _ = attention_case([300, 40], [40, 3], 4, 2, 16, dtype, n_splits=n_splits, seed=3)
+    close(got, want, tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 24, 64, 65])
+def test_attention_window_edge(window, dtype):
+    """Make the key just outside the window the one every query would prefer: if the edge is
+    off by one the output jumps to that key's value."""
+    def prefer_outside(qs, ks, vs):
+        for q, k, v in zip(qs, ks, vs):
+            n = len(k)
+            if n - 1 - window >= 0:
+                k[n - 1 - window] = 0
+                k[n - 1 - window, :, 0] = 30.0
+                q[n - 1, :, 0] = 30.0
+                v[n - 1 - window] = 100.0
+    tol = 3e-6 if dtype == "float32" else 1e-2
+    got, want, _ = attention_case([200, 66, 25], [1, 1, 1], 6, 3, 32, dtype, window=window, scale_up=prefer_outside)
+    assert float(want.abs().max()) < 50
+    close(got, want, tol)
+    got, want, _ = attention_case([200, 66], [200, 30], 6, 3, 32, dtype, window=window, seed=4)
+    close(got, want, tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    def one_far_key(qs, ks, vs):
+        q, k, v = qs[0], ks[0], vs[0]
+        k[3] = 0; k[3, :, 5] = 16.0
+        q[-1] = 0; q[-1, :, 5] = 16.0
+        v[3] = 7.0
+    got, want, (qs, ks, vs) = attention_case([900], [1], 14, 2, 64, dtype, scale_up=one_far_key, n_splits=4)
+    close(got, want, 3e-6 if dtype == "float32" else 1e-2)
+    assert float((got - 7.0).abs().max()) < 0.2                       # nearly all weight on key 3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_qkv_epilogue_adds_bias_rotates_and_writes_the_cache(dtype):
+    t = DT[dtype]
+    H, KV, hd, N = 6, 3, 32, 9
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(N, (H + 2 * KV) * hd, generator=g)
+    bias = torch.randn((H + 2 * KV) * hd, generator=g)
+    lens = [70, 5]                                   # tokens 0..3 continue a sequence at 66..69, 4..8 start one
+    positions = torch.tensor([66, 67, 68, 69, 0, 1, 2, 3, 4], dtype=torch.int32)
+    tok_seq = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1, 1], dtype=torch.int32)
+    kv = make_paged([torch.zeros(n, KV, hd) for n in lens], [torch.zeros(n, KV, hd) for n in lens], t)
+    table = kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), 128)
+    q_out = torch.empty(N, H * hd, dtype=t, device=DEV)
+    kernels.qkv_post(qkv.to(DEV), bias.to(DEV), positions.to(DEV), tok_seq.to(DEV), table, H, KV, hd, q_out, kv)
+    full = qkv + bias
+    q_want = plain_impl.rope_neox(full[:, :H * hd].view(N, H, hd), positions, 1e6)
+    k_want = plain_impl.rope_neox(full[:, H * hd:(H + KV) * hd].view(N, KV, hd), positions, 1e6)
+    v_want = full[:, (H + KV) * hd:].view(N, KV, hd)
+    tol = 2e-6 if dtype == "float32" else 5e-3
+    close(q_out.float().view(N, H, hd), q_want, tol)
+    per_entry = kv.k_pool.shape[1]
+    pages = kv.page_table.cpu()
+    for n in range(N):
+        page = int(pages[tok_seq[n], positions[n] // 64])
+        close(kv.k_pool[1, page, :, positions[n] % 64].float(), k_want[n], tol)
+        close(kv.v_pool[1, page, :, positions[n] % 64].float(), v_want[n], tol)
+    assert torch.isnan(kv.k_pool[0].float()).all()                    # the other entry of the pool is untouched
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul(dtype):
+    t = DT[dtype]
+    gu = (torch.randn(7, 2 * 344) * 3).to(t)
+    out = torch.empty(7, 344, dtype=t, device=DEV)
+    kernels.silu_mul(gu.to(DEV), out)
+    g, u = gu.float()[:, :344], gu.float()[:, 344:]
+    close(out.float(), g * (1 / (1 + torch.exp(-g))) * u, 2e-6 if dtype == "float32" else 5e-3)
+
+
+def test_gather_rows():
+    x, d = torch.randn(11, 72, device=DEV), torch.randn(11, 72, device=DEV)
+    rows = torch.tensor([10, 0, 3, 3], dtype=torch.int32, device=DEV)
+    ox, od = torch.empty(4, 72, device=DEV), torch.empty(4, 72, device=DEV)
+    kernels.gather_rows(x, d, rows, ox, od)
+    assert torch.equal(ox, x[rows.long()]) and torch.equal(od, d[rows.long()])
+
+
+@pytest.mark.parametrize("xd,wd,yd", [("float32", "float32", "float32"), ("bfloat16", "float32", "float32"),
+                                      ("float32", "bfloat16", "bfloat16"), ("bfloat16", "bfloat16", "float32")])
+@pytest.mark.parametrize("M,N,K", [(1, 70, 33), (5, 1000, 896), (130, 64, 344), (64, 129, 16)])
+def test_float32_linear_takes_any_size_and_gives_each_row_the_same_sum(M, N, K, xd, wd, yd):
+    g = torch.Generator().manual_seed(M * N)
+    x = torch.randn(M, K, generator=g).to(DT[xd])
+    w = torch.randn(N, K, generator=g).to(DT[wd])
+    y = torch.empty(M, N, dtype=DT[yd], device=DEV)
+    kernels.linear_simt(x.to(DEV), w.to(DEV), y)
+    close(y.float(), x.double() @ w.double().t(), 3e-6 if yd == "float32" else 5e-3)
+    y1 = torch.empty(1, N, dtype=DT[yd], device=DEV)
+    kernels.linear_simt(x[M - 1:].contiguous().to(DEV), w.to(DEV), y1)
+    assert torch.equal(y1[0], y[M - 1])                               # bit for bit, whatever the batch
+
+
+def test_argmax_lowest_index_wins():
+    logits = torch.randn(4, 151936)
+    logits[0, 77] = 50; logits[0, 150000] = 50
+    logits[1, 151935] = 60
+    logits[2] = 0.0
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    kernels.argmax(logits.to(DEV), out)
+    assert out.tolist() == [77, 151935, 0, int(logits[3].argmax())]
+
+
+def test_refusals_are_errors_not_wrong_results():
+    q = torch.zeros(1, 4 * 320, device=DEV)
+    kv = make_paged([torch.zeros(1, 1, 320)], [torch.zeros(1, 1, 320)], torch.float32)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(kernels.KernelError, match="size"):
+        kernels.attention_simt(q, torch.empty_like(q), z, z, 1, 1, 4, kv, 1.0)
+    with pytest.raises(kernels.KernelError, match="CUDA device only"):
+        kernels.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
