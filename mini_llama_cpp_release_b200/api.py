@@ -35,14 +35,17 @@ class LLM:
 
     def generate(self, prompts: Sequence[Sequence[int]], n_predict: int = 16, temperature: float = 0.0,
                  top_k: int = 0, seed: int = 0, stop_token_ids: Optional[Sequence[int]] = None,
-                 max_batch: Optional[int] = None, return_details: bool = False
+                 max_batch: Optional[int] = None, return_details: bool = False, on_step=None
                  ) -> Union[List[List[int]], List[GenerationResult]]:
         """Generated ids for each prompt (lists of token ids).  `stop_token_ids` defaults to the
-        checkpoint's `eos_token_id`, if it has one."""
+        checkpoint's `eos_token_id`, if it has one.  `on_step(live, chosen, logits)`, if given, is
+        called after every choice with the indices of the live requests, their chosen ids and
+        the logits they were chosen from."""
         if stop_token_ids is None:
             stop_token_ids = self.config.eos_token_id or ()
         sampler = DeviceSampler(SamplingParams(temperature, top_k, seed), self.model.runtime.device)
-        results = generate(self.context, sampler, prompts, n_predict, stop_token_ids, max_batch=max_batch)
+        results = generate(self.context, sampler, prompts, n_predict, stop_token_ids, max_batch=max_batch,
+                           on_step=on_step)
         return results if return_details else [r.tokens for r in results]
 
 

@@ -327,3 +327,34 @@ extern "C" int mlc_sample(const float* logits, int rows, int vocab, float temper
 extern "C" float mlc_uniform_of(unsigned long long seed, int seq_id, int position) {
     return uniform_of(seed, seq_id, position);
 }
+
+// After a decode step whose tokens were chosen on the device: make the chosen tokens the
+// next step's input and move every sequence one position on, so that the next step can
+// start without the host.  `history`, if given, keeps each step's choices
+// [max_steps][n]; `counter` counts the steps taken.
+__global__ void decode_advance_kernel(const int* __restrict__ chosen, int n, int* __restrict__ tokens,
+                                      int* __restrict__ positions, int* __restrict__ start_pos,
+                                      int* __restrict__ sample_pos, int* __restrict__ history,
+                                      int* __restrict__ counter, int max_steps) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int step = *counter;
+    if (i < n) {
+        tokens[i] = chosen[i];
+        positions[i] += 1;
+        start_pos[i] += 1;
+        sample_pos[i] += 1;
+        if (history != nullptr && step < max_steps) history[(long long)step * n + i] = chosen[i];
+    }
+    __syncthreads();
+    if (i == 0) *counter = step + 1;
+}
+
+extern "C" int mlc_decode_advance(const int* chosen, int n, int* tokens, int* positions, int* start_pos,
+                                  int* sample_pos, int* history, int* counter, int max_steps, void* stream) {
+    if (n <= 0) return 0;
+    if (n > 1024) return MLC_ERR_BAD_SIZE;
+    decode_advance_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(chosen, n, tokens, positions, start_pos,
+                                                                    sample_pos, history, counter, max_steps);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}

@@ -14,6 +14,7 @@ import torch
 
 from ..cache.paged import PAGE_SIZE, PagedCache
 from .batch import MiniBatch, SequenceChunk
+from .decode_runner import DecodeRunner
 from .model import Model
 from .step_info import StepInfo
 
@@ -36,6 +37,9 @@ class Context:
         self.max_position = model.config.max_position_embeddings
         self.token_history: Dict[int, List[int]] = {}
         self.n_steps = 0
+        # decoding through captured graphs needs every part to be free of host round trips
+        self.use_graphs = all(getattr(p, "graph_safe", False) for p in model.graph_relevant_parts())
+        self._runners: Dict[tuple, DecodeRunner] = {}
 
     # ------------------------------------------------------------------ slots
     def acquire(self) -> int:
@@ -133,3 +137,94 @@ class Context:
             self.token_history[c.slot].extend(c.tokens)                      # src/batch.cpp:49
         self.n_steps += 1
         return logits
+
+    # ------------------------------------------------------------------ decoding through a captured graph
+    def _runner(self, n_seqs: int, need_len: int, sampler) -> DecodeRunner:
+        bucket = 256
+        while bucket < need_len:
+            bucket *= 2
+        bucket = min(bucket, max(need_len, self.max_position))
+        p = sampler.params
+        key = (n_seqs, bucket, p.greedy) if p.greedy else (n_seqs, bucket, p.temperature, p.top_k, sampler.seed)
+        runner = self._runners.get(key)
+        if runner is None:
+            if len(self._runners) >= 12:
+                self._runners.pop(next(iter(self._runners)))
+            runner = DecodeRunner(self, n_seqs, bucket, sampler)
+            self._runners[key] = runner
+        return runner
+
+    def _check_decode(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int) -> None:
+        vocab = self.model.config.vocab_size
+        if not slots or len(slots) != len(tokens) or len(set(slots)) != len(slots):
+            raise ValueError("decode: one token for each of a set of distinct slots")
+        for s, t in zip(slots, tokens):
+            if s not in self.cache.length:
+                raise ValueError(f"decode: slot {s} is not held")
+            if not 0 <= int(t) < vocab:
+                raise IndexError(f"decode: token id {t} is outside the vocabulary [0, {vocab})")
+            if self.cache.length[s] + n_steps > self.max_position:
+                raise ContextOverflow(f"slot {s}: {self.cache.length[s]} cached + {n_steps} new tokens pass "
+                                      f"max_position_embeddings {self.max_position}")
+
+    def decode_and_sample(self, slots: Sequence[int], tokens: Sequence[int], sampler, seq_ids: Sequence[int]):
+        """One decode step for `slots` fed with `tokens`, the next tokens chosen on the device.
+        Returns (chosen ids as a list, the step's logits [n, vocab] on the device).  Copies the
+        step's inputs to the device and the chosen ids back; `last_copy_bytes` says how much."""
+        self._check_decode(slots, tokens, 1)
+        slots = list(slots)
+        with torch.cuda.device(self.model.runtime.device):
+            for s in slots:
+                self.cache.reserve(s, 1)
+            lengths = [self.cache.length[s] for s in slots]
+            runner = self._runner(len(slots), max(lengths) + 1, sampler)
+            h2d = 0
+            if runner.graph is None:
+                runner.load(slots, tokens, seq_ids)
+                runner.capture()
+                runner.loaded_slots = None
+            if runner.loaded_slots != slots or runner.loaded_ids != list(seq_ids):
+                runner.load(slots, tokens, seq_ids)
+                runner.loaded_ids = list(seq_ids)
+                h2d += runner.host_buf.numel() * 4
+            else:
+                h2d += runner.load_step(tokens, lengths)
+                h2d += runner.refresh_pages(slots)
+            runner.replay()
+            chosen = runner.read_chosen()
+        for s, t in zip(slots, tokens):
+            self.cache.commit(s, 1)
+            self.token_history[s].append(int(t))
+        self.n_steps += 1
+        self.last_copy_bytes = (h2d, 4 * len(slots))
+        return chosen, runner.logits
+
+    def decode_on_device(self, slots: Sequence[int], tokens: Sequence[int], sampler, seq_ids: Sequence[int],
+                         n_steps: int, before=None, after=None) -> torch.Tensor:
+        """`n_steps` decode steps back to back without the host in between: every step's chosen
+        tokens are the next step's input.  Returns the chosen ids [n_steps, n] (device).
+        `before` and `after`, if given, are called around the replays (for timing)."""
+        self._check_decode(slots, tokens, n_steps)
+        slots = list(slots)
+        if n_steps > DecodeRunner.HISTORY_STEPS:
+            raise ValueError(f"decode_on_device keeps at most {DecodeRunner.HISTORY_STEPS} steps")
+        with torch.cuda.device(self.model.runtime.device):
+            for s in slots:
+                self.cache.reserve(s, n_steps)
+            runner = self._runner(len(slots), max(self.cache.length[s] for s in slots) + n_steps, sampler)
+            if runner.graph is None:
+                runner.load(slots, tokens, seq_ids)
+                runner.capture()
+            runner.load(slots, tokens, seq_ids)
+            runner.loaded_slots = None                 # the buffers will not describe a host-known state afterwards
+            if before is not None:
+                before()
+            for _ in range(n_steps):
+                runner.replay()
+            if after is not None:
+                after()
+            out = runner.history[:n_steps].clone()
+        for s in slots:
+            self.cache.commit(s, n_steps)
+        self.n_steps += n_steps
+        return out

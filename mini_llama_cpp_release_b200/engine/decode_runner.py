@@ -1,0 +1,195 @@
+"""Decoding as a replayed CUDA graph: one token for each of a fixed set of sequences.
+
+A decode step launches a few kernels per layer, each lasting microseconds; issued one by
+one from the host the launches cost more than the kernels.  The runner captures one step
+(the model's forward over one token per sequence, the choice of the next token, and a
+small kernel that makes the chosen tokens the next step's input and moves every sequence
+one position on) into a CUDA graph over fixed buffers.  A step is then: copy the step's
+inputs into the buffers (or leave what the previous step put there), replay, read the
+chosen tokens.  The captured function is the same `Model.forward` that every other step
+runs.
+
+The reference launches its kernels one by one on the default stream and synchronises
+after each attention kernel (src/cuda_attention.cu:29-32).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import kernels
+from ..sampling.sampler import DeviceSampler
+from .step_info import StepInfo
+
+
+def _round_up_pow2(n: int) -> int:
+    p = 1
+    while p < n:
+        p <<= 1
+    return p
+
+
+class DecodeRunner:
+    """Buffers and graph for `n_seqs` sequences decoding together, valid while no sequence
+    grows beyond `max_len` tokens."""
+
+    HISTORY_STEPS = 1024
+
+    def __init__(self, context, n_seqs: int, max_len: int, sampler: DeviceSampler):
+        self.ctx = context
+        self.model = context.model
+        self.cache = context.cache
+        self.B = n_seqs
+        self.max_len = max_len
+        self.sampler = sampler
+        rt = self.model.runtime
+        dev = rt.device
+        B = n_seqs
+        self.pages_per_seq = max(1, (max_len + self.cache.page_size - 1) // self.cache.page_size)
+        n_groups = len(self.cache.groups)
+        # one int32 buffer; the per-step inputs come first so that one copy brings them
+        names = [("tokens", B), ("positions", B), ("start_pos", B), ("sample_pos", B),
+                 ("tok_seq", B), ("cu_seqlens", B + 1), ("slots", B), ("want_rows", B), ("seq_ids", B), ("chosen", B),
+                 ("counter", 1)] + [(f"pages{g}", B * self.pages_per_seq) for g in range(n_groups)]
+        self.offsets = {}
+        total = 0
+        for name, n in names:
+            self.offsets[name] = (total, n)
+            total += (n + 3) // 4 * 4
+        self.dev_buf = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.host_buf = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.step_inputs = 4 * B                                    # ints copied to the device at every step
+        self.history = torch.zeros(self.HISTORY_STEPS, B, dtype=torch.int32, device=dev)
+        self.chosen_host = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.slots_long = torch.zeros(B, dtype=torch.int64, device=dev)
+        h = self.host_view
+        h("tok_seq")[:] = torch.arange(B, dtype=torch.int32)
+        h("cu_seqlens")[:] = torch.arange(B + 1, dtype=torch.int32)
+        h("want_rows")[:] = torch.arange(B, dtype=torch.int32)
+        for g in range(n_groups):
+            h(f"pages{g}")[:] = -1
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.launches_per_step = 0
+        self.loaded_slots: Optional[List[int]] = None
+        self.loaded_ids: Optional[List[int]] = None
+        self.page_counts: Optional[List[List[int]]] = None
+
+    # ------------------------------------------------------------------ buffers
+    def view(self, name: str) -> torch.Tensor:
+        o, n = self.offsets[name]
+        return self.dev_buf[o:o + n]
+
+    def host_view(self, name: str) -> torch.Tensor:
+        o, n = self.offsets[name]
+        return self.host_buf[o:o + n]
+
+    def step_info(self) -> StepInfo:
+        B = self.B
+        tables = [self.view(f"pages{g}").view(B, self.pages_per_seq) for g in range(len(self.cache.groups))]
+        return StepInfo(n_tokens=B, n_seqs=B, max_q_len=1, max_kv_len=self.max_len,
+                        tokens=self.view("tokens"), positions=self.view("positions"), tok_seq=self.view("tok_seq"),
+                        cu_seqlens=self.view("cu_seqlens"), start_pos=self.view("start_pos"), slots=self.view("slots"),
+                        want_rows=self.view("want_rows"), page_tables=tables, slots_long=self.slots_long)
+
+    # ------------------------------------------------------------------ one step's body
+    def _body(self) -> None:
+        step = self.step_info()
+        self.logits = self.model.forward(step, self.cache)
+        self.sampler.sample_device(self.logits, self.view("seq_ids"), self.view("sample_pos"), out=self.view("chosen"))
+        kernels.decode_advance(self.view("chosen"), self.view("tokens"), self.view("positions"), self.view("start_pos"),
+                               self.view("sample_pos"), self.history, self.view("counter"))
+
+    def capture(self) -> None:
+        """Run the step once eagerly (libraries initialise, tables are built), then capture it.
+        Both runs happen on the buffers' current contents, which must describe valid sequences;
+        the caller reloads the buffers afterwards."""
+        dev = self.model.runtime.device
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(stream):
+            self._body()
+        torch.cuda.current_stream(dev).wait_stream(stream)
+        torch.cuda.synchronize(dev)
+        before, lib_before = kernels.launch_count(), kernels.library_launch_count()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=stream):
+            self._body()
+        self.launches_per_step = kernels.launch_count() - before
+        self.library_launches_per_step = kernels.library_launch_count() - lib_before
+        torch.cuda.synchronize(dev)
+
+    # ------------------------------------------------------------------ loading a batch
+    def load(self, slots: Sequence[int], tokens: Sequence[int], seq_ids: Sequence[int]) -> None:
+        """Everything about the batch: called when the set of sequences changes."""
+        B = self.B
+        assert len(slots) == B
+        h = self.host_view
+        lengths = [self.cache.length[s] for s in slots]
+        h("tokens")[:] = torch.tensor(list(tokens), dtype=torch.int32)
+        h("positions")[:] = torch.tensor(lengths, dtype=torch.int32)
+        h("start_pos")[:] = h("positions")
+        h("sample_pos")[:] = h("positions") + 1
+        h("slots")[:] = torch.tensor(list(slots), dtype=torch.int32)
+        h("seq_ids")[:] = torch.tensor(list(seq_ids), dtype=torch.int32)
+        h("counter")[:] = 0
+        self._fill_pages(slots)
+        self.dev_buf.copy_(self.host_buf, non_blocking=True)
+        self.slots_long.copy_(h("slots").long(), non_blocking=True)
+        self.loaded_slots = list(slots)
+
+    def _fill_pages(self, slots: Sequence[int]) -> None:
+        P = self.pages_per_seq
+        self.page_counts = []
+        for g in range(len(self.cache.groups)):
+            t = self.host_view(f"pages{g}").view(self.B, P)
+            counts = []
+            for b, s in enumerate(slots):
+                pl = self.cache.page_lists[s][g]
+                if len(pl) > P:
+                    raise RuntimeError("decode runner: a sequence outgrew the runner's page table")
+                t[b, :len(pl)] = torch.tensor(pl, dtype=torch.int32)
+                t[b, len(pl):] = -1
+                counts.append(len(pl))
+            self.page_counts.append(counts)
+
+    def refresh_pages(self, slots: Sequence[int]) -> int:
+        """Copy the page tables again if any sequence got or lost a page; returns bytes copied."""
+        changed = False
+        for g in range(len(self.cache.groups)):
+            for b, s in enumerate(slots):
+                pl = self.cache.page_lists[s][g]
+                if len(pl) != self.page_counts[g][b] or (self.cache.groups[g].need.kind == "window"):
+                    changed = True
+        if not changed:
+            return 0
+        self._fill_pages(slots)
+        n = 0
+        for g in range(len(self.cache.groups)):
+            o, cnt = self.offsets[f"pages{g}"]
+            self.dev_buf[o:o + cnt].copy_(self.host_buf[o:o + cnt], non_blocking=True)
+            n += cnt * 4
+        return n
+
+    def load_step(self, tokens: Sequence[int], lengths: Sequence[int]) -> int:
+        """The per-step inputs from the host: tokens and positions.  Returns bytes copied."""
+        h = self.host_view
+        pos = torch.tensor(list(lengths), dtype=torch.int32)
+        h("tokens")[:] = torch.tensor(list(tokens), dtype=torch.int32)
+        h("positions")[:] = pos
+        h("start_pos")[:] = pos
+        h("sample_pos")[:] = pos + 1
+        end = self.offsets["sample_pos"][0] + self.B              # the four segments lie first, in this order
+        self.dev_buf[:end].copy_(self.host_buf[:end], non_blocking=True)
+        return 4 * end
+
+    def replay(self) -> None:
+        self.graph.replay()
+        kernels.bindings.count_launches(self.launches_per_step)
+        kernels.count_library_launches(self.library_launches_per_step)
+
+    def read_chosen(self) -> List[int]:
+        self.chosen_host.copy_(self.view("chosen"), non_blocking=True)
+        torch.cuda.current_stream(self.model.runtime.device).synchronize()
+        return self.chosen_host.tolist()

@@ -80,8 +80,13 @@ def generate_batch(ctx, sampler, prompts: Sequence[Sequence[int]], seq_ids: Sequ
         live = list(range(len(prompts)))
         lengths = [len(p) for p in prompts]
         logits = ctx.forward_batch(MiniBatch.prefill(slots, prompts))
+        fused = bool(getattr(ctx, "use_graphs", False)) and hasattr(ctx, "decode_and_sample")
+        chosen_next = None
         while True:
-            chosen = sampler.sample(logits, [seq_ids[i] for i in live], [lengths[i] for i in live])
+            if chosen_next is not None:
+                chosen, chosen_next = chosen_next, None
+            else:
+                chosen = sampler.sample(logits, [seq_ids[i] for i in live], [lengths[i] for i in live])
             if on_step is not None:
                 on_step(live, chosen, logits)
             still: List[int] = []
@@ -103,9 +108,14 @@ def generate_batch(ctx, sampler, prompts: Sequence[Sequence[int]], seq_ids: Sequ
             live = still
             if not live:
                 break
-            logits = ctx.forward_batch(MiniBatch.decode([slots[i] for i in live], feed))
             for i in live:
                 lengths[i] += 1
+            if fused:
+                # forward, choice and the move to the next position are one captured graph
+                chosen_next, logits = ctx.decode_and_sample([slots[i] for i in live], feed, sampler,
+                                                            [seq_ids[i] for i in live])
+            else:
+                logits = ctx.forward_batch(MiniBatch.decode([slots[i] for i in live], feed))
     finally:
         for s in slots:
             if s >= 0:

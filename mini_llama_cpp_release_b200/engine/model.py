@@ -81,6 +81,18 @@ class Model:
     def reads_cache_of(self) -> List[Optional[int]]:
         return [e.reads_cache_of for e in self.spec.schedule]
 
+    def graph_relevant_parts(self) -> List[Part]:
+        """Every part a step runs, children included."""
+        out: List[Part] = []
+
+        def walk(p: Part) -> None:
+            out.append(p)
+            for c in p.children():
+                walk(c)
+        for p in self.parts.all_parts():
+            walk(p)
+        return out
+
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights one step reads: every schedule entry's layer, the final norm and the head."""
         total = sum(self.parts.blocks[e.layer].weight_bytes() for e in self.spec.schedule)

@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "attention_mma_available", "attention_mma",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "decode_advance",
 ]
 
 
@@ -42,6 +42,19 @@ def reset_launch_count() -> None:
 def count_launches(n: int) -> None:
     global _launches
     _launches += n
+
+
+_library_launches = 0
+
+
+def count_library_launches(n: int) -> None:
+    """Library matrix products issued (kept apart from this package's own kernels)."""
+    global _library_launches
+    _library_launches += n
+
+
+def library_launch_count() -> int:
+    return _library_launches
 
 
 def dtype_code(t: torch.dtype) -> int:
@@ -82,6 +95,7 @@ def core() -> ctypes.CDLL:
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
+            "mlc_decode_advance": [P, I, P, P, P, P, P, P, I, P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -242,6 +256,17 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, seq_
         raise KernelError(f"top-k sampling on the device keeps at most 1024 candidates; got top_k={top_k}")
     _check(core().mlc_sample(logits.data_ptr(), rows, vocab, float(temperature), int(top_k), int(seed) & (2**64 - 1),
                              seq_ids.data_ptr(), positions.data_ptr(), out.data_ptr(), _stream()), "sampling")
+
+
+def decode_advance(chosen: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, start_pos: torch.Tensor,
+                   sample_pos: torch.Tensor, history: Optional[torch.Tensor], counter: torch.Tensor) -> None:
+    """The chosen tokens become the next step's input; every sequence moves one position on."""
+    require_cuda(chosen, tokens, positions, start_pos, sample_pos, history, counter)
+    n = chosen.numel()
+    max_steps = history.shape[0] if history is not None else 0
+    _check(core().mlc_decode_advance(chosen.data_ptr(), n, tokens.data_ptr(), positions.data_ptr(), start_pos.data_ptr(),
+                                     sample_pos.data_ptr(), _ptr(history), counter.data_ptr(), max_steps, _stream()),
+           "decode advance")
 
 
 def uniform_of(seed: int, seq_id: int, position: int) -> float:

@@ -26,6 +26,8 @@ from .linear import Linear
 
 @register_part("mixer", "gqa_attention")
 class GQAttention(Part):
+    graph_safe = True
+
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None,
                  out_bias: bool = False):

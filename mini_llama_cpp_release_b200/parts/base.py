@@ -90,7 +90,13 @@ class Runtime:
 
 
 class Part:
-    """Base of all parts: keeps the name prefix and the constructor parameters."""
+    """Base of all parts: keeps the name prefix and the constructor parameters.
+
+    `graph_safe`: the part's forward only launches work on the current stream (no host round
+    trip, no data-dependent host decision), so a step through it can be captured into a CUDA
+    graph.  Parts say so explicitly; a part that does not is run step by step."""
+
+    graph_safe = False
 
     def __init__(self, name: str, **params: Any):
         self.name = name

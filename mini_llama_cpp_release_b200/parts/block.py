@@ -17,6 +17,8 @@ from .base import MixerMemory, Part
 
 @register_part("block", "prenorm")
 class PreNormBlock(Part):
+    graph_safe = True
+
     def __init__(self, name: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
                  feed_forward_norm: PartSpec, names: Optional[dict] = None):
         super().__init__(name)

@@ -15,6 +15,8 @@ from .linear import Linear
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, name: str, vocab_size: int, hidden_size: int):
         super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
@@ -37,6 +39,8 @@ class TokenEmbedding(Part):
 
 @register_part("head", "linear_head")
 class LinearHead(Part):
+    graph_safe = True
+
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
         super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size, tied_to=tied_to)
         self.vocab, self.hidden, self.tied_to = int(vocab_size), int(hidden_size), tied_to

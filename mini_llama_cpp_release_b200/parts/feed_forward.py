@@ -13,6 +13,8 @@ from .linear import Linear
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
+    graph_safe = True
+
     def __init__(self, name: str, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         super().__init__(name, hidden_size=hidden_size, intermediate_size=intermediate_size, activation=activation)
         if activation != "silu":

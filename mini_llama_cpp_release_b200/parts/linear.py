@@ -43,5 +43,5 @@ class Linear:
             torch.mm(x, self.weight.t(), out_dtype=torch.float32, out=out)
         else:
             torch.mm(x, self.weight.t(), out=out)
-        kernels.bindings.count_launches(1)
+        kernels.count_library_launches(1)
         return out

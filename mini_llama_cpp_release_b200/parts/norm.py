@@ -18,6 +18,8 @@ from .base import Part, TensorSpec
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
+    graph_safe = True
+
     def __init__(self, name: str, size: int, eps: float):
         super().__init__(name, size=size, eps=eps)
         self.size = int(size)

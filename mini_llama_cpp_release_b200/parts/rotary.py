@@ -30,6 +30,8 @@ def neox_inv_freq(head_dim: int, theta: float) -> torch.Tensor:
 
 @register_part("position", "rope_neox")
 class RopeNeox(Part):
+    graph_safe = True
+
     fusable = True        # the attention part applies it inside its Q/K/V epilogue
 
     def __init__(self, name: str, head_dim: int, theta: float, max_positions: int):
@@ -46,10 +48,10 @@ class RopeNeox(Part):
         self.inv_freq = neox_inv_freq(self.head_dim, self.theta).to(runtime.device)
 
     def prepare(self, n_positions: int) -> None:
-        """Make sure the table covers positions 0 .. n_positions-1."""
-        n = min(int(n_positions), self.max_positions)
-        if self.table is None or self.table.shape[0] < n:
-            self.table = kernels.rope_table(self.inv_freq, n)
+        """Make sure the table exists.  It is built once, for every position the model allows,
+        and never replaced: captured graphs keep reading the same memory."""
+        if self.table is None:
+            self.table = kernels.rope_table(self.inv_freq, self.max_positions)
 
     def rotate(self, x: torch.Tensor, positions: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """Rotate float32 x [n, heads, head_dim] by int32 positions [n]; on its own, outside attention."""
@@ -64,6 +66,8 @@ class RopeNeox(Part):
 
 @register_part("position", "none")
 class NoPosition(Part):
+    graph_safe = True
+
     fusable = True
 
     def __init__(self, name: str, **_):
