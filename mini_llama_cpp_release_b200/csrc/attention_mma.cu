@@ -1,0 +1,429 @@
+// Attention over the paged cache on the tensor cores, for bfloat16 activations and cache,
+// compiled for one head size (-DMLC_HEAD_DIM=16, 32, ..., 256).
+//
+// The arithmetic is the reference's (score = (q·k)·1/sqrt(hd) over keys lo(p)..p, softmax,
+// weighted sum of values, query head h on kv head h/(H/KV): src/forward.cpp:524-526,
+// 585-611; src/ops.cpp:43-70) with the usual streaming form of the softmax: a running
+// maximum and sum per row in float32, scores and accumulators in float32, probabilities
+// rounded to bfloat16 only as the operand of the second product.
+//
+// Shape of the work.  A block has four warps and a tile of 16·RT rows; a row is one
+// (token, query head) pair, and all rows of a block share one kv head, so the G query heads
+// of a group ride on the same key and value tiles (for 14 heads on 2 kv heads: 9 tokens x 7
+// heads per 64-row tile).  Keys come in tiles of 64, one cache page, copied to shared
+// memory with cp.async in two stages.
+//   RT = 4: each warp owns 16 rows and walks all 64 keys of a tile (prompts, chunks).
+//   RT = 1: the block has 16 rows (one decoded token's group of heads) and the four warps
+//           split each tile's keys 4 x 16, merging their partial results at the end.
+//   RT = 2: 32 rows, two warps per row tile, 2 x 32 keys.
+// A sequence's key range can also be split over blocks (n_splits); partial (max, sum,
+// weighted values) then go to scratch memory and mlc_attention_combine merges them.
+#include "common.cuh"
+
+#ifndef MLC_HEAD_DIM
+#error "compile with -DMLC_HEAD_DIM=<head size>"
+#endif
+
+namespace mlc {
+
+constexpr int HD = MLC_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be 16, 32, ..., 256");
+constexpr int TILE = 64;                 // keys per tile = tokens per cache page
+constexpr int STRIDE = HD + 8;           // shared-memory row stride in elements: 16 bytes of padding keep ldmatrix conflict-free
+constexpr int CPR = HD / 8;              // 16-byte chunks per row
+constexpr int KS_QK = HD / 16;           // k-steps of q·k
+constexpr int NT_O = HD / 8;             // output n-tiles
+constexpr bool Q_IN_REGS = (HD <= 128);
+
+struct MmaArgs {
+    const bf16* q;            // [N][H][HD]
+    bf16* out;                // [N][H][HD]
+    const int* cu_seqlens;    // [B+1]
+    const int* start_pos;     // [B]
+    float* part_ml;           // [N*H][n_splits][2]
+    float* part_o;            // [N*H][n_splits][HD]
+    float scale_log2;         // scale * log2(e)
+    int q_heads;
+    int group;
+    int window;
+    int tokens_per_block;
+    int heads_per_block;
+    int head_chunks;
+    int n_splits;
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;        // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const bf16* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const bf16* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int RT>
+__global__ void __launch_bounds__(128)
+attention_mma_kernel(MmaArgs a, PagedKV c) {
+    constexpr int KP = 4 / RT;             // warps sharing a row tile, each with its part of a key tile
+    constexpr int KEYS_W = TILE / KP;      // keys per warp per tile
+    constexpr int NT_S = KEYS_W / 8;       // score n-tiles per warp
+    constexpr int KS_PV = KEYS_W / 16;     // k-steps of p·v per warp
+    constexpr int ROWS = 16 * RT;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [ROWS][STRIDE]
+    bf16* Ks = Qs + ROWS * STRIDE;                                // [2][TILE][STRIDE]
+    bf16* Vs = Ks + 2 * TILE * STRIDE;                            // [2][TILE][STRIDE]
+
+    const int b = blockIdx.z;
+    int y = blockIdx.y;
+    const int split = y % a.n_splits;  y /= a.n_splits;
+    const int chunk = y % a.head_chunks;  y /= a.head_chunks;
+    const int kvh = y;
+    const int tok0 = blockIdx.x * a.tokens_per_block;
+    const int seq_tok0 = a.cu_seqlens[b];
+    const int q_len = a.cu_seqlens[b + 1] - seq_tok0;
+    if (tok0 >= q_len) return;
+    const int start = a.start_pos[b];
+    const int n_tok = min(a.tokens_per_block, q_len - tok0);
+    const int GH = a.heads_per_block;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rt = warp % RT, part = warp / RT;
+
+    // ---- stage the query rows (zeros for rows that do not exist)
+    for (int idx = tid; idx < ROWS * CPR; idx += 128) {
+        const int r = idx / CPR, ch = idx % CPR;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t < n_tok && hg < a.group) {
+            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+            v = *reinterpret_cast<const uint4*>(a.q + row * HD + ch * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + r * STRIDE + ch * 8) = v;
+    }
+
+    // ---- key range of the block and of this split, in tiles
+    const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
+    const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
+    const int tile_begin = lo_block / TILE, tile_end = p_last / TILE + 1;
+    const int per_split = (tile_end - tile_begin + a.n_splits - 1) / a.n_splits;
+    const int my_begin = tile_begin + split * per_split;
+    const int my_end = min(tile_end, my_begin + per_split);
+
+    const bf16* kp = (const bf16*)c.k_pool;
+    const bf16* vp = (const bf16*)c.v_pool;
+    auto load_tile = [&](int stage, int tile) {
+        const int page = c.page_table[(long long)b * c.pages_per_seq + tile];
+        const long long base = c.entry_offset + ((long long)max(page, 0) * c.kv_heads + kvh) * TILE * HD;
+        bf16* kd = Ks + stage * TILE * STRIDE;
+        bf16* vd = Vs + stage * TILE * STRIDE;
+        for (int idx = tid; idx < TILE * CPR; idx += 128) {
+            const int j = idx / CPR, ch = idx % CPR;
+            const int kpos = tile * TILE + j;
+            const bool valid = page >= 0 && kpos >= lo_block && kpos <= p_last;
+            const long long off = valid ? base + (long long)j * HD + ch * 8 : 0;
+            cp_async_16(kd + j * STRIDE + ch * 8, kp + off, valid);
+            cp_async_16(vd + j * STRIDE + ch * 8, vp + off, valid);
+        }
+    };
+
+    // ---- this thread's two rows (lane/4 and lane/4 + 8 of the warp's row tile)
+    int row_hi[2], row_lo[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int r = rt * 16 + (lane >> 2) + 8 * e;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        row_ok[e] = (t < n_tok) && (hg < a.group);
+        row_hi[e] = row_ok[e] ? start + tok0 + t : -1;
+        row_lo[e] = (a.window > 0) ? max(0, row_hi[e] - a.window + 1) : 0;
+    }
+    // the warp's rows span these positions (rows are ordered by token)
+    const int warp_t_first = (rt * 16) / GH, warp_t_last = min((rt * 16 + 15) / GH, n_tok - 1);
+    const int warp_hi = start + tok0 + warp_t_last;
+    const int warp_lo = (a.window > 0) ? max(0, start + tok0 + warp_t_first - a.window + 1) : 0;
+    const bool warp_has_rows = warp_t_first < n_tok;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[NT_O][4];
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
+    unsigned qf[Q_IN_REGS ? KS_QK : 1][4];
+
+    if (my_begin < my_end) {
+        load_tile(0, my_begin);
+        cp_async_commit();
+    }
+    __syncthreads();                       // Qs is staged
+    if (Q_IN_REGS) {
+#pragma unroll
+        for (int kk = 0; kk < KS_QK; ++kk)
+            ldmatrix_x4(qf[Q_IN_REGS ? kk : 0], Qs + (rt * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+    }
+
+    for (int tile = my_begin, it = 0; tile < my_end; ++tile, ++it) {
+        const int stage = it & 1;
+        if (tile + 1 < my_end) {
+            load_tile(stage ^ 1, tile + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+
+        const int key0 = tile * TILE + part * KEYS_W;          // first key of this warp's part
+        if (warp_has_rows && key0 <= warp_hi && key0 + KEYS_W - 1 >= warp_lo) {
+            const bf16* kt = Ks + stage * TILE * STRIDE + part * KEYS_W * STRIDE;
+            const bf16* vt = Vs + stage * TILE * STRIDE + part * KEYS_W * STRIDE;
+            float s[NT_S][4];
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < KS_QK; ++kk) {
+                unsigned af[4];
+                if (Q_IN_REGS) {
+                    af[0] = qf[Q_IN_REGS ? kk : 0][0]; af[1] = qf[Q_IN_REGS ? kk : 0][1];
+                    af[2] = qf[Q_IN_REGS ? kk : 0][2]; af[3] = qf[Q_IN_REGS ? kk : 0][3];
+                } else {
+                    ldmatrix_x4(af, Qs + (rt * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+                }
+#pragma unroll
+                for (int jp = 0; jp < NT_S / 2; ++jp) {
+                    unsigned bfr[4];
+                    ldmatrix_x4(bfr, kt + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+                    mma_bf16(s[2 * jp], af, bfr[0], bfr[1]);
+                    mma_bf16(s[2 * jp + 1], af, bfr[2], bfr[3]);
+                }
+            }
+            // scale, mask, running maximum
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int kpos = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
+                    const int rr = e >> 1;
+                    const bool in_range = kpos >= row_lo[rr] && kpos <= row_hi[rr];
+                    const float v = in_range ? s[j][e] * a.scale_log2 : -INFINITY;
+                    s[j][e] = v;
+                    mx[rr] = fmaxf(mx[rr], v);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+                const float m_new = fmaxf(m[rr], mx[rr]);
+                const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+                corr[rr] = exp2f(m[rr] - m_use);             // 0 when nothing was seen before
+                m[rr] = m_new;
+                mx[rr] = m_use;
+            }
+            float ls[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = exp2f(s[j][e] - mx[e >> 1]);
+                    s[j][e] = p;
+                    ls[e >> 1] += p;
+                }
+            }
+            l[0] = l[0] * corr[0] + ls[0];
+            l[1] = l[1] * corr[1] + ls[1];
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+            // o += p · v
+#pragma unroll
+            for (int kk = 0; kk < KS_PV; ++kk) {
+                unsigned pf[4];
+                pf[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pf[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pf[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pf[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int jp = 0; jp < NT_O / 2; ++jp) {
+                    unsigned bfr[4];
+                    ldmatrix_x4_trans(bfr, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + jp * 16 + (lane >> 4) * 8);
+                    mma_bf16(o[2 * jp], pf, bfr[0], bfr[1]);
+                    mma_bf16(o[2 * jp + 1], pf, bfr[2], bfr[3]);
+                }
+            }
+        }
+        __syncthreads();                   // all warps are done with this stage before it is refilled
+    }
+
+    // the row sums are still spread over the four lanes of a quad
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+    }
+
+    constexpr float LN2 = 0.6931471805599453f;
+    if (KP == 1) {
+        // each warp owns its rows: write straight from registers
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            if (!row_ok[rr]) continue;
+            const int r = rt * 16 + (lane >> 2) + 8 * rr;
+            const int t = r / GH, hg = chunk * GH + r % GH;
+            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+            if (a.n_splits == 1) {
+                const float inv = 1.0f / l[rr];
+                bf16* dst = a.out + row * HD + 2 * (lane & 3);
+#pragma unroll
+                for (int j = 0; j < NT_O; ++j)
+                    *reinterpret_cast<unsigned*>(dst + 8 * j) = pack_bf16(o[j][2 * rr] * inv, o[j][2 * rr + 1] * inv);
+            } else {
+                const long long pr = row * a.n_splits + split;
+                if ((lane & 3) == 0) {
+                    a.part_ml[pr * 2] = m[rr] * LN2;
+                    a.part_ml[pr * 2 + 1] = l[rr];
+                }
+                float* dst = a.part_o + pr * HD + 2 * (lane & 3);
+#pragma unroll
+                for (int j = 0; j < NT_O; ++j) {
+                    dst[8 * j] = o[j][2 * rr];
+                    dst[8 * j + 1] = o[j][2 * rr + 1];
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- several warps hold parts of the same rows: merge them through shared memory
+    float* Oc = reinterpret_cast<float*>(Ks);                       // [4 warps][16][HD]
+    float* MLc = Oc + 4 * 16 * HD;                                  // [4 warps][16][2]
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int r16 = (lane >> 2) + 8 * rr;
+        float* dst = Oc + (warp * 16 + r16) * HD + 2 * (lane & 3);
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) {
+            dst[8 * j] = o[j][2 * rr];
+            dst[8 * j + 1] = o[j][2 * rr + 1];
+        }
+        if ((lane & 3) == 0) {
+            MLc[(warp * 16 + r16) * 2] = m[rr];
+            MLc[(warp * 16 + r16) * 2 + 1] = l[rr];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < ROWS * HD; idx += 128) {
+        const int r = idx / HD, d = idx % HD;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        if (!(t < n_tok && hg < a.group)) continue;
+        const int rtile = r / 16, r16 = r % 16;
+        float M = -INFINITY;
+#pragma unroll
+        for (int p = 0; p < KP; ++p) M = fmaxf(M, MLc[((rtile + RT * p) * 16 + r16) * 2]);
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int p = 0; p < KP; ++p) {
+            const int w = rtile + RT * p;
+            const float mw = MLc[(w * 16 + r16) * 2];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - M);
+                L += MLc[(w * 16 + r16) * 2 + 1] * f;
+                acc += Oc[(w * 16 + r16) * HD + d] * f;
+            }
+        }
+        const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+        if (a.n_splits == 1) {
+            a.out[row * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const long long pr = row * a.n_splits + split;
+            a.part_o[pr * HD + d] = acc;
+            if (d == 0) {
+                a.part_ml[pr * 2] = M * LN2;
+                a.part_ml[pr * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+template <int RT>
+static int launch_mma(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_t s) {
+    constexpr int ROWS = 16 * RT;
+    const size_t smem = (size_t)(ROWS + 4 * TILE) * STRIDE * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attention_mma_kernel<RT><<<grid, 128, smem, s>>>(a, c);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace mlc
+
+using namespace mlc;
+
+extern "C" int mlc_attention_mma_head_dim() { return HD; }
+
+// q, out: bfloat16 [n_tokens][q_heads][HD]; the cache pools hold bfloat16 in pages of 64 tokens.
+// row_tiles: 1, 2 or 4 (16, 32 or 64 rows per block).  n_splits > 1 writes partial results to
+// part_ml / part_o (sizes as for mlc_attention_simt) and leaves `out` to the combine kernel.
+extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
+                                 int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
+                                 int window, int row_tiles, int n_splits, float* part_ml, float* part_o,
+                                 void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
+                                 int pages_per_seq, int page_size, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (hd != HD || page_size != TILE) return MLC_ERR_BAD_SIZE;
+    if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    if (row_tiles != 1 && row_tiles != 2 && row_tiles != 4) return MLC_ERR_BAD_SIZE;
+    if (n_splits < 1 || (n_splits > 1 && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
+    MmaArgs a;
+    a.q = (const bf16*)q;
+    a.out = (bf16*)out;
+    a.cu_seqlens = cu_seqlens;
+    a.start_pos = start_pos;
+    a.part_ml = part_ml;
+    a.part_o = part_o;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.q_heads = q_heads;
+    a.group = q_heads / kv_heads;
+    a.window = window;
+    const int rows = 16 * row_tiles;
+    a.heads_per_block = a.group < rows ? a.group : rows;
+    a.tokens_per_block = rows / a.heads_per_block;
+    a.head_chunks = (a.group + a.heads_per_block - 1) / a.heads_per_block;
+    a.n_splits = n_splits;
+    const long long gy = (long long)kv_heads * a.head_chunks * n_splits;
+    if (gy > 65535) return MLC_ERR_BAD_SIZE;
+    PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, kv_heads, hd};
+    dim3 grid((max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, (unsigned)gy, n_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (row_tiles == 4) return launch_mma<4>(a, c, grid, s);
+    if (row_tiles == 2) return launch_mma<2>(a, c, grid, s);
+    return launch_mma<1>(a, c, grid, s);
+}

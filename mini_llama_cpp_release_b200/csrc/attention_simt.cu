@@ -281,3 +281,21 @@ extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int
     }
     return 0;
 }
+
+// Merge partial results that another attention kernel left in part_ml / part_o
+// (maxima in natural-log units, sums and weighted values relative to them).
+extern "C" int mlc_attention_combine(const float* part_ml, const float* part_o, long long n_rows, int n_splits,
+                                     int hd, void* out, int dtype, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (n_splits < 1 || hd <= 0) return MLC_ERR_BAD_SIZE;
+    const unsigned blocks = (unsigned)((n_rows + 3) / 4);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MLC_DTYPE_F32)
+        attention_combine_kernel<float><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, (float*)out);
+    else if (dtype == MLC_DTYPE_BF16)
+        attention_combine_kernel<bf16><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, (bf16*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}

@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_library", "decode_advance",
 ]
 
 
@@ -93,6 +93,7 @@ def core() -> ctypes.CDLL:
             "mlc_convert": [P, I, LL, P, I, P],
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
+            "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
             "mlc_decode_advance": [P, I, P, P, P, P, P, P, I, P],
@@ -280,5 +281,63 @@ def attention_mma_available() -> bool:
     return os.path.exists(os.path.join(os.path.dirname(_build.__file__), "attention_mma.cu"))
 
 
-def attention_mma(q, o, step, q_heads, kv, scale, window, runtime) -> None:
-    raise KernelError("the tensor-core attention kernels are not part of this build")
+_attn_libs = {}
+
+
+def attention_library(head_dim: int) -> ctypes.CDLL:
+    """The tensor-core attention kernels for one head size, built on first use."""
+    lib = _attn_libs.get(head_dim)
+    if lib is None:
+        lib = _build.attention_library(head_dim)
+        P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P, P, LL, I, I, P]
+        lib.mlc_attention_mma.restype = c_int
+        lib.mlc_attention_mma_head_dim.restype = c_int
+        if lib.mlc_attention_mma_head_dim() != head_dim:
+            raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
+        _attn_libs[head_dim] = lib
+    return lib
+
+
+def attention_mma_plan(max_q_len: int, n_seqs: int, max_kv_len: int, q_heads: int, kv_heads: int, n_sms: int):
+    """(row_tiles, n_splits) for a step: 64-row blocks for prompts, 16- or 32-row blocks whose
+    warps share the keys for single tokens, and key splits when the rows alone leave SMs idle."""
+    group = q_heads // kv_heads
+    if max_q_len == 1:
+        row_tiles = 1 if group <= 16 else (2 if group <= 32 else 4)
+    else:
+        row_tiles = 4
+    rows = 16 * row_tiles
+    heads_per_block = min(group, rows)
+    tokens_per_block = rows // heads_per_block
+    head_chunks = (group + heads_per_block - 1) // heads_per_block
+    blocks = ((max_q_len + tokens_per_block - 1) // tokens_per_block) * kv_heads * head_chunks * n_seqs
+    n_splits = 1
+    if blocks < 2 * n_sms:
+        by_fill = (2 * n_sms + blocks - 1) // blocks
+        by_len = max(1, max_kv_len // 256)              # at least four 64-key tiles per split
+        n_splits = max(1, min(by_fill, by_len, 64))
+    return row_tiles, n_splits
+
+
+def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
+                  max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int, row_tiles: int, n_splits: int,
+                  part_ml: Optional[torch.Tensor] = None, part_o: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry."""
+    require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o)
+    if q.dtype != torch.bfloat16 or kv.k_pool.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention takes bfloat16 queries and cache")
+    n_tokens = q.shape[0]
+    hd = kv.head_dim
+    if n_splits > 1:
+        assert part_ml is not None and part_ml.numel() >= n_tokens * q_heads * n_splits * 2
+        assert part_o is not None and part_o.numel() >= n_tokens * q_heads * n_splits * hd
+    lib = attention_library(hd)
+    _check(lib.mlc_attention_mma(q.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), start_pos.data_ptr(), n_seqs,
+                                 n_tokens, max_q_len, q_heads, kv.kv_heads, hd, float(scale), int(window), row_tiles,
+                                 n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(),
+                                 kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq, kv.page_size, _stream()),
+           "tensor-core attention")
+    if n_splits > 1:
+        _check(core().mlc_attention_combine(part_ml.data_ptr(), part_o.data_ptr(), n_tokens * q_heads, n_splits, hd,
+                                            out.data_ptr(), dtype_code(out.dtype), _stream()), "attention combine")

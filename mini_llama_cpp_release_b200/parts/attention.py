@@ -82,8 +82,9 @@ class GQAttention(Part):
             self.bias = torch.cat([get(n + "q_proj.bias"), get(n + "k_proj.bias"), get(n + "v_proj.bias")]).to(torch.float32).contiguous()
         else:
             self.bias = None
-        self.use_tensor_cores = (runtime.dtype == torch.bfloat16 and self.hd % 16 == 0
-                                 and kernels.attention_mma_available())
+        self.use_tensor_cores = runtime.dtype == torch.bfloat16 and self.hd % 16 == 0
+        if self.use_tensor_cores:
+            kernels.attention_library(self.hd)          # compiled now, for this model's head size, not at the first step
 
     def weight_bytes(self) -> int:
         b = self.qkv.nbytes() + self.o.nbytes()
@@ -114,7 +115,14 @@ class GQAttention(Part):
         rt = self.runtime
         window = self.window or 0
         if self.use_tensor_cores:
-            kernels.attention_mma(q, o, step, self.H, kv, self.scale, window, rt)
+            row_tiles, n_splits = kernels.attention_mma_plan(step.max_q_len, step.n_seqs, step.max_kv_len, self.H,
+                                                             self.KV, rt.n_sms)
+            part_ml = part_o = None
+            if n_splits > 1:
+                part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
+                part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
+            kernels.attention_mma(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
+                                  self.scale, window, row_tiles, n_splits, part_ml, part_o)
             return
         n_splits = choose_splits(step, self.H, self.KV, rt.n_sms, tokens_per_block=max(1, 16 // min(16, self.H // self.KV)))
         part_ml = part_o = None

@@ -86,7 +86,7 @@ def make_paged(ks, vs, dtype, page_size=64, entries=2, entry=1, spare=3, seed=0)
     return KVView(k_pool.to(DEV), v_pool.to(DEV), entry * n_pages * KV * page_size * hd, table.to(DEV), page_size, KV, hd)
 
 
-def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0, scale_up=None):
+def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0, scale_up=None, impl="simt", row_tiles=4):
     """Sequences of `lens` cached tokens of which the last `q_lens` are this step's; compare
     with the plain attention of each whole sequence."""
     g = torch.Generator().manual_seed(seed)
@@ -105,8 +105,12 @@ def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0,
     N = q.shape[0]
     part_ml = torch.empty(N * H * n_splits * 2, device=DEV) if n_splits > 1 else None
     part_o = torch.empty(N * H * n_splits * hd, device=DEV) if n_splits > 1 else None
-    kernels.attention_simt(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
-                           1.0 / math.sqrt(hd), window, n_splits, part_ml, part_o)
+    if impl == "mma":
+        kernels.attention_mma(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
+                              1.0 / math.sqrt(hd), window, row_tiles, n_splits, part_ml, part_o)
+    else:
+        kernels.attention_simt(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
+                               1.0 / math.sqrt(hd), window, n_splits, part_ml, part_o)
     want = torch.cat([plain_impl.attention(qq, k, v, window or None)[n - m:] for qq, k, v, n, m in zip(qs, ks, vs, lens, q_lens)])
     return out.float().cpu(), want, (qs, ks, vs)
 
@@ -236,6 +240,64 @@ def test_argmax_lowest_index_wins():
     out = torch.empty(4, dtype=torch.int32, device=DEV)
     kernels.argmax(logits.to(DEV), out)
     assert out.tolist() == [77, 151935, 0, int(logits[3].argmax())]
+
+
+@pytest.mark.parametrize("row_tiles", [1, 2, 4])
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (14, 2, 64), (8, 1, 32), (6, 6, 80), (40, 1, 48), (3, 1, 256), (12, 2, 128), (70, 1, 16)])
+def test_tensor_core_attention_prompts_chunks_and_single_tokens(H, KV, hd, row_tiles):
+    kw = dict(impl="mma", row_tiles=row_tiles)
+    got, want, _ = attention_case([7, 1, 130, 64], [7, 1, 130, 64], H, KV, hd, "bfloat16", **kw)
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([200, 65, 3, 64, 128, 129], [1, 1, 1, 1, 1, 1], H, KV, hd, "bfloat16", seed=1, **kw)
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([150, 90, 300], [22, 90, 2], H, KV, hd, "bfloat16", seed=2, **kw)
+    close(got, want, 1e-2)
+
+
+@pytest.mark.parametrize("row_tiles", [1, 4])
+@pytest.mark.parametrize("n_splits", [2, 5, 64])
+def test_tensor_core_attention_key_splits(n_splits, row_tiles):
+    kw = dict(impl="mma", row_tiles=row_tiles, n_splits=n_splits)
+    got, want, _ = attention_case([700, 33, 1], [1, 1, 1], 14, 2, 64, "bfloat16", **kw)
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([300, 40], [40, 3], 4, 2, 16, "bfloat16", seed=3, **kw)
+    close(got, want, 1e-2)
+
+
+@pytest.mark.parametrize("row_tiles", [1, 4])
+@pytest.mark.parametrize("window", [1, 24, 64, 65, 130])
+def test_tensor_core_attention_window_edge_and_far_key(window, row_tiles):
+    def prefer_outside(qs, ks, vs):
+        for q, k, v in zip(qs, ks, vs):
+            n = len(k)
+            if n - 1 - window >= 0:
+                k[n - 1 - window] = 0
+                k[n - 1 - window, :, 0] = 30.0
+                q[n - 1, :, 0] = 30.0
+                v[n - 1 - window] = 100.0
+    kw = dict(impl="mma", row_tiles=row_tiles)
+    got, want, _ = attention_case([200, 66, 25], [1, 1, 1], 6, 3, 32, "bfloat16", window=window, scale_up=prefer_outside, **kw)
+    assert float(want.abs().max()) < 50
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([200, 66], [200, 30], 6, 3, 32, "bfloat16", window=window, seed=4, **kw)
+    close(got, want, 1e-2)
+
+    def one_far_key(qs, ks, vs):
+        q, k, v = qs[0], ks[0], vs[0]
+        k[3] = 0; k[3, :, 5] = 16.0
+        q[-1] = 0; q[-1, :, 5] = 16.0
+        v[3] = 7.0
+    got, want, _ = attention_case([900], [1], 14, 2, 64, "bfloat16", scale_up=one_far_key, n_splits=4, **kw)
+    close(got, want, 1e-2)
+    assert float((got - 7.0).abs().max()) < 0.2
+
+
+def test_tensor_core_attention_ignores_what_lies_beyond_a_sequences_end():
+    """Pages are handed out dirty: whatever bit patterns follow a sequence's last token in its
+    last page (NaN here) must not reach the result."""
+    got, want, _ = attention_case([70, 5], [70, 1], 4, 2, 64, "bfloat16", impl="mma", row_tiles=4)
+    assert torch.isfinite(got).all()
+    close(got, want, 1e-2)
 
 
 def test_refusals_are_errors_not_wrong_results():
