@@ -214,6 +214,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_ml, cons
 
 }  // namespace mlc
 
+#ifndef MLC_KERNELS_ONLY   // a file that includes this one for its kernels defines its own entry points
 using namespace mlc;
 
 // q, out: [n_tokens][q_heads][hd] of `dtype`; the cache pools hold the same type.
@@ -299,3 +300,4 @@ extern "C" int mlc_attention_combine(const float* part_ml, const float* part_o, 
     MLC_LAUNCH_CHECK();
     return 0;
 }
+#endif  // MLC_KERNELS_ONLY

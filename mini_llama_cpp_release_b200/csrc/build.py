@@ -78,9 +78,14 @@ def _headers() -> List[str]:
     return sorted(f for f in os.listdir(_HERE) if f.endswith((".cuh", ".h")))
 
 
+# sources that other sources include
+INCLUDED_SOURCES = {"attention_noalloc.cu": ["attention_simt.cu"]}
+
+
 def _digest(sources: Sequence[str], defines: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for name in list(sources) + _headers():
+    extra = [inc for s in sources for inc in INCLUDED_SOURCES.get(s, [])]
+    for name in list(sources) + extra + _headers():
         h.update(name.encode())
         with open(os.path.join(_HERE, name), "rb") as f:
             h.update(f.read())
@@ -160,9 +165,15 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     return load_library(f"mlc_attn_hd{head_dim}", ["attention_mma.cu"], [f"-DMLC_HEAD_DIM={head_dim}"])
 
 
+def noalloc_library() -> ctypes.CDLL:
+    """The allocation-free attention entry point (csrc/attention_noalloc.h), a library of its
+    own so that only processes that ask for it hold its fixed scratch array."""
+    return load_library("mlc_noalloc", ["attention_noalloc.cu"])
+
+
 def build_everything(head_dims: Iterable[int] = (16, 64, 128)) -> List[str]:
     """Compile every library (the core and the attention variants for the given head sizes)."""
-    paths = [build_library("mlc_core", CORE_SOURCES)]
+    paths = [build_library("mlc_core", CORE_SOURCES), build_library("mlc_noalloc", ["attention_noalloc.cu"])]
     if os.path.exists(os.path.join(_HERE, "attention_mma.cu")):
         for hd in head_dims:
             paths.append(build_library(f"mlc_attn_hd{hd}", ["attention_mma.cu"], [f"-DMLC_HEAD_DIM={hd}"]))
