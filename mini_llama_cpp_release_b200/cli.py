@@ -1,0 +1,230 @@
+"""Command line in the manner of the reference's `mini-llama` (src/main.cpp:1415-1453):
+
+    python -m mini_llama_cpp_release_b200 generate --model DIR --tokens "5,17,3;9,9" -n 16
+    python -m mini_llama_cpp_release_b200 bench DIR -n 64 --prompt-len 128 --batch 4
+    python -m mini_llama_cpp_release_b200 inspect DIR
+    python -m mini_llama_cpp_release_b200 replay --model DIR --dtype float32 --out OUT --max-tokens 4096 < trace.jsonl
+
+Option names and meanings follow the reference where it has them (src/main.cpp:278-295,
+1204-1224): `--model`, `-n/--n-predict` (default 16; 64 for bench), `--temperature` (0 =
+greedy), `--top-k` (0 = off), `--seed` (0 = not reproducible), `--dump-logits <dir>`,
+`--device <N>`, `--verbose`.  There is no tokenizer here, so `-p/--prompt <text>` becomes
+`--tokens "<ids>"` with `;` between sequences; `--backend`, `--quant`, `--threads` and
+`--tokenizer` have nothing to select and are gone.  As in the reference, a first argument
+that is an option means `generate`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from typing import List, Optional, Sequence
+
+
+def parse_token_lists(text: str) -> List[List[int]]:
+    out = []
+    for part in text.split(";"):
+        part = part.strip()
+        if part:
+            out.append([int(t) for t in part.replace(",", " ").split()])
+    if not out:
+        raise SystemExit("no token ids given")
+    return out
+
+
+def add_engine_options(ap: argparse.ArgumentParser) -> None:
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
+    ap.add_argument("--device", type=int, default=0, help="CUDA device id (default: 0)")
+    ap.add_argument("--max-tokens", "--ctx", type=int, default=None, dest="max_tokens",
+                    help="tokens the cache holds (default: what the request needs)")
+
+
+def cmd_generate(argv: Sequence[str]) -> int:
+    ap = argparse.ArgumentParser(prog="mini-llama generate")
+    ap.add_argument("--model", required=True, help="model folder (config.json + model.safetensors)")
+    ap.add_argument("--tokens", help='prompt token ids, e.g. "5,17,3;9,9" (";" separates sequences)')
+    ap.add_argument("--tokens-file", help="file with one sequence of ids per line")
+    ap.add_argument("-n", "--n-predict", type=int, default=16, help="number of tokens to generate (default: 16)")
+    ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature (default: 0.0 = greedy)")
+    ap.add_argument("--top-k", type=int, default=0, help="top-k sampling (default: 0 = disabled)")
+    ap.add_argument("--seed", type=int, default=0, help="random seed for reproducible sampling (default: 0 = random)")
+    ap.add_argument("--stop-ids", default=None, help="comma-separated stop token ids (default: the model's eos_token_id)")
+    ap.add_argument("--dump-logits", default=None, help="dump the logits of every step to this directory")
+    add_engine_options(ap)
+    args = ap.parse_args(argv)
+    if not 0 <= args.n_predict <= 1_000_000:
+        raise SystemExit("--n-predict must be in 0..1000000")                            # src/main.cpp:66-79
+    if args.tokens_file:
+        with open(args.tokens_file) as f:
+            prompts = parse_token_lists(";".join(f.read().splitlines()))
+    elif args.tokens:
+        prompts = parse_token_lists(args.tokens)
+    else:
+        raise SystemExit("give --tokens or --tokens-file")
+
+    import torch
+    import mini_llama_cpp_release_b200 as ml
+    need = sum(((len(p) + args.n_predict + 63) // 64) * 64 for p in prompts)
+    llm = ml.load(args.model, dtype=args.dtype, device=f"cuda:{args.device}", max_tokens=args.max_tokens or need)
+    stop = [int(t) for t in args.stop_ids.split(",")] if args.stop_ids else None
+
+    on_step = None
+    if args.dump_logits:
+        os.makedirs(args.dump_logits, exist_ok=True)
+        counters = {}
+
+        def on_step(live, chosen, logits):                                               # src/main.cpp:297-307, 700-703
+            rows = logits.detach().float().cpu().numpy()
+            for row, i in enumerate(live):
+                k = counters.get(i, len(prompts[i]) - 1)
+                prefix = "" if len(prompts) == 1 else f"seq{i}_"
+                rows[row].astype("<f4").tofile(os.path.join(args.dump_logits, f"{prefix}logits_step{k}.bin"))
+                counters[i] = k + 1
+
+    results = llm.generate(prompts, n_predict=args.n_predict, temperature=args.temperature, top_k=args.top_k,
+                           seed=args.seed, stop_token_ids=stop, return_details=True, on_step=on_step)
+    for i, r in enumerate(results):
+        print(f"sequence {i}: prompt {r.prompt_len} tokens, generated {len(r.tokens)} ({r.finish_reason})")
+        print("generated ids:", " ".join(str(t) for t in r.tokens))
+    if args.dump_logits:
+        with open(os.path.join(args.dump_logits, "generation_tokens.txt"), "w") as f:       # src/main.cpp:322-337
+            for r in results:
+                f.write(" ".join(str(t) for t in r.tokens) + "\n")
+    return 0
+
+
+def cmd_bench(argv: Sequence[str]) -> int:
+    ap = argparse.ArgumentParser(prog="mini-llama bench")
+    ap.add_argument("model", help="model folder")
+    ap.add_argument("-n", "--n-predict", type=int, default=64, help="tokens to generate per sequence (default: 64)")
+    ap.add_argument("--prompt-len", type=int, default=128)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--verbose", action="store_true", help="print the logits' shape and top-5 after the prefill")
+    add_engine_options(ap)
+    args = ap.parse_args(argv)
+
+    import torch
+    import mini_llama_cpp_release_b200 as ml
+    from mini_llama_cpp_release_b200.engine import MiniBatch
+    from mini_llama_cpp_release_b200.sampling import DeviceSampler, SamplingParams
+    dev = f"cuda:{args.device}"
+    cfg = ml.ModelConfig.from_folder(args.model)
+    n_predict = max(1, min(args.n_predict, cfg.max_position_embeddings - args.prompt_len))   # src/main.cpp:1338-1340
+    per_seq = ((args.prompt_len + n_predict + 63) // 64) * 64
+    llm = ml.load(args.model, dtype=args.dtype, device=dev, max_tokens=args.max_tokens or args.batch * per_seq)
+    ctx = llm.context
+    g = torch.Generator().manual_seed(args.seed)
+    prompts = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt_len), generator=g).tolist()
+    sampler = DeviceSampler(SamplingParams(), llm.model.runtime.device)
+
+    def run():
+        slots = [ctx.acquire() for _ in prompts]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        logits = ctx.forward_batch(MiniBatch.prefill(slots, prompts))
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        first = logits.argmax(-1).tolist()                     # the first token is outside both timers (src/debug.cpp:122)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        toks = first
+        for _ in range(n_predict - 1):
+            toks, _ = ctx.decode_and_sample(slots, toks, sampler, list(range(len(slots))))
+        torch.cuda.synchronize()
+        t3 = time.perf_counter()
+        for s in slots:
+            ctx.release(s)
+        return logits, (t1 - t0) * 1e3, (t3 - t2) * 1e3
+
+    run()                                                       # warm-up: kernels compiled, graphs captured
+    logits, prefill_ms, decode_ms = run()
+    generated, decode_tokens = args.batch * n_predict, args.batch * (n_predict - 1)
+    if args.verbose:
+        print("logits shape:", list(logits.shape))
+        top = torch.topk(logits[0], 5)
+        print("top-5:", [(int(i), round(float(v), 4)) for v, i in zip(top.values, top.indices)])
+        print("cache:", f"{len(ctx.cache.groups)} group(s), {ctx.cache.n_pages} pages of {ctx.cache.page_size} tokens,",
+              f"{ctx.cache.bytes() / 2**20:.1f} MiB")
+    print(f"prompt tokens:     {args.batch * args.prompt_len}")
+    print(f"generated tokens:  {generated}")
+    print(f"decode tokens:     {decode_tokens}")
+    print(f"prefill ms:        {prefill_ms:.3f}")
+    print(f"decode ms:         {decode_ms:.3f}")
+    print(f"tokens/s (total):  {generated * 1000.0 / (prefill_ms + decode_ms):.1f}")          # include/mini_llama/debug.h:21-34
+    print(f"tokens/s (decode): {decode_tokens * 1000.0 / decode_ms:.1f}" if decode_tokens else "tokens/s (decode): n/a")
+    print(f"weight bytes:      {llm.model.load_summary.get('bytes', 0)}")
+    return 0
+
+
+def cmd_inspect(argv: Sequence[str]) -> int:
+    ap = argparse.ArgumentParser(prog="mini-llama inspect")
+    ap.add_argument("model", help="model folder")
+    args = ap.parse_args(argv)
+    from mini_llama_cpp_release_b200.config import ModelConfig, build_model_spec
+    from mini_llama_cpp_release_b200.engine.model import build_parts
+    from mini_llama_cpp_release_b200.weights import Checkpoint, compare, expected_tensors
+    cfg = ModelConfig.from_folder(args.model)
+    spec = build_model_spec(cfg)
+    print("config:")
+    for k, v in cfg.to_dict().items():
+        print(f"  {k}: {v}")
+    print(f"architecture: {cfg.architecture} -> {len(spec.layers)} layers, {len(spec.schedule)} runs per step")
+    specs = expected_tensors(build_parts(spec).all_parts())
+    with Checkpoint(args.model) as ck:
+        total = params = 0
+        print("tensors:")
+        for name, e in ck.entries.items():
+            nbytes = e.end - e.begin
+            total += nbytes
+            params += e.numel
+            role = specs[name].role if name in specs else "(not used)"
+            print(f"  {name:55s} {str(list(e.shape)):18s} {e.dtype:5s} {nbytes:12d} B  {role}")
+        problems = compare(ck.entries, specs, ["lm_head.weight"] if cfg.tie_word_embeddings else [])
+    print(f"parameters: {params}   bytes: {total}")
+    kv = 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim
+    print(f"cache per token per sequence: {kv * 2} B in bfloat16, {kv * 4} B in float32")
+    for line in problems:
+        print("PROBLEM:", line)
+    return 1 if problems else 0
+
+
+def cmd_replay(argv: Sequence[str]) -> int:
+    ap = argparse.ArgumentParser(prog="mini-llama replay")
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--max-tokens", type=int, required=True)
+    ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--trace", default=None, help="trace file (default: standard input)")
+    args = ap.parse_args(argv)
+    import mini_llama_cpp_release_b200 as ml
+    from mini_llama_cpp_release_b200.engine.replay import Replayer
+    llm = ml.load(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens)
+    src = open(args.trace) if args.trace else sys.stdin
+    return Replayer(llm.context, args.out).run(src, sys.stdout)
+
+
+COMMANDS = {"generate": cmd_generate, "bench": cmd_bench, "inspect": cmd_inspect, "replay": cmd_replay}
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv[0] in ("-h", "--help"):
+        print(__doc__)
+        return 0
+    if argv[0] == "--device-info":
+        import torch
+        for i in range(torch.cuda.device_count()):
+            p = torch.cuda.get_device_properties(i)
+            print(f"device {i}: {p.name}, sm_{p.major}{p.minor}, {p.multi_processor_count} SMs, {p.total_memory / 2**30:.1f} GiB")
+        return 0
+    if argv[0].startswith("-"):
+        return cmd_generate(argv)                                                          # src/main.cpp:1437-1447
+    cmd = COMMANDS.get(argv[0])
+    if cmd is None:
+        print(f"unknown command {argv[0]!r}; one of: {', '.join(COMMANDS)}", file=sys.stderr)
+        return 2
+    return cmd(argv[1:])
