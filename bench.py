@@ -234,6 +234,7 @@ def prefill_flops(cfg, layers: int, T: int) -> float:
 
 
 def main() -> int:
+    global PROMPT_LEN
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -242,6 +243,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--only", default=None, choices=["decode", "prefill"],
+                    help="run one part only and print a short line (for profiling a small case)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the --only runs")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -257,6 +261,8 @@ def main() -> int:
     import mini_llama_cpp_release_b200 as ml
     from mini_llama_cpp_release_b200 import kernels
 
+    if args.only:
+        PROMPT_LEN = max(1, min(args.prompt_len, CTX_LEN - 64))
     warmup = max(3, args.warmup)
     steps = max(1, min(args.steps, CTX_LEN - PROMPT_LEN - warmup - 8, 1000))
     pk = peaks()
@@ -264,6 +270,16 @@ def main() -> int:
     max_batch = max(args.batch, 1 if args.no_points else 64)
     llm = ml.load(folder, dtype="bfloat16", max_tokens=max_batch * CTX_LEN, max_seqs=max_batch)
     cache = llm.context.cache
+
+    if args.only == "prefill":
+        ms = time_prefill(llm, iters=max(1, min(args.steps, 5)), warmup=min(warmup, 3))
+        print(json.dumps({"only": "prefill", "ms": round(ms, 3), "tokens": PROMPT_LEN, "layers": args.layers}))
+        return 0
+    if args.only == "decode":
+        ms_step, tok_s, launches, lib_launches, mean_len, _ = time_decode(llm, args.batch, steps, warmup, seed=1)
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms_step, 4), "tokens_per_s": round(tok_s, 1),
+                          "launches_per_step": launches, "library_launches_per_step": lib_launches, "layers": args.layers}))
+        return 0
 
     prefill_ms = time_prefill(llm)
     flops = prefill_flops(QWEN2_0_5B, args.layers, PROMPT_LEN)

@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 ]
 
 # library name → (sources, extra -D flags may be added per variant)
-CORE_SOURCES = ["elementwise.cu", "attention_simt.cu", "sampling.cu", "linear_simt.cu"]
+CORE_SOURCES = ["elementwise.cu", "attention_simt.cu", "sampling.cu", "linear_simt.cu", "gemm_tcgen05.cu"]
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}

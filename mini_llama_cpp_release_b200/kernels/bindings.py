@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_library", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "decode_advance",
 ]
 
 
@@ -94,6 +94,7 @@ def core() -> ctypes.CDLL:
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
+            "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
             "mlc_decode_advance": [P, I, P, P, P, P, P, P, I, P],
@@ -341,3 +342,72 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
     if n_splits > 1:
         _check(core().mlc_attention_combine(part_ml.data_ptr(), part_o.data_ptr(), n_tokens * q_heads, n_splits, hd,
                                             out.data_ptr(), dtype_code(out.dtype), _stream()), "attention combine")
+
+
+EPI_STORE, EPI_SILU_MUL, EPI_QKV = 0, 1, 2
+_status = {}
+
+
+def gemm_status(device: torch.device) -> torch.Tensor:
+    """One int32 per device that the tensor-core kernels leave non-zero when a bounded wait ran out."""
+    key = torch.device(device).index or 0
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
+
+
+def check_gemm_status(device: torch.device) -> None:
+    """Raise if any tcgen05 kernel on this device gave up a wait (synchronises)."""
+    t = _status.get(torch.device(device).index or 0)
+    if t is not None:
+        code = int(t.item())
+        if code:
+            t.zero_()
+            who = {1: "the TMA loader", 2: "the tensor-core issuer", 3: "the epilogue"}.get(code, str(code))
+            raise KernelError(f"a tcgen05 matrix product gave up waiting on a barrier ({who}); its output is not valid")
+
+
+def gemm_block_tokens(n_tok: int, row_tiles: int, n_sms: int) -> int:
+    for bn in (16, 32, 64, 128):
+        if n_tok <= bn:
+            return bn
+    return 256 if row_tiles * ((n_tok + 255) // 256) >= n_sms else 128
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, n_splits: int = 1,
+                 block_tokens: Optional[int] = None, bias: Optional[torch.Tensor] = None,
+                 positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
+                 rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
+                 kv: Optional[KVView] = None, n_sms: int = 148) -> None:
+    """bfloat16 x [n, K] times bfloat16 w [rows, K] transposed on the tcgen05 tensor cores, with
+    the epilogue done before anything is stored (see csrc/gemm_tcgen05.cu)."""
+    require_cuda(x, w, out, bias, positions, tok_seq, rope)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 matrix product takes bfloat16 operands")
+    n_tok, K = x.shape
+    n_out = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    if K % 8:
+        raise KernelError(f"the tcgen05 matrix product needs an inner size that is a multiple of 8, got {K}")
+    if block_tokens is None:
+        block_tokens = gemm_block_tokens(n_tok, (n_out + 127) // 128, n_sms)
+    if epilogue == EPI_STORE:
+        assert out.numel() == n_splits * n_tok * n_out
+    elif epilogue == EPI_SILU_MUL:
+        assert out.numel() == n_tok * (n_out // 2) and n_splits == 1
+    else:
+        assert out.numel() == n_tok * q_heads * head_dim and n_splits == 1
+    if kv is not None:
+        assert kv.k_pool.dtype == out.dtype
+        cache = (kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset,
+                 kv.pages_per_seq, kv.page_size)
+    else:
+        cache = (None, None, None, 0, 0, 1)
+    status = gemm_status(x.device)
+    _check(core().mlc_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
+                                   block_tokens, n_splits, epilogue, status.data_ptr(), _ptr(bias), _ptr(positions),
+                                   _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
+                                   kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product")
