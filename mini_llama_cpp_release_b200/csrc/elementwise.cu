@@ -22,17 +22,19 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 }
 
 // ------------------------------------------------------------------ residual add + RMSNorm
-// x (float32, the residual stream) += delta when delta is given; out = x·scale·gain.
+// x (float32, the residual stream) += the sum of the delta slices, when given (a branch output,
+// possibly left as split-K partial sums [n_slices][n][d]); out = x·scale·gain.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
-                                   const float* __restrict__ gain, float eps, int d,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_slices,
+                                   long long slice_stride, const float* __restrict__ gain, float eps, int d,
                                    T* __restrict__ out) {
     __shared__ float scratch[32];
     const long long base = (long long)blockIdx.x * d;
     float ss = 0.0f;
     if (delta != nullptr) {
         for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            const float v = x[base + i] + delta[base + i];
+            float v = x[base + i];
+            for (int s = 0; s < n_slices; ++s) v += delta[s * slice_stride + base + i];
             x[base + i] = v;
             ss += v * v;
         }
@@ -132,13 +134,17 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gu, int inter, long long
 }
 
 // ------------------------------------------------------------------ row gather
-__global__ void gather_rows_kernel(const float* __restrict__ x, const float* __restrict__ delta,
-                                   const int* __restrict__ rows, int d, float* __restrict__ out_x,
-                                   float* __restrict__ out_delta) {
+__global__ void gather_rows_kernel(const float* __restrict__ x, const float* __restrict__ delta, int n_slices,
+                                   long long slice_stride, const int* __restrict__ rows, int d,
+                                   float* __restrict__ out_x, float* __restrict__ out_delta) {
     const long long src = (long long)rows[blockIdx.x] * d, dst = (long long)blockIdx.x * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         out_x[dst + i] = x[src + i];
-        if (delta != nullptr) out_delta[dst + i] = delta[src + i];
+        if (delta != nullptr) {
+            float v = 0.0f;
+            for (int s = 0; s < n_slices; ++s) v += delta[s * slice_stride + src + i];
+            out_delta[dst + i] = v;
+        }
     }
 }
 
@@ -174,15 +180,16 @@ extern "C" int mlc_embed(const void* table, int table_dtype, const int* ids, int
     return 0;
 }
 
-extern "C" int mlc_add_rmsnorm(float* x, const float* delta, const float* gain, float eps, int n, int d,
+extern "C" int mlc_add_rmsnorm(float* x, const float* delta, int n_slices, const float* gain, float eps, int n, int d,
                                void* out, int out_dtype, void* stream) {
     if (n <= 0) return 0;
-    if (d <= 0) return MLC_ERR_BAD_SIZE;
+    if (d <= 0 || (delta != nullptr && n_slices < 1)) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    const long long stride = (long long)n * d;
     if (out_dtype == MLC_DTYPE_F32)
-        add_rmsnorm_kernel<float><<<n, row_threads(d), 0, s>>>(x, delta, gain, eps, d, (float*)out);
+        add_rmsnorm_kernel<float><<<n, row_threads(d), 0, s>>>(x, delta, n_slices, stride, gain, eps, d, (float*)out);
     else if (out_dtype == MLC_DTYPE_BF16)
-        add_rmsnorm_kernel<bf16><<<n, row_threads(d), 0, s>>>(x, delta, gain, eps, d, (bf16*)out);
+        add_rmsnorm_kernel<bf16><<<n, row_threads(d), 0, s>>>(x, delta, n_slices, stride, gain, eps, d, (bf16*)out);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();
@@ -244,10 +251,11 @@ extern "C" int mlc_silu_mul(const void* gate_up, int in_dtype, int n, int inter,
     return 0;
 }
 
-extern "C" int mlc_gather_rows(const float* x, const float* delta, const int* rows, int n_rows, int d,
-                               float* out_x, float* out_delta, void* stream) {
+extern "C" int mlc_gather_rows(const float* x, const float* delta, int n_slices, long long slice_stride, const int* rows,
+                               int n_rows, int d, float* out_x, float* out_delta, void* stream) {
     if (n_rows <= 0) return 0;
-    gather_rows_kernel<<<n_rows, row_threads(d), 0, (cudaStream_t)stream>>>(x, delta, rows, d, out_x, out_delta);
+    gather_rows_kernel<<<n_rows, row_threads(d), 0, (cudaStream_t)stream>>>(x, delta, n_slices, slice_stride, rows, d,
+                                                                            out_x, out_delta);
     MLC_LAUNCH_CHECK();
     return 0;
 }

@@ -12,6 +12,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+from .. import kernels
 from ..cache.paged import PAGE_SIZE, PagedCache
 from .batch import MiniBatch, SequenceChunk
 from .decode_runner import DecodeRunner
@@ -132,6 +133,7 @@ class Context:
         with torch.cuda.device(self.model.runtime.device):
             step = self.describe(batch)
             logits = self.model.forward(step, self.cache)
+            kernels.check_gemm_status(self.model.runtime.device)      # a tensor-core kernel that gave up a wait is an error
         for c in batch.chunks:
             self.cache.commit(c.slot, len(c.tokens))
             self.token_history[c.slot].extend(c.tokens)                      # src/batch.cpp:49

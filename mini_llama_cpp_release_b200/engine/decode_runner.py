@@ -192,4 +192,7 @@ class DecodeRunner:
     def read_chosen(self) -> List[int]:
         self.chosen_host.copy_(self.view("chosen"), non_blocking=True)
         torch.cuda.current_stream(self.model.runtime.device).synchronize()
+        self.reads = getattr(self, "reads", 0) + 1
+        if self.reads % 64 == 1:
+            kernels.check_gemm_status(self.model.runtime.device)
         return self.chosen_host.tolist()

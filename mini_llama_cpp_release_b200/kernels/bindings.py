@@ -85,11 +85,11 @@ def core() -> ctypes.CDLL:
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
         sigs = {
             "mlc_embed": [P, I, P, I, I, P, P],
-            "mlc_add_rmsnorm": [P, P, P, F, I, I, P, I, P],
+            "mlc_add_rmsnorm": [P, P, I, P, F, I, I, P, I, P],
             "mlc_rope_table": [P, I, I, P, P],
             "mlc_qkv_post": [P, P, P, P, P, I, I, I, I, I, P, I, P, P, P, LL, I, I, I, P],
             "mlc_silu_mul": [P, I, I, I, P, I, P],
-            "mlc_gather_rows": [P, P, P, I, I, P, P, P],
+            "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
             "mlc_convert": [P, I, LL, P, I, P],
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
@@ -155,12 +155,16 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
                 out: torch.Tensor) -> None:
-    """x (float32) += delta if given; out = x * 1/sqrt(mean(x^2) + eps) * gain."""
+    """x (float32) += delta if given (delta [n, d], or partial sums [slices, n, d] that are added up);
+    out = x * 1/sqrt(mean(x^2) + eps) * gain."""
     require_cuda(x, delta, gain, out)
     n, d = x.shape
     assert x.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == d and out.shape == x.shape
-    assert delta is None or (delta.dtype == torch.float32 and delta.shape == x.shape)
-    _check(core().mlc_add_rmsnorm(x.data_ptr(), _ptr(delta), gain.data_ptr(), float(eps), n, d, out.data_ptr(),
+    n_slices = 1
+    if delta is not None:
+        assert delta.dtype == torch.float32 and tuple(delta.shape[-2:]) == (n, d)
+        n_slices = delta.shape[0] if delta.dim() == 3 else 1
+    _check(core().mlc_add_rmsnorm(x.data_ptr(), _ptr(delta), n_slices, gain.data_ptr(), float(eps), n, d, out.data_ptr(),
                                   dtype_code(out.dtype), _stream()), "rmsnorm")
 
 
@@ -226,10 +230,14 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 def gather_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, out_x: torch.Tensor,
                 out_delta: Optional[torch.Tensor]) -> None:
+    """out_x = x[rows]; out_delta = delta[rows] (summed over the leading axis if delta is [slices, n, d])."""
     require_cuda(x, delta, rows, out_x, out_delta)
     assert x.dtype == torch.float32 and rows.dtype == torch.int32
     assert (delta is None) == (out_delta is None)
-    _check(core().mlc_gather_rows(x.data_ptr(), _ptr(delta), rows.data_ptr(), rows.numel(), x.shape[1],
+    n_slices, stride = 1, 0
+    if delta is not None and delta.dim() == 3:
+        n_slices, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+    _check(core().mlc_gather_rows(x.data_ptr(), _ptr(delta), n_slices, stride, rows.data_ptr(), rows.numel(), x.shape[1],
                                   out_x.data_ptr(), _ptr(out_delta), _stream()), "gather")
 
 

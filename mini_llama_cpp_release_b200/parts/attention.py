@@ -75,13 +75,26 @@ class GQAttention(Part):
         super().bind(get, runtime)
         n = self.name
         wq, wk, wv = get(n + "q_proj.weight"), get(n + "k_proj.weight"), get(n + "v_proj.weight")
-        self.qkv = Linear(torch.cat([wq, wk, wv], dim=0), runtime)
+        w = torch.cat([wq, wk, wv], dim=0)
+        if self.qkv_bias:
+            bias = torch.cat([get(n + "q_proj.bias"), get(n + "k_proj.bias"), get(n + "v_proj.bias")]).to(torch.float32)
+        else:
+            bias = None
+        # The fused projection (bias, rotation and cache write inside the tcgen05 kernel's epilogue)
+        # wants each head's rows in the order (0, hd/2, 1, hd/2+1, ...): rotation partners then sit
+        # on neighbouring accumulator lanes.
+        self.fused = (runtime.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.hidden % 8 == 0
+                      and getattr(self.position, "fusable", False))
+        if self.fused:
+            half = self.hd // 2
+            within = torch.stack([torch.arange(half), torch.arange(half) + half], dim=1).reshape(-1)
+            order = (torch.arange(self.H + 2 * self.KV)[:, None] * self.hd + within[None, :]).reshape(-1).to(w.device)
+            w = w[order]
+            bias = bias[order] if bias is not None else None
+        self.qkv = Linear(w, runtime)
+        self.bias = bias.contiguous() if bias is not None else None
         self.q_only: Optional[Linear] = None                    # made when a run reads another run's cache
         self.o = Linear(get(n + "o_proj.weight"), runtime)
-        if self.qkv_bias:
-            self.bias = torch.cat([get(n + "q_proj.bias"), get(n + "k_proj.bias"), get(n + "v_proj.bias")]).to(torch.float32).contiguous()
-        else:
-            self.bias = None
         self.use_tensor_cores = runtime.dtype == torch.bfloat16 and self.hd % 16 == 0
         if self.use_tensor_cores:
             kernels.attention_library(self.hd)          # compiled now, for this model's head size, not at the first step
@@ -97,18 +110,24 @@ class GQAttention(Part):
         self.position.prepare(step.max_kv_len)
         table = self.position.table
         q = rt.empty(n, self.H * self.hd)
+        kv_heads = self.KV if memory.writes_cache else 0
         if memory.writes_cache:
-            qkv = self.qkv(h, torch.float32)
-            kernels.qkv_post(qkv, self.bias, step.positions, step.tok_seq, table, self.H, self.KV, self.hd, q, memory.kv)
+            proj, bias = self.qkv, self.bias
         else:
             if self.q_only is None:
                 self.q_only = Linear(self.qkv.weight[: self.H * self.hd], rt)   # a view of the fused rows
-            bias = self.bias[: self.H * self.hd].contiguous() if self.bias is not None else None
-            kernels.qkv_post(self.q_only(h, torch.float32), bias, step.positions, step.tok_seq, table, self.H, 0,
-                             self.hd, q, None)
+            proj = self.q_only
+            bias = self.bias[: self.H * self.hd] if self.bias is not None else None
+        if self.fused:
+            kernels.gemm_tcgen05(h, proj.weight, q, kernels.bindings.EPI_QKV, bias=bias, positions=step.positions,
+                                 tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
+                                 kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms)
+        else:
+            kernels.qkv_post(proj(h, torch.float32), bias, step.positions, step.tok_seq, table, self.H, kv_heads,
+                             self.hd, q, memory.kv if memory.writes_cache else None)
         o = rt.empty(n, self.H * self.hd)
         self.attend(q, o, step, memory.kv)
-        return self.o(o, torch.float32)
+        return self.o(o, torch.float32, partial_ok=True)
 
     def attend(self, q: torch.Tensor, o: torch.Tensor, step, kv) -> None:
         """Attention of the step's tokens over the cache entry `kv` (which already holds their keys)."""

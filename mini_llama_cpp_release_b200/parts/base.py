@@ -14,8 +14,9 @@ Interfaces (duck-typed; the classes below document them):
   position       prepare(runtime, n_positions); table (or None); rotate(x, positions)
   mixer          cache_need() -> CacheNeed | None; state_spec() -> StateSpec | None;
                  forward(h, step, memory) -> float32 [n, hidden] (the branch's output,
-                 not yet added to the residual stream)
-  feed_forward   forward(h, step) -> float32 [n, hidden]
+                 not yet added to the residual stream), or partial sums [slices, n, hidden]
+                 that the next norm adds up
+  feed_forward   forward(h, step) -> float32 [n, hidden] or [slices, n, hidden]
   block          forward(x, pending, step, memory) -> (x, pending): arranges norm, mixer,
                  norm, feed-forward around the residual stream; `pending` is a branch output
                  whose addition is left to the next norm kernel.

@@ -32,7 +32,16 @@ class SwiGLU(Part):
     def bind(self, get, runtime):
         super().bind(get, runtime)
         n = self.name
-        self.gate_up = Linear(torch.cat([get(n + "gate_proj.weight"), get(n + "up_proj.weight")], dim=0), runtime)
+        gate, up = get(n + "gate_proj.weight"), get(n + "up_proj.weight")
+        # The fused product (SiLU·mul inside the tcgen05 kernel's epilogue) wants gate_j and up_j on
+        # neighbouring rows: g0, u0, g1, u1, ...  Otherwise the rows are [gate; up].
+        self.fused = runtime.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 \
+            and self.hidden % 8 == 0
+        if self.fused:
+            w = torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden)
+        else:
+            w = torch.cat([gate, up], dim=0)
+        self.gate_up = Linear(w, runtime)
         self.down = Linear(get(n + "down_proj.weight"), runtime)
 
     def weight_bytes(self) -> int:
@@ -40,7 +49,9 @@ class SwiGLU(Part):
 
     def forward(self, h: torch.Tensor, step=None) -> torch.Tensor:
         rt = self.runtime
-        gu = self.gate_up(h, rt.dtype)
         a = rt.empty(h.shape[0], self.inter)
-        kernels.silu_mul(gu, a)
-        return self.down(a, torch.float32)
+        if self.fused:
+            kernels.gemm_tcgen05(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
+        else:
+            kernels.silu_mul(self.gate_up(h, rt.dtype), a)
+        return self.down(a, torch.float32, partial_ok=True)

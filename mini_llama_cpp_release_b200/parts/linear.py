@@ -1,13 +1,17 @@
 """y = x · Wᵀ for a weight stored [out, in] (src/matmul_optimized.cpp:40-54), the one
 contraction every part is made of.
 
-Which kernel runs is decided by the operand types, never by the model:
+Which kernel runs is decided by the operand types and sizes, never by the model:
   * any float32 operand (the whole 32-bit path, or a tensor the checkpoint stores in
     32-bit while the engine computes in bfloat16): the float32 multiply-add kernel of
     csrc/linear_simt.cu.  No tensor-core mode takes part.
-  * bfloat16 × bfloat16: the tensor-core matrix product with float32 accumulation.  Where
-    the reference calls cuBLAS for its linears (src/cuda_matmul.cpp:216-233) the library
-    product stands here too.
+  * bfloat16 × bfloat16 with an inner size that is a multiple of 8: the tcgen05/TMA kernel of
+    csrc/gemm_tcgen05.cu, always when an epilogue is fused (Q/K/V with bias, rotation and
+    cache write; gate/up with SiLU·mul), and for plain products of up to 64 rows (decoding),
+    where the K range is split over blocks and the partial sums are left to the consumer.
+  * plain bfloat16 products of more rows (prompts): the library's tensor-core product with
+    float32 accumulation, as the reference calls cuBLAS for its linears
+    (src/cuda_matmul.cpp:216-233).
 """
 from __future__ import annotations
 
@@ -18,6 +22,20 @@ import torch
 from .. import kernels
 from .base import Runtime
 
+SMALL_BATCH = 64          # up to this many rows a plain product runs on the tcgen05 kernel with split K
+
+
+def split_count(n_out: int, k: int, n_tok: int, n_sms: int) -> int:
+    """How many blocks share the K range of a skinny product: enough to occupy the SMs, each
+    with at least two 64-element K steps."""
+    if n_tok > SMALL_BATCH:
+        return 1
+    row_tiles = (n_out + 127) // 128
+    k_blocks = (k + 63) // 64
+    s = max(1, min(n_sms // max(1, row_tiles), k_blocks // 2))
+    per = (k_blocks + s - 1) // s
+    return (k_blocks + per - 1) // per
+
 
 class Linear:
     def __init__(self, weight: torch.Tensor, runtime: Runtime):
@@ -25,20 +43,29 @@ class Linear:
         self.weight = weight.contiguous()
         self.runtime = runtime
         self.out_features, self.in_features = weight.shape
+        self.tensor_core_ok = (weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
+                               and self.weight.data_ptr() % 16 == 0)
 
     def nbytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype = torch.float32,
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype = torch.float32, partial_ok: bool = False) -> torch.Tensor:
+        """[n, out] in `out_dtype`; with `partial_ok` possibly float32 partial sums [slices, n, out]
+        whose sum over the first axis is the product."""
         assert x.dim() == 2 and x.shape[1] == self.in_features, (x.shape, self.weight.shape)
+        rt = self.runtime
         m = x.shape[0]
-        if out is None:
-            out = self.runtime.empty(m, self.out_features, dtype=out_dtype)
         if x.dtype == torch.float32 or self.weight.dtype == torch.float32:
+            out = rt.empty(m, self.out_features, dtype=out_dtype)
             kernels.linear_simt(x, self.weight, out)
             return out
         kernels.require_cuda(x)
+        if self.tensor_core_ok and m <= SMALL_BATCH:
+            splits = split_count(self.out_features, self.in_features, m, rt.n_sms) if (partial_ok and out_dtype == torch.float32) else 1
+            out = rt.empty(splits, m, self.out_features, dtype=out_dtype)
+            kernels.gemm_tcgen05(x, self.weight, out, kernels.bindings.EPI_STORE, splits, n_sms=rt.n_sms)
+            return out if splits > 1 else out[0]
+        out = rt.empty(m, self.out_features, dtype=out_dtype)
         if out.dtype == torch.float32:
             torch.mm(x, self.weight.t(), out_dtype=torch.float32, out=out)
         else:

@@ -232,6 +232,91 @@ def test_float32_linear_takes_any_size_and_gives_each_row_the_same_sum(M, N, K, 
     assert torch.equal(y1[0], y[M - 1])                               # bit for bit, whatever the batch
 
 
+@pytest.mark.parametrize("T,N,K,bn,splits", [(16, 128, 64, 16, 1), (1, 1000, 344, None, 1), (8, 896, 4864, 16, 19),
+                                              (64, 1152, 896, 64, 1), (200, 300, 72, None, 1), (33, 130, 176, 64, 2),
+                                              (600, 264, 128, 256, 1), (300, 777, 200, 128, 1)])
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+def test_tcgen05_product_plain_store(T, N, K, bn, splits, out_dtype):
+    g = torch.Generator().manual_seed(T + N)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    out = torch.full((splits, T, N), float("nan"), dtype=DT[out_dtype], device=DEV)
+    kernels.gemm_tcgen05(x.to(DEV), w.to(DEV), out, 0, splits, bn)
+    kernels.check_gemm_status(DEV)
+    close(out.float().sum(0), x.double() @ w.double().t(), 3e-6 if out_dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("T,I,K", [(5, 344, 128), (64, 100, 72), (300, 4864, 896)])
+def test_tcgen05_product_with_silu_mul_epilogue(T, I, K):
+    g = torch.Generator().manual_seed(I)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    gate = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    up = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()          # g0, u0, g1, u1, ...
+    out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05(x.to(DEV), w.to(DEV), out, 1)
+    kernels.check_gemm_status(DEV)
+    gg, uu = x.float() @ gate.float().t(), x.float() @ up.float().t()
+    close(out.float(), gg * (1 / (1 + torch.exp(-gg))) * uu, 8e-3)
+
+
+@pytest.mark.parametrize("H,KV,hd,T", [(6, 3, 32, 9), (14, 2, 64, 70), (3, 1, 16, 5), (2, 2, 80, 130), (2, 1, 256, 3)])
+def test_tcgen05_product_with_qkv_epilogue(H, KV, hd, T):
+    """Bias, rotation and cache write inside the product's epilogue, rows stored pair-interleaved."""
+    K = 72
+    g = torch.Generator().manual_seed(hd)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((H + 2 * KV) * hd, K, generator=g) * 0.3).to(torch.bfloat16)
+    bias = torch.randn((H + 2 * KV) * hd, generator=g)
+    half = hd // 2
+    within = torch.stack([torch.arange(half), torch.arange(half) + half], dim=1).reshape(-1)
+    order = (torch.arange(H + 2 * KV)[:, None] * hd + within[None, :]).reshape(-1)
+    lens = [T - T // 3 + 66, T // 3] if T >= 3 else [T + 66]
+    q_lens = [T - T // 3, T // 3] if T >= 3 else [T]
+    positions = torch.cat([torch.arange(n - m, n) for n, m in zip(lens, q_lens)]).to(torch.int32)
+    tok_seq = torch.cat([torch.full((m,), b) for b, m in enumerate(q_lens)]).to(torch.int32)
+    kv = make_paged([torch.zeros(n, KV, hd) for n in lens], [torch.zeros(n, KV, hd) for n in lens], torch.bfloat16)
+    table = kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), 512)
+    q_out = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05(x.to(DEV), w[order].contiguous().to(DEV), q_out, 2, bias=bias[order].contiguous().to(DEV),
+                         positions=positions.to(DEV), tok_seq=tok_seq.to(DEV), rope=table, q_heads=H, kv_heads=KV,
+                         head_dim=hd, kv=kv)
+    kernels.check_gemm_status(DEV)
+    full = x.float() @ w.float().t() + bias
+    q_want = plain_impl.rope_neox(full[:, :H * hd].reshape(T, H, hd), positions, 1e6)
+    k_want = plain_impl.rope_neox(full[:, H * hd:(H + KV) * hd].reshape(T, KV, hd), positions, 1e6)
+    v_want = full[:, (H + KV) * hd:].reshape(T, KV, hd)
+    close(q_out.float().view(T, H, hd), q_want, 8e-3)
+    pages = kv.page_table.cpu()
+    k_got = torch.stack([kv.k_pool[1, int(pages[tok_seq[n], positions[n] // 64]), :, positions[n] % 64].float().cpu() for n in range(T)])
+    v_got = torch.stack([kv.v_pool[1, int(pages[tok_seq[n], positions[n] // 64]), :, positions[n] % 64].float().cpu() for n in range(T)])
+    close(k_got, k_want, 8e-3)
+    close(v_got, v_want, 8e-3)
+    assert torch.isnan(kv.k_pool[0].float()).all()
+
+
+def test_tcgen05_product_refuses_what_it_cannot_take():
+    x = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(kernels.KernelError, match="multiple of 8"):
+        kernels.gemm_tcgen05(x, w, torch.empty(1, 4, 8, device=DEV))
+    with pytest.raises(kernels.KernelError, match="bfloat16"):
+        kernels.gemm_tcgen05(x.float(), w, torch.empty(1, 4, 8, device=DEV))
+
+
+def test_norm_and_gather_add_up_split_partial_sums():
+    x, parts, gain = torch.randn(5, 72), torch.randn(7, 5, 72), torch.ones(72)
+    xd = x.clone().to(DEV)
+    out = torch.empty(5, 72, device=DEV)
+    kernels.add_rmsnorm(xd, parts.to(DEV), gain.to(DEV), 1e-6, out)
+    close(xd, x + parts.sum(0), 1e-6)
+    close(out, plain_impl.rmsnorm(x + parts.sum(0), gain, 1e-6), 3e-6)
+    rows = torch.tensor([4, 0], dtype=torch.int32, device=DEV)
+    ox, od = torch.empty(2, 72, device=DEV), torch.empty(2, 72, device=DEV)
+    kernels.gather_rows(x.to(DEV), parts.to(DEV), rows, ox, od)
+    close(od, parts.sum(0)[[4, 0]], 1e-6)
+
+
 def test_argmax_lowest_index_wins():
     logits = torch.randn(4, 151936)
     logits[0, 77] = 50; logits[0, 150000] = 50
