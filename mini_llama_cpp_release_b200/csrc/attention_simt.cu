@@ -188,25 +188,36 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
 }
 
 // Merge the partial results of the key splits of each (token, head) row; one warp per row.
+// The lanes first share out the splits (maximum, weights, sum), then the output dims; the
+// loads of a lane do not depend on each other, so they are in flight together.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_o,
                                          long long n_rows, int n_splits, int hd, T* __restrict__ out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n_rows) return;
     const int lane = threadIdx.x & 31;
+    const float* ml = part_ml + row * n_splits * 2;
     float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(row * n_splits + s) * 2]);
+    for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, __ldg(ml + 2 * s));
+    M = warp_max(M);
     float L = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = part_ml[(row * n_splits + s) * 2];
-        if (ms != -INFINITY) L += part_ml[(row * n_splits + s) * 2 + 1] * expf(ms - M);
+    for (int s = lane; s < n_splits; s += 32) {
+        const float ms = __ldg(ml + 2 * s);
+        if (ms != -INFINITY) L += __ldg(ml + 2 * s + 1) * expf(ms - M);
     }
+    L = warp_sum(L);
     const float inv = 1.0f / L;
+    const float* po = part_o + row * n_splits * hd;
     for (int d = lane; d < hd; d += 32) {
         float o = 0.0f;
+#pragma unroll 8
         for (int s = 0; s < n_splits; ++s) {
-            const float ms = part_ml[(row * n_splits + s) * 2];
-            if (ms != -INFINITY) o += part_o[(row * n_splits + s) * hd + d] * expf(ms - M);
+            const float ms = __ldg(ml + 2 * s);
+            const float w = (ms != -INFINITY) ? expf(ms - M) : 0.0f;
+            const float v = __ldg(po + (long long)s * hd + d);
+            o += (w != 0.0f) ? v * w : 0.0f;           // an empty split's values were never written
         }
         out[row * hd + d] = from_float<T>(o * inv);
     }

@@ -28,6 +28,37 @@ namespace mlc {
 
 typedef __nv_bfloat16 bf16;
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched through launch_pdl may start while the kernel before it on the stream is still
+// running; it must call grid_dependency_wait() before it reads anything an earlier kernel wrote
+// (the wait returns once every earlier kernel has finished and its writes are visible), and it
+// calls grid_launch_dependents() to let the kernel after it start in the same way.  The launch
+// latency of a chain of short kernels then overlaps with their execution.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Whether kernels are launched with the programmatic-serialization attribute (one switch per library).
+inline int& pdl_enabled() {
+    static int enabled = 1;
+    return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
 

@@ -29,12 +29,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
                                    long long slice_stride, const float* __restrict__ gain, float eps, int d,
                                    T* __restrict__ out) {
     __shared__ float scratch[32];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const long long base = (long long)blockIdx.x * d;
     float ss = 0.0f;
     if (delta != nullptr) {
         for (int i = threadIdx.x; i < d; i += blockDim.x) {
             float v = x[base + i];
-            for (int s = 0; s < n_slices; ++s) v += delta[s * slice_stride + base + i];
+#pragma unroll 8
+            for (int s = 0; s < n_slices; ++s) v += __ldg(delta + s * slice_stride + base + i);
             x[base + i] = v;
             ss += v * v;
         }
@@ -161,6 +164,14 @@ static inline int row_threads(int d) {
     return t;
 }
 
+// Few rows: one element per thread where the row allows it, so that every load of the row is in flight at once.
+static inline int norm_threads(int d, int n) {
+    if (n > 1024) return row_threads(d);
+    int t = 32;
+    while (t < d && t < 1024) t <<= 1;
+    return t;
+}
+
 }  // namespace mlc
 
 using namespace mlc;
@@ -186,13 +197,14 @@ extern "C" int mlc_add_rmsnorm(float* x, const float* delta, int n_slices, const
     if (d <= 0 || (delta != nullptr && n_slices < 1)) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const long long stride = (long long)n * d;
+    cudaError_t e;
     if (out_dtype == MLC_DTYPE_F32)
-        add_rmsnorm_kernel<float><<<n, row_threads(d), 0, s>>>(x, delta, n_slices, stride, gain, eps, d, (float*)out);
+        e = launch_pdl(add_rmsnorm_kernel<float>, dim3(n), dim3(norm_threads(d, n)), 0, s, x, delta, n_slices, stride, gain, eps, d, (float*)out);
     else if (out_dtype == MLC_DTYPE_BF16)
-        add_rmsnorm_kernel<bf16><<<n, row_threads(d), 0, s>>>(x, delta, n_slices, stride, gain, eps, d, (bf16*)out);
+        e = launch_pdl(add_rmsnorm_kernel<bf16>, dim3(n), dim3(norm_threads(d, n)), 0, s, x, delta, n_slices, stride, gain, eps, d, (bf16*)out);
     else
         return MLC_ERR_BAD_DTYPE;
-    MLC_LAUNCH_CHECK();
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
 
@@ -271,5 +283,11 @@ extern "C" int mlc_convert(const void* in, int in_dtype, long long total, void* 
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+// Switch programmatic dependent launch on (1, the default) or off (0) for this library's kernels.
+extern "C" int mlc_set_pdl(int enabled) {
+    mlc::pdl_enabled() = enabled ? 1 : 0;
     return 0;
 }

@@ -135,7 +135,8 @@ template <int BN> struct GemmShape {
     static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN <= 64) ? 8 : (BN <= 128 ? 6 : 4);
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int META_BYTES = BN * 16;      // per token: position, cache offset (QKV epilogue)
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + META_BYTES;
 };
 
 template <typename T> __device__ __forceinline__ void store_out(void* base, long long idx, float v) {
@@ -157,6 +158,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const unsigned tmem_slot = bar_base + 8u * (2 * S::STAGES + 1);
     unsigned char* smem_generic = smem_dyn + (base - smem_u32(smem_dyn));
     volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + S::STAGES * S::STAGE_BYTES + 8 * (2 * S::STAGES + 1));
+    int* tok_pos = reinterpret_cast<int*>(smem_generic + S::STAGES * S::STAGE_BYTES + 256);              // [BN]
+    long long* tok_off = reinterpret_cast<long long*>(tok_pos + BN);                                      // [BN], 8-byte aligned: BN*4 is a multiple of 8
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * G_BM, n0 = blockIdx.y * BN, split = blockIdx.z;
@@ -219,6 +222,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else {
         // ---------------- epilogue: warp q reads tensor-memory lanes 32q .. 32q+31
         const int q = warp & 3;
+        if (EPI == EPI_QKV) {
+            for (int t = threadIdx.x - 64; t < BN; t += 128) {
+                int p = 0;
+                long long off = 0;
+                if (n0 + t < g.n_tok) {
+                    p = __ldg(g.positions + n0 + t);
+                    if (g.kv_heads > 0) off = paged_offset(g.cache, __ldg(g.tok_seq + n0 + t), p, 0);
+                }
+                tok_pos[t] = p;
+                tok_off[t] = off;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps only
+        }
         const bool ok = mbar_wait(accum_bar, 0, g.status, 3);
         tcgen05_fence_after();
         const int row = m0 + q * 32 + lane;
@@ -256,35 +272,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 } else {
                     // QKV: stored row order inside a head is (0, hd/2, 1, hd/2+1, ...): even lane holds
-                    // dim i = (row % hd) / 2, its odd neighbour dim i + hd/2
+                    // dim i = (row % hd) / 2, its odd neighbour dim i + hd/2.  Positions and cache offsets
+                    // of the tile's tokens were put in shared memory while the products ran.
                     const int hd = g.hd, half = hd >> 1;
                     const int head = row / hd, within = row % hd;
                     const int i = within >> 1;
                     const bool second = (within & 1) != 0;
-                    const float b = (g.bias != nullptr && row < g.n_out) ? g.bias[row] : 0.0f;
+                    const int d = second ? i + half : i;
+                    const bool row_ok = row < g.n_out;
+                    const float b = (g.bias != nullptr && row_ok) ? __ldg(g.bias + row) : 0.0f;
+                    const bool rotate = head < g.q_heads + g.kv_heads && g.rope != nullptr;
+                    const bool is_q = head < g.q_heads;
+                    const bool is_k = !is_q && head < g.q_heads + g.kv_heads;
+                    const int kvh = is_k ? head - g.q_heads : head - g.q_heads - g.kv_heads;
+                    const long long head_off = (long long)kvh * g.cache.page_size * hd + d;
+                    // rotation factors of the 16 tokens first (independent loads), then arithmetic and stores
+                    float2 cs[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int tok = n0 + c0 + j;
+                        const int t = c0 + j;
+                        cs[j] = make_float2(1.0f, 0.0f);
+                        if (rotate && row_ok && n0 + t < g.n_tok)
+                            cs[j] = __ldg(g.rope + (long long)min(tok_pos[t], g.rope_positions - 1) * half + i);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = c0 + j;
                         const float mine = v[j] + b;
                         const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                        if (row >= g.n_out || tok >= g.n_tok) continue;
-                        const int p = g.positions[tok];
-                        float y = mine;
-                        if (head < g.q_heads + g.kv_heads && g.rope != nullptr) {
-                            const float2 cs = g.rope[(long long)min(p, g.rope_positions - 1) * half + i];
-                            // first half: x0·c − x1·s; second half: x0·s + x1·c, with (x0, x1) = (dim i, dim i + hd/2)
-                            y = second ? (other * cs.y + mine * cs.x) : (mine * cs.x - other * cs.y);
-                        }
-                        const int d = second ? i + half : i;
-                        if (head < g.q_heads) {
-                            const long long idx = ((long long)tok * g.q_heads + head) * hd + d;
+                        // first half: x0·c − x1·s; second half: x0·s + x1·c, with (x0, x1) = (dim i, dim i + hd/2)
+                        const float y = second ? (other * cs[j].y + mine * cs[j].x) : (mine * cs[j].x - other * cs[j].y);
+                        if (!row_ok || n0 + t >= g.n_tok) continue;
+                        if (is_q) {
+                            const long long idx = ((long long)(n0 + t) * g.q_heads + head) * hd + d;
                             if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, y);
                             else store_out<bf16>(g.out, idx, y);
                         } else {
-                            const bool is_k = head < g.q_heads + g.kv_heads;
-                            const int kvh = is_k ? head - g.q_heads : head - g.q_heads - g.kv_heads;
-                            const long long off = paged_offset(g.cache, g.tok_seq[tok], p, kvh) + d;
                             void* pool = is_k ? g.cache.k_pool : g.cache.v_pool;
+                            const long long off = tok_off[t] + head_off;
                             if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(pool, off, y);
                             else store_out<bf16>(pool, off, y);
                         }
@@ -361,7 +386,9 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 using namespace mlc;
 
 // x: bfloat16 [n_tok][K]; w: bfloat16 [n_out][K] (K a multiple of 8, both 16-byte aligned).
-// epilogue 0: out [n_splits][n_tok][n_out] (float32 or bfloat16); 1: out [n_tok][n_out/2], n_splits must be 1;
+// epilogue 0: out [n_splits][n_tok][n_out] (float32 or bfloat16): with n_splits > 1 the K range is shared out over
+// blocks and each leaves its partial sums in its own slice for the consumer to add; 1: out [n_tok][n_out/2],
+// n_splits must be 1;
 // 2: out = q [n_tok][q_heads*hd], k and v go to the cache, n_splits must be 1.
 // block_tokens: 16, 32, 64, 128 or 256.  status: one int on the device, 0 before the call; a bounded
 // wait that ran out leaves 1 (loader), 2 (tensor cores) or 3 (epilogue) there.

@@ -75,6 +75,42 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* 
     if (threadIdx.x == 0) out[blockIdx.x] = (best.i == 0x7fffffff) ? 0 : best.i;
 }
 
+// The same over many blocks per row: block (chunk, row) reduces its part of the row and leaves
+// (value, index) in `partial`; the block that finishes a row last (counted in `done`, which it
+// sets back to zero) merges the row's partial results.  `done` must be zero before the first call.
+constexpr int ARGMAX_CHUNKS = 64;
+__global__ void __launch_bounds__(256)
+argmax_split_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out, float* __restrict__ partial_v,
+                    int* __restrict__ partial_i, unsigned int* __restrict__ done) {
+    __shared__ MaxIdx scratch[32];
+    __shared__ bool is_last;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int r = blockIdx.y, chunk = blockIdx.x;
+    const float* row = logits + (long long)r * vocab;
+    const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int begin = chunk * per, end = min(vocab, begin + per);
+    MaxIdx best{-INFINITY, 0x7fffffff};
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, MaxIdx{__ldg(row + i), i});
+    best = block_argmax(best, scratch);
+    if (threadIdx.x == 0) {
+        partial_v[r * ARGMAX_CHUNKS + chunk] = best.v;
+        partial_i[r * ARGMAX_CHUNKS + chunk] = best.i;
+        __threadfence();
+        is_last = atomicAdd(&done[r], 1u) == ARGMAX_CHUNKS - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    MaxIdx m{-INFINITY, 0x7fffffff};
+    if (threadIdx.x < ARGMAX_CHUNKS) m = MaxIdx{partial_v[r * ARGMAX_CHUNKS + threadIdx.x], partial_i[r * ARGMAX_CHUNKS + threadIdx.x]};
+    m = block_argmax(m, scratch);
+    if (threadIdx.x == 0) {
+        out[r] = (m.i == 0x7fffffff) ? 0 : m.i;
+        done[r] = 0;
+    }
+}
+
 // Inclusive scan of one float per thread over the block; returns this thread's inclusive
 // prefix, *total gets the block's sum.  scratch: 32 floats.
 __device__ __forceinline__ float block_scan(float v, float* scratch, float* total) {
@@ -305,6 +341,16 @@ extern "C" int mlc_argmax(const float* logits, int rows, int vocab, int* out, vo
 
 // temperature > 0.  top_k == 0: the whole vocabulary in index order; 2 <= top_k <= 1024 (after
 // clamping to the vocabulary): sorted candidates.  Greedy cases go to mlc_argmax.
+// scratch: rows * 64 floats, rows * 64 ints and rows counters that are zero (they are left zero).
+extern "C" int mlc_argmax_split(const float* logits, int rows, int vocab, int* out, float* partial_v, int* partial_i,
+                                unsigned int* done, void* stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || rows > 65535) return MLC_ERR_BAD_SIZE;
+    cudaError_t e = launch_pdl(argmax_split_kernel, dim3(ARGMAX_CHUNKS, rows), dim3(256), 0, (cudaStream_t)stream, logits, vocab, out,
+                               partial_v, partial_i, done);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
 extern "C" int mlc_sample(const float* logits, int rows, int vocab, float temperature, int top_k,
                           unsigned long long seed, const int* seq_ids, const int* positions, int* out,
                           void* stream) {

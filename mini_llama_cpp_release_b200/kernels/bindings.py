@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -96,6 +96,7 @@ def core() -> ctypes.CDLL:
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
+            "mlc_argmax_split": [P, I, I, P, P, P, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
             "mlc_decode_advance": [P, I, P, P, P, P, P, P, I, P],
         }
@@ -103,6 +104,8 @@ def core() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        lib.mlc_set_pdl.argtypes = [c_int]
+        lib.mlc_set_pdl.restype = c_int
         lib.mlc_uniform_of.argtypes = [c_ulonglong, c_int, c_int]
         lib.mlc_uniform_of.restype = c_float
         _core = lib
@@ -251,10 +254,27 @@ def linear_simt(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
                                   dtype_code(y.dtype), m, n, k, _stream()), "linear")
 
 
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """First index of the maximum of every row.  Large rows are shared out over 64 blocks each,
+    with scratch memory that is kept per device and row count."""
     require_cuda(logits, out)
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == logits.shape[0]
-    _check(core().mlc_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()), "argmax")
+    rows, vocab = logits.shape
+    if vocab < 16384:
+        _check(core().mlc_argmax(logits.data_ptr(), rows, vocab, out.data_ptr(), _stream()), "argmax")
+        return
+    key = (logits.device.index or 0, rows)
+    scratch = _argmax_scratch.get(key)
+    if scratch is None:
+        scratch = (torch.empty(rows * 64, dtype=torch.float32, device=logits.device),
+                   torch.empty(rows * 64, dtype=torch.int32, device=logits.device),
+                   torch.zeros(rows, dtype=torch.int32, device=logits.device))
+        _argmax_scratch[key] = scratch
+    _check(core().mlc_argmax_split(logits.data_ptr(), rows, vocab, out.data_ptr(), scratch[0].data_ptr(),
+                                   scratch[1].data_ptr(), scratch[2].data_ptr(), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, seq_ids: torch.Tensor,
@@ -277,6 +297,11 @@ def decode_advance(chosen: torch.Tensor, tokens: torch.Tensor, positions: torch.
     _check(core().mlc_decode_advance(chosen.data_ptr(), n, tokens.data_ptr(), positions.data_ptr(), start_pos.data_ptr(),
                                      sample_pos.data_ptr(), _ptr(history), counter.data_ptr(), max_steps, _stream()),
            "decode advance")
+
+
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch for this package's kernels (on by default)."""
+    core().mlc_set_pdl(1 if enabled else 0)
 
 
 def uniform_of(seed: int, seq_id: int, position: int) -> float:
@@ -324,7 +349,7 @@ def attention_mma_plan(max_q_len: int, n_seqs: int, max_kv_len: int, q_heads: in
     n_splits = 1
     if blocks < 2 * n_sms:
         by_fill = (2 * n_sms + blocks - 1) // blocks
-        by_len = max(1, max_kv_len // 256)              # at least four 64-key tiles per split
+        by_len = max(1, max_kv_len // 128)              # at least two 64-key tiles per split
         n_splits = max(1, min(by_fill, by_len, 64))
     return row_tiles, n_splits
 

@@ -23,6 +23,7 @@ from .. import kernels
 from .base import Runtime
 
 SMALL_BATCH = 64          # up to this many rows a plain product runs on the tcgen05 kernel with split K
+MAX_SPLITS = 8            # partial sums the consumer has to add
 
 
 def split_count(n_out: int, k: int, n_tok: int, n_sms: int) -> int:
@@ -32,7 +33,7 @@ def split_count(n_out: int, k: int, n_tok: int, n_sms: int) -> int:
         return 1
     row_tiles = (n_out + 127) // 128
     k_blocks = (k + 63) // 64
-    s = max(1, min(n_sms // max(1, row_tiles), k_blocks // 2))
+    s = max(1, min(n_sms // max(1, row_tiles), k_blocks // 2, MAX_SPLITS))
     per = (k_blocks + s - 1) // s
     return (k_blocks + per - 1) // per
 
