@@ -11,7 +11,7 @@
 // (token, query head) pair, and all rows of a block share one kv head, so the G query heads
 // of a group ride on the same key and value tiles (for 14 heads on 2 kv heads: 9 tokens x 7
 // heads per 64-row tile).  Keys come in tiles of 64, one cache page, copied to shared
-// memory with cp.async in two stages.
+// memory with cp.async, two to four tiles ahead.
 //   RT = 4: each warp owns 16 rows and walks all 64 keys of a tile (prompts, chunks).
 //   RT = 1: the block has 16 rows (one decoded token's group of heads) and the four warps
 //           split each tile's keys 4 x 16, merging their partial results at the end.
@@ -34,6 +34,8 @@ constexpr int CPR = HD / 8;              // 16-byte chunks per row
 constexpr int KS_QK = HD / 16;           // k-steps of q·k
 constexpr int NT_O = HD / 8;             // output n-tiles
 constexpr bool Q_IN_REGS = (HD <= 128);
+constexpr int NSTAGE = (HD <= 64) ? 3 : 2;   // key/value tiles in flight per block
+constexpr int MAX_TILES_STAGED = 1024;   // page numbers kept in shared memory (65,536 keys); later tiles look theirs up
 
 struct MmaArgs {
     const bf16* q;            // [N][H][HD]
@@ -91,8 +93,8 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [ROWS][STRIDE]
-    bf16* Ks = Qs + ROWS * STRIDE;                                // [2][TILE][STRIDE]
-    bf16* Vs = Ks + 2 * TILE * STRIDE;                            // [2][TILE][STRIDE]
+    bf16* Ks = Qs + ROWS * STRIDE;                                // [NSTAGE][TILE][STRIDE]
+    bf16* Vs = Ks + NSTAGE * TILE * STRIDE;                       // [NSTAGE][TILE][STRIDE]
 
     const int b = blockIdx.z;
     int y = blockIdx.y;
@@ -129,10 +131,18 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     const int my_begin = tile_begin + split * per_split;
     const int my_end = min(tile_end, my_begin + per_split);
 
+    // the pages of this block's tiles, fetched once: a lookup in global memory per tile would put
+    // its latency in front of every tile's copies
+    __shared__ int tile_pages[MAX_TILES_STAGED];
+    for (int t = my_begin + tid; t < my_end && t - my_begin < MAX_TILES_STAGED; t += 128)
+        tile_pages[t - my_begin] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
+    __syncthreads();
+
     const bf16* kp = (const bf16*)c.k_pool;
     const bf16* vp = (const bf16*)c.v_pool;
     auto load_tile = [&](int stage, int tile) {
-        const int page = c.page_table[(long long)b * c.pages_per_seq + tile];
+        const int page = (tile - my_begin < MAX_TILES_STAGED) ? tile_pages[tile - my_begin]
+                                                              : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
         const long long base = c.entry_offset + ((long long)max(page, 0) * c.kv_heads + kvh) * TILE * HD;
         bf16* kd = Ks + stage * TILE * STRIDE;
         bf16* vd = Vs + stage * TILE * STRIDE;
@@ -170,8 +180,11 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
 
     unsigned qf[Q_IN_REGS ? KS_QK : 1][4];
 
-    if (my_begin < my_end) {
-        load_tile(0, my_begin);
+    // tiles my_begin .. my_begin + NSTAGE - 2 are requested before the loop; every iteration requests
+    // one more and waits until all but the NSTAGE - 1 newest requests have landed
+#pragma unroll
+    for (int p = 0; p < NSTAGE - 1; ++p) {
+        if (my_begin + p < my_end) load_tile(p, my_begin + p);
         cp_async_commit();
     }
     __syncthreads();                       // Qs is staged
@@ -182,14 +195,10 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     }
 
     for (int tile = my_begin, it = 0; tile < my_end; ++tile, ++it) {
-        const int stage = it & 1;
-        if (tile + 1 < my_end) {
-            load_tile(stage ^ 1, tile + 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int stage = it % NSTAGE;
+        if (tile + NSTAGE - 1 < my_end) load_tile((it + NSTAGE - 1) % NSTAGE, tile + NSTAGE - 1);
+        cp_async_commit();
+        cp_async_wait<NSTAGE - 1>();
         __syncthreads();
 
         const int key0 = tile * TILE + part * KEYS_W;          // first key of this warp's part
@@ -318,6 +327,7 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     }
 
     // ---- several warps hold parts of the same rows: merge them through shared memory
+    static_assert(2 * NSTAGE * TILE * STRIDE * sizeof(bf16) >= (4 * 16 * HD + 4 * 16 * 2) * sizeof(float), "merge buffer");
     float* Oc = reinterpret_cast<float*>(Ks);                       // [4 warps][16][HD]
     float* MLc = Oc + 4 * 16 * HD;                                  // [4 warps][16][2]
 #pragma unroll
@@ -368,10 +378,295 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     }
 }
 
+
+// ------------------------------------------------------------------ decode: 16 rows, warp-private pipelines
+// One decoded token per sequence gives a block at most 16 rows (the query heads of one kv head).
+// With so few rows the work per key is small and what counts is how few instructions a key costs
+// and how many bytes are in flight.  Each warp therefore runs on its own: it copies whole
+// sub-tiles of DKT keys (keys and values) into its own two shared-memory stages, computes all 16
+// rows against them, and never meets the other warps until the end, where the four partial
+// results are merged.  Warp w takes sub-tiles w, w + 4, w + 8, ... of the block's key range.
+constexpr int DKT = (HD <= 64) ? 64 : (HD <= 128 ? 32 : 16);     // keys per sub-tile
+constexpr int D_STAGE = DKT * STRIDE;                            // elements per stage and operand
+constexpr int D_NT_S = DKT / 8, D_KS_PV = DKT / 16;
+constexpr int D_NSTAGE = 3;                                      // stages per warp: two sub-tiles in flight while one is used
+
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(MmaArgs a, PagedKV c) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][STRIDE]
+    bf16* KVs = Qs + 16 * STRIDE;                                 // [4 warps][D_NSTAGE][K | V][DKT][STRIDE]
+    __shared__ int tile_pages[MAX_TILES_STAGED];
+
+    const int b = blockIdx.z;
+    int y = blockIdx.y;
+    const int split = y % a.n_splits;  y /= a.n_splits;
+    const int chunk = y % a.head_chunks;  y /= a.head_chunks;
+    const int kvh = y;
+    const int tok0 = blockIdx.x * a.tokens_per_block;
+    const int seq_tok0 = a.cu_seqlens[b];
+    const int q_len = a.cu_seqlens[b + 1] - seq_tok0;
+    if (tok0 >= q_len) return;
+    const int start = a.start_pos[b];
+    const int n_tok = min(a.tokens_per_block, q_len - tok0);
+    const int GH = a.heads_per_block;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
+    const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
+    const int tile_begin = lo_block / TILE, tile_end = p_last / TILE + 1;          // in 64-key pages
+    const int per_split = (tile_end - tile_begin + a.n_splits - 1) / a.n_splits;
+    const int my_begin = tile_begin + split * per_split;
+    const int my_end = min(tile_end, my_begin + per_split);
+
+    for (int idx = tid; idx < 16 * CPR; idx += 128) {
+        const int r = idx / CPR, ch = idx % CPR;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t < n_tok && hg < a.group) {
+            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+            v = *reinterpret_cast<const uint4*>(a.q + row * HD + ch * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + r * STRIDE + ch * 8) = v;
+    }
+    for (int t = my_begin + tid; t < my_end && t - my_begin < MAX_TILES_STAGED; t += 128)
+        tile_pages[t - my_begin] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
+    __syncthreads();
+
+    int row_hi[2], row_lo[2];
+    bool row_ok[2];
+    int all_hi = 0x7fffffff, all_lo = 0;          // keys in [all_lo, all_hi] are visible to every existing row
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int r = (lane >> 2) + 8 * e;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        row_ok[e] = (t < n_tok) && (hg < a.group);
+        row_hi[e] = row_ok[e] ? start + tok0 + t : -1;
+        row_lo[e] = (a.window > 0) ? max(0, row_hi[e] - a.window + 1) : 0;
+    }
+    all_hi = start + tok0;                                                           // the first token's position
+    all_lo = (a.window > 0) ? max(0, p_last - a.window + 1) : 0;                     // the last token's window start
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[NT_O][4];
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
+    constexpr int SUB = TILE / DKT;                     // sub-tiles per page
+    const int st_begin = my_begin * SUB, st_end = my_end * SUB;
+    const bf16* kp = (const bf16*)c.k_pool;
+    const bf16* vp = (const bf16*)c.v_pool;
+    bf16* my_stages = KVs + warp * D_NSTAGE * 2 * D_STAGE;
+    auto load_sub = [&](int stage, int st) {
+        const int tile = st / SUB;
+        const int page = (tile - my_begin < MAX_TILES_STAGED) ? tile_pages[tile - my_begin]
+                                                              : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
+        const long long base = c.entry_offset + (((long long)max(page, 0) * c.kv_heads + kvh) * TILE + (st % SUB) * DKT) * HD;
+        bf16* kd = my_stages + stage * 2 * D_STAGE;
+        bf16* vd = kd + D_STAGE;
+#pragma unroll 4
+        for (int idx = lane; idx < DKT * CPR; idx += 32) {
+            const int j = idx / CPR, ch = idx % CPR;
+            const int kpos = st * DKT + j;
+            const bool valid = page >= 0 && kpos >= lo_block && kpos <= p_last;
+            const long long off = valid ? base + (long long)j * HD + ch * 8 : 0;
+            cp_async_16(kd + j * STRIDE + ch * 8, kp + off, valid);
+            cp_async_16(vd + j * STRIDE + ch * 8, vp + off, valid);
+        }
+    };
+
+    unsigned qf[Q_IN_REGS ? KS_QK : 1][4];
+    if (Q_IN_REGS) {
+#pragma unroll
+        for (int kk = 0; kk < KS_QK; ++kk)
+            ldmatrix_x4(qf[Q_IN_REGS ? kk : 0], Qs + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
+    }
+
+    int st = st_begin + warp;
+#pragma unroll
+    for (int p = 0; p < D_NSTAGE - 1; ++p) {
+        if (st + 4 * p < st_end) load_sub(p, st + 4 * p);
+        cp_async_commit();
+    }
+    for (int it = 0; st < st_end; st += 4, ++it) {
+        const int stage = it % D_NSTAGE;
+        if (st + 4 * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + 4 * (D_NSTAGE - 1));
+        cp_async_commit();
+        cp_async_wait<D_NSTAGE - 1>();
+        __syncwarp();
+
+        const int key0 = st * DKT;
+        if (key0 <= p_last && key0 + DKT - 1 >= lo_block) {
+            const bf16* kt = my_stages + stage * 2 * D_STAGE;
+            const bf16* vt = kt + D_STAGE;
+            float sc[D_NT_S][4];
+#pragma unroll
+            for (int j = 0; j < D_NT_S; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < KS_QK; ++kk) {
+                unsigned af[4];
+                if (Q_IN_REGS) {
+                    af[0] = qf[Q_IN_REGS ? kk : 0][0]; af[1] = qf[Q_IN_REGS ? kk : 0][1];
+                    af[2] = qf[Q_IN_REGS ? kk : 0][2]; af[3] = qf[Q_IN_REGS ? kk : 0][3];
+                } else {
+                    ldmatrix_x4(af, Qs + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
+                }
+#pragma unroll
+                for (int jp = 0; jp < D_NT_S / 2; ++jp) {
+                    unsigned bfr[4];
+                    ldmatrix_x4(bfr, kt + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+                    mma_bf16(sc[2 * jp], af, bfr[0], bfr[1]);
+                    mma_bf16(sc[2 * jp + 1], af, bfr[2], bfr[3]);
+                }
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+            const bool all_visible = key0 >= all_lo && key0 + DKT - 1 <= all_hi;       // the same for the whole warp
+            if (all_visible) {
+#pragma unroll
+                for (int j = 0; j < D_NT_S; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float v = row_ok[e >> 1] ? sc[j][e] * a.scale_log2 : -INFINITY;
+                        sc[j][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < D_NT_S; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int kpos = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
+                        const int rr = e >> 1;
+                        const bool in_range = kpos >= row_lo[rr] && kpos <= row_hi[rr];
+                        const float v = in_range ? sc[j][e] * a.scale_log2 : -INFINITY;
+                        sc[j][e] = v;
+                        mx[rr] = fmaxf(mx[rr], v);
+                    }
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+                const float m_new = fmaxf(m[rr], mx[rr]);
+                const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+                corr[rr] = exp2f(m[rr] - m_use);
+                m[rr] = m_new;
+                mx[rr] = m_use;
+            }
+            float ls[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < D_NT_S; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = exp2f(sc[j][e] - mx[e >> 1]);
+                    sc[j][e] = p;
+                    ls[e >> 1] += p;
+                }
+            }
+            l[0] = l[0] * corr[0] + ls[0];
+            l[1] = l[1] * corr[1] + ls[1];
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+#pragma unroll
+            for (int kk = 0; kk < D_KS_PV; ++kk) {
+                unsigned pf[4];
+                pf[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+                pf[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+                pf[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                pf[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+                for (int jp = 0; jp < NT_O / 2; ++jp) {
+                    unsigned bfr[4];
+                    ldmatrix_x4_trans(bfr, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + jp * 16 + (lane >> 4) * 8);
+                    mma_bf16(o[2 * jp], pf, bfr[0], bfr[1]);
+                    mma_bf16(o[2 * jp + 1], pf, bfr[2], bfr[3]);
+                }
+            }
+        }
+        __syncwarp();                      // the stage is read out before the next copy into it is issued
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+    }
+
+    // ---- merge the four warps' partial results
+    __syncthreads();
+    float* Oc = reinterpret_cast<float*>(KVs);                      // [4 warps][16][HD]
+    float* MLc = Oc + 4 * 16 * HD;                                  // [4 warps][16][2]
+    static_assert(4 * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (4 * 16 * HD + 4 * 16 * 2) * sizeof(float), "merge buffer");
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int r16 = (lane >> 2) + 8 * rr;
+        float* dst = Oc + (warp * 16 + r16) * HD + 2 * (lane & 3);
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) {
+            dst[8 * j] = o[j][2 * rr];
+            dst[8 * j + 1] = o[j][2 * rr + 1];
+        }
+        if ((lane & 3) == 0) {
+            MLc[(warp * 16 + r16) * 2] = m[rr];
+            MLc[(warp * 16 + r16) * 2 + 1] = l[rr];
+        }
+    }
+    __syncthreads();
+    constexpr float LN2 = 0.6931471805599453f;
+    for (int idx = tid; idx < 16 * HD; idx += 128) {
+        const int r = idx / HD, d = idx % HD;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        if (!(t < n_tok && hg < a.group)) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, MLc[(w * 16 + r) * 2]);
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = MLc[(w * 16 + r) * 2];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - M);
+                L += MLc[(w * 16 + r) * 2 + 1] * f;
+                acc += Oc[(w * 16 + r) * HD + d] * f;
+            }
+        }
+        const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+        if (a.n_splits == 1) {
+            a.out[row * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const long long pr = row * a.n_splits + split;
+            a.part_o[pr * HD + d] = acc;
+            if (d == 0) {
+                a.part_ml[pr * 2] = M * LN2;
+                a.part_ml[pr * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_t s) {
+    const size_t smem = (size_t)(16 * STRIDE + 4 * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attention_decode_kernel<<<grid, 128, smem, s>>>(a, c);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
 template <int RT>
 static int launch_mma(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_t s) {
     constexpr int ROWS = 16 * RT;
-    const size_t smem = (size_t)(ROWS + 4 * TILE) * STRIDE * sizeof(bf16);
+    const size_t smem = (size_t)(ROWS + 2 * NSTAGE * TILE) * STRIDE * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -390,11 +685,12 @@ using namespace mlc;
 extern "C" int mlc_attention_mma_head_dim() { return HD; }
 
 // q, out: bfloat16 [n_tokens][q_heads][HD]; the cache pools hold bfloat16 in pages of 64 tokens.
-// row_tiles: 1, 2 or 4 (16, 32 or 64 rows per block).  n_splits > 1 writes partial results to
+// row_tiles: 1, 2 or 4 (16, 32 or 64 rows per block); with row_tiles 1, warp_private != 0 picks the
+// kernel whose warps each stream their own sub-tiles (the decode form).  n_splits > 1 writes partial results to
 // part_ml / part_o (sizes as for mlc_attention_simt) and leaves `out` to the combine kernel.
 extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
                                  int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
-                                 int window, int row_tiles, int n_splits, float* part_ml, float* part_o,
+                                 int window, int row_tiles, int warp_private, int n_splits, float* part_ml, float* part_o,
                                  void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
                                  int pages_per_seq, int page_size, void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
@@ -425,5 +721,6 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     cudaStream_t s = (cudaStream_t)stream;
     if (row_tiles == 4) return launch_mma<4>(a, c, grid, s);
     if (row_tiles == 2) return launch_mma<2>(a, c, grid, s);
+    if (warp_private) return launch_decode(a, c, grid, s);
     return launch_mma<1>(a, c, grid, s);
 }

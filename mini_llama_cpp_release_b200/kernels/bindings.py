@@ -324,7 +324,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     if lib is None:
         lib = _build.attention_library(head_dim)
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
-        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P, P, LL, I, I, P]
+        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, P]
         lib.mlc_attention_mma.restype = c_int
         lib.mlc_attention_mma_head_dim.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
@@ -347,16 +347,17 @@ def attention_mma_plan(max_q_len: int, n_seqs: int, max_kv_len: int, q_heads: in
     head_chunks = (group + heads_per_block - 1) // heads_per_block
     blocks = ((max_q_len + tokens_per_block - 1) // tokens_per_block) * kv_heads * head_chunks * n_seqs
     n_splits = 1
-    if blocks < 2 * n_sms:
-        by_fill = (2 * n_sms + blocks - 1) // blocks
-        by_len = max(1, max_kv_len // 128)              # at least two 64-key tiles per split
-        n_splits = max(1, min(by_fill, by_len, 64))
+    if blocks < n_sms:
+        by_fill = max(1, n_sms // blocks)                # one wave of blocks: a second wave would cost what the split saves
+        by_len = max(1, max_kv_len // 256)              # at least four 64-key tiles per split
+        n_splits = max(1, min(by_fill, by_len, 32))
     return row_tiles, n_splits
 
 
 def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
                   max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int, row_tiles: int, n_splits: int,
-                  part_ml: Optional[torch.Tensor] = None, part_o: Optional[torch.Tensor] = None) -> None:
+                  part_ml: Optional[torch.Tensor] = None, part_o: Optional[torch.Tensor] = None,
+                  warp_private: bool = True) -> None:
     """Tensor-core attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry."""
     require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o)
     if q.dtype != torch.bfloat16 or kv.k_pool.dtype != torch.bfloat16:
@@ -369,7 +370,7 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
     lib = attention_library(hd)
     _check(lib.mlc_attention_mma(q.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), start_pos.data_ptr(), n_seqs,
                                  n_tokens, max_q_len, q_heads, kv.kv_heads, hd, float(scale), int(window), row_tiles,
-                                 n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(),
+                                 1 if warp_private else 0, n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(),
                                  kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq, kv.page_size, _stream()),
            "tensor-core attention")
     if n_splits > 1:

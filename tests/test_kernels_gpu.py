@@ -86,7 +86,8 @@ def make_paged(ks, vs, dtype, page_size=64, entries=2, entry=1, spare=3, seed=0)
     return KVView(k_pool.to(DEV), v_pool.to(DEV), entry * n_pages * KV * page_size * hd, table.to(DEV), page_size, KV, hd)
 
 
-def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0, scale_up=None, impl="simt", row_tiles=4):
+def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0, scale_up=None, impl="simt", row_tiles=4,
+                   warp_private=True):
     """Sequences of `lens` cached tokens of which the last `q_lens` are this step's; compare
     with the plain attention of each whole sequence."""
     g = torch.Generator().manual_seed(seed)
@@ -107,7 +108,7 @@ def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0,
     part_o = torch.empty(N * H * n_splits * hd, device=DEV) if n_splits > 1 else None
     if impl == "mma":
         kernels.attention_mma(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
-                              1.0 / math.sqrt(hd), window, row_tiles, n_splits, part_ml, part_o)
+                              1.0 / math.sqrt(hd), window, row_tiles, n_splits, part_ml, part_o, warp_private)
     else:
         kernels.attention_simt(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
                                1.0 / math.sqrt(hd), window, n_splits, part_ml, part_o)
@@ -327,10 +328,10 @@ def test_argmax_lowest_index_wins():
     assert out.tolist() == [77, 151935, 0, int(logits[3].argmax())]
 
 
-@pytest.mark.parametrize("row_tiles", [1, 2, 4])
+@pytest.mark.parametrize("row_tiles", [0, 1, 2, 4])
 @pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (14, 2, 64), (8, 1, 32), (6, 6, 80), (40, 1, 48), (3, 1, 256), (12, 2, 128), (70, 1, 16)])
 def test_tensor_core_attention_prompts_chunks_and_single_tokens(H, KV, hd, row_tiles):
-    kw = dict(impl="mma", row_tiles=row_tiles)
+    kw = dict(impl="mma", row_tiles=max(1, row_tiles), warp_private=(row_tiles != 0))      # 0: the block-cooperative 16-row form
     got, want, _ = attention_case([7, 1, 130, 64], [7, 1, 130, 64], H, KV, hd, "bfloat16", **kw)
     close(got, want, 1e-2)
     got, want, _ = attention_case([200, 65, 3, 64, 128, 129], [1, 1, 1, 1, 1, 1], H, KV, hd, "bfloat16", seed=1, **kw)
@@ -339,17 +340,17 @@ def test_tensor_core_attention_prompts_chunks_and_single_tokens(H, KV, hd, row_t
     close(got, want, 1e-2)
 
 
-@pytest.mark.parametrize("row_tiles", [1, 4])
+@pytest.mark.parametrize("row_tiles", [0, 1, 4])
 @pytest.mark.parametrize("n_splits", [2, 5, 64])
 def test_tensor_core_attention_key_splits(n_splits, row_tiles):
-    kw = dict(impl="mma", row_tiles=row_tiles, n_splits=n_splits)
+    kw = dict(impl="mma", row_tiles=max(1, row_tiles), n_splits=n_splits, warp_private=(row_tiles != 0))
     got, want, _ = attention_case([700, 33, 1], [1, 1, 1], 14, 2, 64, "bfloat16", **kw)
     close(got, want, 1e-2)
     got, want, _ = attention_case([300, 40], [40, 3], 4, 2, 16, "bfloat16", seed=3, **kw)
     close(got, want, 1e-2)
 
 
-@pytest.mark.parametrize("row_tiles", [1, 4])
+@pytest.mark.parametrize("row_tiles", [0, 1, 4])
 @pytest.mark.parametrize("window", [1, 24, 64, 65, 130])
 def test_tensor_core_attention_window_edge_and_far_key(window, row_tiles):
     def prefer_outside(qs, ks, vs):
@@ -360,7 +361,7 @@ def test_tensor_core_attention_window_edge_and_far_key(window, row_tiles):
                 k[n - 1 - window, :, 0] = 30.0
                 q[n - 1, :, 0] = 30.0
                 v[n - 1 - window] = 100.0
-    kw = dict(impl="mma", row_tiles=row_tiles)
+    kw = dict(impl="mma", row_tiles=max(1, row_tiles), warp_private=(row_tiles != 0))
     got, want, _ = attention_case([200, 66, 25], [1, 1, 1], 6, 3, 32, "bfloat16", window=window, scale_up=prefer_outside, **kw)
     assert float(want.abs().max()) < 50
     close(got, want, 1e-2)
