@@ -96,6 +96,8 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     bf16* Ks = Qs + ROWS * STRIDE;                                // [NSTAGE][TILE][STRIDE]
     bf16* Vs = Ks + NSTAGE * TILE * STRIDE;                       // [NSTAGE][TILE][STRIDE]
 
+    grid_launch_dependents();
+    grid_dependency_wait();                    // queries and the step's keys were written by the kernel before
     const int b = blockIdx.z;
     int y = blockIdx.y;
     const int split = y % a.n_splits;  y /= a.n_splits;
@@ -398,6 +400,8 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     bf16* KVs = Qs + 16 * STRIDE;                                 // [4 warps][D_NSTAGE][K | V][DKT][STRIDE]
     __shared__ int tile_pages[MAX_TILES_STAGED];
 
+    grid_launch_dependents();
+    grid_dependency_wait();                    // queries and the step's keys were written by the kernel before
     const int b = blockIdx.z;
     int y = blockIdx.y;
     const int split = y % a.n_splits;  y /= a.n_splits;
@@ -658,9 +662,8 @@ static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStre
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attention_decode_kernel<<<grid, 128, smem, s>>>(a, c);
-    MLC_LAUNCH_CHECK();
-    return 0;
+    cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(128), smem, s, a, c);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 template <int RT>
@@ -673,9 +676,8 @@ static int launch_mma(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attention_mma_kernel<RT><<<grid, 128, smem, s>>>(a, c);
-    MLC_LAUNCH_CHECK();
-    return 0;
+    cudaError_t e = launch_pdl(attention_mma_kernel<RT>, grid, dim3(128), smem, s, a, c);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 }  // namespace mlc

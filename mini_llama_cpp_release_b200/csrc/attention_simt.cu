@@ -302,13 +302,13 @@ extern "C" int mlc_attention_combine(const float* part_ml, const float* part_o, 
     if (n_splits < 1 || hd <= 0) return MLC_ERR_BAD_SIZE;
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);
     cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
     if (dtype == MLC_DTYPE_F32)
-        attention_combine_kernel<float><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, (float*)out);
+        e = launch_pdl(attention_combine_kernel<float>, dim3(blocks), dim3(128), 0, s, part_ml, part_o, n_rows, n_splits, hd, (float*)out);
     else if (dtype == MLC_DTYPE_BF16)
-        attention_combine_kernel<bf16><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, (bf16*)out);
+        e = launch_pdl(attention_combine_kernel<bf16>, dim3(blocks), dim3(128), 0, s, part_ml, part_o, n_rows, n_splits, hd, (bf16*)out);
     else
         return MLC_ERR_BAD_DTYPE;
-    MLC_LAUNCH_CHECK();
-    return 0;
+    return e == cudaSuccess ? 0 : (int)e;
 }
 #endif  // MLC_KERNELS_ONLY

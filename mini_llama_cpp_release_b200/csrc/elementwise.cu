@@ -15,6 +15,8 @@ namespace mlc {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, int d,
                              float* __restrict__ out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int n = blockIdx.x;
     const T* row = table + (long long)ids[n] * d;
     float* o = out + (long long)n * d;
@@ -140,6 +142,8 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gu, int inter, long long
 __global__ void gather_rows_kernel(const float* __restrict__ x, const float* __restrict__ delta, int n_slices,
                                    long long slice_stride, const int* __restrict__ rows, int d,
                                    float* __restrict__ out_x, float* __restrict__ out_delta) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const long long src = (long long)rows[blockIdx.x] * d, dst = (long long)blockIdx.x * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         out_x[dst + i] = x[src + i];
@@ -181,14 +185,14 @@ extern "C" int mlc_embed(const void* table, int table_dtype, const int* ids, int
     if (n <= 0) return 0;
     if (d <= 0) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
     if (table_dtype == MLC_DTYPE_F32)
-        embed_kernel<float><<<n, row_threads(d), 0, s>>>((const float*)table, ids, d, out);
+        e = launch_pdl(embed_kernel<float>, dim3(n), dim3(norm_threads(d, n)), 0, s, (const float*)table, ids, d, out);
     else if (table_dtype == MLC_DTYPE_BF16)
-        embed_kernel<bf16><<<n, row_threads(d), 0, s>>>((const bf16*)table, ids, d, out);
+        e = launch_pdl(embed_kernel<bf16>, dim3(n), dim3(norm_threads(d, n)), 0, s, (const bf16*)table, ids, d, out);
     else
         return MLC_ERR_BAD_DTYPE;
-    MLC_LAUNCH_CHECK();
-    return 0;
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 extern "C" int mlc_add_rmsnorm(float* x, const float* delta, int n_slices, const float* gain, float eps, int n, int d,
@@ -266,10 +270,9 @@ extern "C" int mlc_silu_mul(const void* gate_up, int in_dtype, int n, int inter,
 extern "C" int mlc_gather_rows(const float* x, const float* delta, int n_slices, long long slice_stride, const int* rows,
                                int n_rows, int d, float* out_x, float* out_delta, void* stream) {
     if (n_rows <= 0) return 0;
-    gather_rows_kernel<<<n_rows, row_threads(d), 0, (cudaStream_t)stream>>>(x, delta, n_slices, slice_stride, rows, d,
-                                                                            out_x, out_delta);
-    MLC_LAUNCH_CHECK();
-    return 0;
+    cudaError_t e = launch_pdl(gather_rows_kernel, dim3(n_rows), dim3(norm_threads(d, n_rows)), 0, (cudaStream_t)stream, x, delta,
+                               n_slices, slice_stride, rows, d, out_x, out_delta);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 extern "C" int mlc_convert(const void* in, int in_dtype, long long total, void* out, int out_dtype, void* stream) {

@@ -184,10 +184,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     tcgen05_fence_after();
     const unsigned tmem_acc = *tmem_slot_ptr;
 
+    grid_launch_dependents();                  // the next kernel may start its own set-up now
     if (warp == 0) {
-        // ---------------- TMA producer
+        // ---------------- TMA producer.  The weights do not depend on the kernels before this one: the first
+        // round of weight tiles is requested before the wait for those kernels, the activations after it.
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            const int early = min(n_kb, S::STAGES);
+            for (int i = 0; i < early; ++i) {
+                mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
+                tma_load_2d(a_base + i * G_A_BYTES, &map_w, (kb_begin + i) * G_BK, m0, full_bar(i));
+            }
+            grid_dependency_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(b_base + i * S::B_BYTES, &map_x, (kb_begin + i) * G_BK, n0, full_bar(i));
+            for (int i = early; i < n_kb; ++i) {
                 const int s = i % S::STAGES;
                 const unsigned phase = (i / S::STAGES) & 1;
                 if (!mbar_wait(empty_bar(s), phase ^ 1u, g.status, 1)) break;
@@ -222,6 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else {
         // ---------------- epilogue: warp q reads tensor-memory lanes 32q .. 32q+31
         const int q = warp & 3;
+        grid_dependency_wait();                // positions, page lists and the output buffers may come from earlier kernels
         if (EPI == EPI_QKV) {
             for (int t = threadIdx.x - 64; t < BN; t += 128) {
                 int p = 0;
@@ -364,9 +375,8 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmA
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, EPI><<<grid, G_THREADS, S::SMEM_BYTES, s>>>(mw, mx, g);
-    MLC_LAUNCH_CHECK();
-    return 0;
+    cudaError_t e = launch_pdl(gemm_tcgen05_kernel<BN, EPI>, grid, dim3(G_THREADS), (size_t)S::SMEM_BYTES, s, mw, mx, g);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 template <int EPI>

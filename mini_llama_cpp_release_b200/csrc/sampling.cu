@@ -382,6 +382,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ chosen, int n, int
                                       int* __restrict__ positions, int* __restrict__ start_pos,
                                       int* __restrict__ sample_pos, int* __restrict__ history,
                                       int* __restrict__ counter, int max_steps) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int step = *counter;
     if (i < n) {
@@ -399,8 +401,7 @@ extern "C" int mlc_decode_advance(const int* chosen, int n, int* tokens, int* po
                                   int* sample_pos, int* history, int* counter, int max_steps, void* stream) {
     if (n <= 0) return 0;
     if (n > 1024) return MLC_ERR_BAD_SIZE;
-    decode_advance_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(chosen, n, tokens, positions, start_pos,
-                                                                    sample_pos, history, counter, max_steps);
-    MLC_LAUNCH_CHECK();
-    return 0;
+    cudaError_t e = mlc::launch_pdl(decode_advance_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, chosen, n, tokens,
+                                    positions, start_pos, sample_pos, history, counter, max_steps);
+    return e == cudaSuccess ? 0 : (int)e;
 }
