@@ -56,6 +56,43 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     }
 }
 
+// The same with 16-byte accesses, for rows whose length is a multiple of 4 (all pointers 16-byte aligned).
+template <typename T>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_slices,
+                                        long long slice_stride, const float* __restrict__ gain, float eps, int d,
+                                        T* __restrict__ out) {
+    __shared__ float scratch[32];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const long long base = (long long)blockIdx.x * d;
+    const int d4 = d >> 2;
+    float4* x4 = reinterpret_cast<float4*>(x + base);
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        float4 v = x4[i];
+        if (delta != nullptr) {
+#pragma unroll 4
+            for (int s = 0; s < n_slices; ++s) {
+                const float4 t = __ldg(reinterpret_cast<const float4*>(delta + s * slice_stride + base) + i);
+                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+            x4[i] = v;
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        const float4 v = x4[i], g = __ldg(g4 + i);
+        T* o = out + base + 4 * i;
+        o[0] = from_float<T>(v.x * scale * g.x);
+        o[1] = from_float<T>(v.y * scale * g.y);
+        o[2] = from_float<T>(v.z * scale * g.z);
+        o[3] = from_float<T>(v.w * scale * g.w);
+    }
+}
+
 // ------------------------------------------------------------------ rotation table
 // table[p][i] = (cos(p·f_i), sin(p·f_i)), the angle formed in float32 from an integer
 // position and a float32 frequency, as src/ops.cpp:132-134 does for each token.
@@ -124,18 +161,63 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, const float* __re
 }
 
 // ------------------------------------------------------------------ SiLU(gate)·up
-// Input row [gate (I) | up (I)], output [I].
+// Input row [gate (I) | up (I)], or with `interleaved` [g0, u0, g1, u1, ...]; output [I].
 template <typename TIn, typename TOut>
-__global__ void silu_mul_kernel(const TIn* __restrict__ gu, int inter, long long total,
+__global__ void silu_mul_kernel(const TIn* __restrict__ gu, int inter, long long total, int interleaved,
                                 TOut* __restrict__ out) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const long long n = idx / inter;
     const int i = (int)(idx % inter);
-    const float g = to_float(gu[n * 2 * inter + i]);
-    const float u = to_float(gu[n * 2 * inter + inter + i]);
+    const TIn* row = gu + n * 2 * inter;
+    const float g = to_float(interleaved ? row[2 * i] : row[i]);
+    const float u = to_float(interleaved ? row[2 * i + 1] : row[inter + i]);
     const float sig = 1.0f / (1.0f + expf(-g));
     out[idx] = from_float<TOut>(g * sig * u);
+}
+
+// Eight outputs per thread with 16-byte loads and stores (bfloat16 in and out, I a multiple of 8).
+__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, int inter, long long total_vec, int interleaved,
+                                     bf16* __restrict__ out) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total_vec) return;
+    const int per_row = inter >> 3;
+    const long long n = idx / per_row;
+    const int i = (int)(idx % per_row) << 3;
+    const bf16* row = gu + n * 2 * inter;
+    float g[8], u[8];
+    if (interleaved) {
+        const uint4 a = *reinterpret_cast<const uint4*>(row + 2 * i);
+        const uint4 b = *reinterpret_cast<const uint4*>(row + 2 * i + 8);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 fa = __bfloat1622float2(pa[k]), fb = __bfloat1622float2(pb[k]);
+            g[k] = fa.x; u[k] = fa.y;
+            g[4 + k] = fb.x; u[4 + k] = fb.y;
+        }
+    } else {
+        const uint4 a = *reinterpret_cast<const uint4*>(row + i);
+        const uint4 b = *reinterpret_cast<const uint4*>(row + inter + i);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 fa = __bfloat1622float2(pa[k]), fb = __bfloat1622float2(pb[k]);
+            g[2 * k] = fa.x; g[2 * k + 1] = fa.y;
+            u[2 * k] = fb.x; u[2 * k + 1] = fb.y;
+        }
+    }
+    uint4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float y0 = g[2 * k] * (1.0f / (1.0f + expf(-g[2 * k]))) * u[2 * k];
+        const float y1 = g[2 * k + 1] * (1.0f / (1.0f + expf(-g[2 * k + 1]))) * u[2 * k + 1];
+        po[k] = __floats2bfloat162_rn(y0, y1);
+    }
+    *reinterpret_cast<uint4*>(out + n * inter + i) = o;
 }
 
 // ------------------------------------------------------------------ row gather
@@ -202,7 +284,13 @@ extern "C" int mlc_add_rmsnorm(float* x, const float* delta, int n_slices, const
     cudaStream_t s = (cudaStream_t)stream;
     const long long stride = (long long)n * d;
     cudaError_t e;
-    if (out_dtype == MLC_DTYPE_F32)
+    const bool vec = (d & 3) == 0 && n > 64 &&
+                     ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)gain) | ((uintptr_t)out)) & 15) == 0;
+    if (vec && out_dtype == MLC_DTYPE_F32)
+        e = launch_pdl(add_rmsnorm_vec4_kernel<float>, dim3(n), dim3(row_threads(d >> 2)), 0, s, x, delta, n_slices, stride, gain, eps, d, (float*)out);
+    else if (vec && out_dtype == MLC_DTYPE_BF16)
+        e = launch_pdl(add_rmsnorm_vec4_kernel<bf16>, dim3(n), dim3(row_threads(d >> 2)), 0, s, x, delta, n_slices, stride, gain, eps, d, (bf16*)out);
+    else if (out_dtype == MLC_DTYPE_F32)
         e = launch_pdl(add_rmsnorm_kernel<float>, dim3(n), dim3(norm_threads(d, n)), 0, s, x, delta, n_slices, stride, gain, eps, d, (float*)out);
     else if (out_dtype == MLC_DTYPE_BF16)
         e = launch_pdl(add_rmsnorm_kernel<bf16>, dim3(n), dim3(norm_threads(d, n)), 0, s, x, delta, n_slices, stride, gain, eps, d, (bf16*)out);
@@ -246,21 +334,29 @@ extern "C" int mlc_qkv_post(const float* qkv, const float* bias, const int* posi
     return 0;
 }
 
-extern "C" int mlc_silu_mul(const void* gate_up, int in_dtype, int n, int inter, void* out, int out_dtype,
-                            void* stream) {
+extern "C" int mlc_silu_mul(const void* gate_up, int in_dtype, int n, int inter, int interleaved, void* out,
+                            int out_dtype, void* stream) {
     if (n <= 0) return 0;
     if (inter <= 0) return MLC_ERR_BAD_SIZE;
     const long long total = (long long)n * inter;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
+    if (in_dtype == MLC_DTYPE_BF16 && out_dtype == MLC_DTYPE_BF16 && (inter & 7) == 0 &&
+        ((((uintptr_t)gate_up) | ((uintptr_t)out)) & 15) == 0) {
+        const long long total_vec = total >> 3;
+        silu_mul_vec8_kernel<<<(unsigned)((total_vec + 255) / 256), 256, 0, s>>>((const bf16*)gate_up, inter, total_vec,
+                                                                                 interleaved, (bf16*)out);
+        MLC_LAUNCH_CHECK();
+        return 0;
+    }
     if (in_dtype == MLC_DTYPE_F32 && out_dtype == MLC_DTYPE_F32)
-        silu_mul_kernel<float, float><<<blocks, 256, 0, s>>>((const float*)gate_up, inter, total, (float*)out);
+        silu_mul_kernel<float, float><<<blocks, 256, 0, s>>>((const float*)gate_up, inter, total, interleaved, (float*)out);
     else if (in_dtype == MLC_DTYPE_F32 && out_dtype == MLC_DTYPE_BF16)
-        silu_mul_kernel<float, bf16><<<blocks, 256, 0, s>>>((const float*)gate_up, inter, total, (bf16*)out);
+        silu_mul_kernel<float, bf16><<<blocks, 256, 0, s>>>((const float*)gate_up, inter, total, interleaved, (bf16*)out);
     else if (in_dtype == MLC_DTYPE_BF16 && out_dtype == MLC_DTYPE_BF16)
-        silu_mul_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((const bf16*)gate_up, inter, total, (bf16*)out);
+        silu_mul_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((const bf16*)gate_up, inter, total, interleaved, (bf16*)out);
     else if (in_dtype == MLC_DTYPE_BF16 && out_dtype == MLC_DTYPE_F32)
-        silu_mul_kernel<bf16, float><<<blocks, 256, 0, s>>>((const bf16*)gate_up, inter, total, (float*)out);
+        silu_mul_kernel<bf16, float><<<blocks, 256, 0, s>>>((const bf16*)gate_up, inter, total, interleaved, (float*)out);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();

@@ -88,7 +88,7 @@ def core() -> ctypes.CDLL:
             "mlc_add_rmsnorm": [P, P, I, P, F, I, I, P, I, P],
             "mlc_rope_table": [P, I, I, P, P],
             "mlc_qkv_post": [P, P, P, P, P, I, I, I, I, I, P, I, P, P, P, LL, I, I, I, P],
-            "mlc_silu_mul": [P, I, I, I, P, I, P],
+            "mlc_silu_mul": [P, I, I, I, I, P, I, P],
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
             "mlc_convert": [P, I, LL, P, I, P],
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
@@ -222,13 +222,13 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor,
         count_launches(1)
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """rows [gate | up] → gate * sigmoid(gate) * up."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """rows [gate | up] (or, interleaved, [g0, u0, g1, u1, ...]) → gate * sigmoid(gate) * up."""
     require_cuda(gate_up, out)
     n, two_i = gate_up.shape
     assert two_i % 2 == 0 and out.shape == (n, two_i // 2)
-    _check(core().mlc_silu_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n, two_i // 2, out.data_ptr(),
-                               dtype_code(out.dtype), _stream()), "silu_mul")
+    _check(core().mlc_silu_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n, two_i // 2, 1 if interleaved else 0,
+                               out.data_ptr(), dtype_code(out.dtype), _stream()), "silu_mul")
 
 
 def gather_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, out_x: torch.Tensor,

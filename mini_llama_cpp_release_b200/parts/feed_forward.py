@@ -11,6 +11,9 @@ from .base import Part, TensorSpec
 from .linear import Linear
 
 
+FUSED_MAX_ROWS = 64
+
+
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
     graph_safe = True
@@ -42,6 +45,9 @@ class SwiGLU(Part):
         else:
             w = torch.cat([gate, up], dim=0)
         self.gate_up = Linear(w, runtime)
+        # Above this many rows the plain product followed by the activation kernel is still the faster
+        # pair: the fused epilogue stores two bytes per lane and does not overlap with the next tile.
+        self.fused_max_rows = FUSED_MAX_ROWS
         self.down = Linear(get(n + "down_proj.weight"), runtime)
 
     def weight_bytes(self) -> int:
@@ -50,8 +56,8 @@ class SwiGLU(Part):
     def forward(self, h: torch.Tensor, step=None) -> torch.Tensor:
         rt = self.runtime
         a = rt.empty(h.shape[0], self.inter)
-        if self.fused:
+        if self.fused and h.shape[0] <= self.fused_max_rows:
             kernels.gemm_tcgen05(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
         else:
-            kernels.silu_mul(self.gate_up(h, rt.dtype), a)
+            kernels.silu_mul(self.gate_up(h, rt.dtype), a, interleaved=self.fused)
         return self.down(a, torch.float32, partial_ok=True)

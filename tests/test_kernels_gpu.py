@@ -208,6 +208,9 @@ def test_silu_mul(dtype):
     kernels.silu_mul(gu.to(DEV), out)
     g, u = gu.float()[:, :344], gu.float()[:, 344:]
     close(out.float(), g * (1 / (1 + torch.exp(-g))) * u, 2e-6 if dtype == "float32" else 5e-3)
+    mixed = torch.stack([gu[:, :344], gu[:, 344:]], dim=2).reshape(7, 688).contiguous()      # g0, u0, g1, u1, ...
+    kernels.silu_mul(mixed.to(DEV), out, interleaved=True)
+    close(out.float(), g * (1 / (1 + torch.exp(-g))) * u, 2e-6 if dtype == "float32" else 5e-3)
 
 
 def test_gather_rows():
