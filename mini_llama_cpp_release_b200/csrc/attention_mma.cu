@@ -387,17 +387,18 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
 // and how many bytes are in flight.  Each warp therefore runs on its own: it copies whole
 // sub-tiles of DKT keys (keys and values) into its own two shared-memory stages, computes all 16
 // rows against them, and never meets the other warps until the end, where the four partial
-// results are merged.  Warp w takes sub-tiles w, w + 4, w + 8, ... of the block's key range.
-constexpr int DKT = (HD <= 64) ? 64 : (HD <= 128 ? 32 : 16);     // keys per sub-tile
+// results are merged.  Warp w of DNW takes sub-tiles w, w + DNW, w + 2 DNW, ... of the block's key range.
+constexpr int DNW = (HD <= 128) ? 8 : 4;                         // warps per block: two per scheduler hide each other's latencies
+constexpr int DKT = (HD <= 64) ? 32 : 16;                        // keys per sub-tile
 constexpr int D_STAGE = DKT * STRIDE;                            // elements per stage and operand
 constexpr int D_NT_S = DKT / 8, D_KS_PV = DKT / 16;
 constexpr int D_NSTAGE = 3;                                      // stages per warp: two sub-tiles in flight while one is used
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(DNW * 32)
 attention_decode_kernel(MmaArgs a, PagedKV c) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][STRIDE]
-    bf16* KVs = Qs + 16 * STRIDE;                                 // [4 warps][D_NSTAGE][K | V][DKT][STRIDE]
+    bf16* KVs = Qs + 16 * STRIDE;                                 // [DNW warps][D_NSTAGE][K | V][DKT][STRIDE]
     __shared__ int tile_pages[MAX_TILES_STAGED];
 
     grid_launch_dependents();
@@ -423,7 +424,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     const int my_begin = tile_begin + split * per_split;
     const int my_end = min(tile_end, my_begin + per_split);
 
-    for (int idx = tid; idx < 16 * CPR; idx += 128) {
+    for (int idx = tid; idx < 16 * CPR; idx += DNW * 32) {
         const int r = idx / CPR, ch = idx % CPR;
         const int t = r / GH, hg = chunk * GH + r % GH;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -433,7 +434,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         }
         *reinterpret_cast<uint4*>(Qs + r * STRIDE + ch * 8) = v;
     }
-    for (int t = my_begin + tid; t < my_end && t - my_begin < MAX_TILES_STAGED; t += 128)
+    for (int t = my_begin + tid; t < my_end && t - my_begin < MAX_TILES_STAGED; t += DNW * 32)
         tile_pages[t - my_begin] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
     __syncthreads();
 
@@ -489,12 +490,12 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     int st = st_begin + warp;
 #pragma unroll
     for (int p = 0; p < D_NSTAGE - 1; ++p) {
-        if (st + 4 * p < st_end) load_sub(p, st + 4 * p);
+        if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
         cp_async_commit();
     }
-    for (int it = 0; st < st_end; st += 4, ++it) {
+    for (int it = 0; st < st_end; st += DNW, ++it) {
         const int stage = it % D_NSTAGE;
-        if (st + 4 * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + 4 * (D_NSTAGE - 1));
+        if (st + DNW * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + DNW * (D_NSTAGE - 1));
         cp_async_commit();
         cp_async_wait<D_NSTAGE - 1>();
         __syncwarp();
@@ -604,9 +605,9 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
 
     // ---- merge the four warps' partial results
     __syncthreads();
-    float* Oc = reinterpret_cast<float*>(KVs);                      // [4 warps][16][HD]
-    float* MLc = Oc + 4 * 16 * HD;                                  // [4 warps][16][2]
-    static_assert(4 * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (4 * 16 * HD + 4 * 16 * 2) * sizeof(float), "merge buffer");
+    float* Oc = reinterpret_cast<float*>(KVs);                      // [DNW warps][16][HD]
+    float* MLc = Oc + DNW * 16 * HD;                                // [DNW warps][16][2]
+    static_assert(DNW * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (DNW * 16 * HD + DNW * 16 * 2) * sizeof(float), "merge buffer");
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         const int r16 = (lane >> 2) + 8 * rr;
@@ -623,16 +624,16 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     }
     __syncthreads();
     constexpr float LN2 = 0.6931471805599453f;
-    for (int idx = tid; idx < 16 * HD; idx += 128) {
+    for (int idx = tid; idx < 16 * HD; idx += DNW * 32) {
         const int r = idx / HD, d = idx % HD;
         const int t = r / GH, hg = chunk * GH + r % GH;
         if (!(t < n_tok && hg < a.group)) continue;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, MLc[(w * 16 + r) * 2]);
+        for (int w = 0; w < DNW; ++w) M = fmaxf(M, MLc[(w * 16 + r) * 2]);
         float L = 0.0f, acc = 0.0f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < DNW; ++w) {
             const float mw = MLc[(w * 16 + r) * 2];
             if (mw != -INFINITY) {
                 const float f = exp2f(mw - M);
@@ -655,14 +656,14 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
 }
 
 static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_t s) {
-    const size_t smem = (size_t)(16 * STRIDE + 4 * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
+    const size_t smem = (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(128), smem, s, a, c);
+    cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(DNW * 32), smem, s, a, c);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
