@@ -20,6 +20,13 @@
 //             by the token's position (src/ops.cpp:125-141), writes q as [token][head][hd] and
 //             k, v into the token's place in the paged cache (src/forward.cpp:553).
 //
+//   ADD       adds y into a float32 [token][row] tensor (the residual stream) with atomic adds,
+//             so that any number of K splits can feed it (src/forward.cpp:772, 779).
+// Prologue NORM (up to 16 tokens): instead of loading bfloat16 activations with TMA the block reads
+// the float32 residual stream itself, computes x·1/sqrt(mean(x²)+eps)·gain per token
+// (src/ops.cpp:19-41) and writes the bfloat16 operand into shared memory in the swizzled layout,
+// which saves the separate norm kernel of a decode step.
+//
 // Every wait on an mbarrier is bounded by a clock; a wait that runs out records a code in
 // `status`, the block skips its stores, frees its tensor memory and returns.
 #include "common.cuh"
@@ -35,7 +42,7 @@ constexpr int G_THREADS = 192;
 constexpr int G_A_BYTES = G_BM * G_BK * 2;                 // 16 KiB per stage
 constexpr unsigned long long G_WAIT_NS = 2000000000ull;     // two seconds
 
-enum { EPI_STORE = 0, EPI_SILU_MUL = 1, EPI_QKV = 2 };
+enum { EPI_STORE = 0, EPI_SILU_MUL = 1, EPI_QKV = 2, EPI_ADD = 3 };
 
 struct GemmArgs {
     void* out;                 // STORE / SILU_MUL: [splits][tokens][n_out or n_out/2]; QKV: q [tokens][q_heads*hd]
@@ -46,6 +53,12 @@ struct GemmArgs {
     int k_blocks_per_split;
     long long split_stride;    // elements between the output slices of two splits
     int* status;
+    // NORM prologue
+    const float* x_f32;        // [tokens][K] float32, or null: activations come through the tensor map
+    const float* gain;         // [K]
+    float eps;
+    int K;
+    int stages;                // shared-memory stages in use (<= GemmShape::STAGES)
     // QKV epilogue
     const float* bias;         // [n_out] in the stored row order, or null
     const int* positions;      // [tokens]
@@ -130,6 +143,71 @@ __host__ __device__ constexpr unsigned umma_idesc(int bn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(G_BM >> 4) << 24);
 }
 
+
+// ------------------------------------------------------------------ NORM prologue helpers
+// Eight stream values times scale times gain, rounded to bfloat16 and packed into 16 bytes.
+__device__ __forceinline__ uint4 scale_pack8(const float4& a, const float4& b, float scale, const float* __restrict__ gain, int ch) {
+    const float4 ga = __ldg(reinterpret_cast<const float4*>(gain) + 2 * ch);
+    const float4 gb = __ldg(reinterpret_cast<const float4*>(gain) + 2 * ch + 1);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * scale * ga.x, a.y * scale * ga.y);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(a.z * scale * ga.z, a.w * scale * ga.w);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x * scale * gb.x, b.y * scale * gb.y);
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(b.z * scale * gb.z, b.w * scale * gb.w);
+    return make_uint4(*reinterpret_cast<unsigned*>(&p0), *reinterpret_cast<unsigned*>(&p1),
+                      *reinterpret_cast<unsigned*>(&p2), *reinterpret_cast<unsigned*>(&p3));
+}
+
+// RMSNorm of rows of up to CPL*256 elements straight into the swizzled shared-memory operand.  Warp `ew`
+// of four takes rows ew, ew+4, ...; two rows at a time, with every load of both rows issued before the
+// first use, so a pair of rows costs one trip to memory.  A lane owns 16-byte chunks lane, lane+32, ...
+template <int CPL>
+__device__ __forceinline__ void norm_rows_to_smem(const float* __restrict__ x, const float* __restrict__ gain, float eps, int K,
+                                                  int k_blocks, int n0, int n_tok, int ew, int lane, int rows, int tile_bytes,
+                                                  unsigned char* b_tiles) {
+    const int chunks = K >> 3, k_chunks = k_blocks * 8;
+    for (int r0 = ew; r0 < rows; r0 += 8) {
+        float4 va[2][CPL], vb[2][CPL];
+        bool live[2];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int r = r0 + 4 * rr;
+            live[rr] = r < rows && n0 + r < n_tok;
+            const float* xr = x + (long long)(n0 + r) * K;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+                const int ch = lane + 32 * j;
+                va[rr][j] = vb[rr][j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (live[rr] && ch < chunks) {
+                    va[rr][j] = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch);
+                    vb[rr][j] = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch + 1);
+                }
+            }
+        }
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int r = r0 + 4 * rr;
+            if (r >= rows) continue;
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+                const float4 a = va[rr][j], b = vb[rr][j];
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+            }
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / (float)K + eps);
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+                const int ch = lane + 32 * j;
+                if (ch >= k_chunks) continue;
+                uint4 packed = make_uint4(0, 0, 0, 0);
+                if (live[rr] && ch < chunks) packed = scale_pack8(va[rr][j], vb[rr][j], scale, gain, ch);
+                const int kb = ch >> 3, c = ch & 7;
+                *reinterpret_cast<uint4*>(b_tiles + kb * tile_bytes + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
+            }
+        }
+    }
+}
+
 template <int BN> struct GemmShape {
     static constexpr int B_BYTES = BN * G_BK * 2;
     static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
@@ -143,22 +221,27 @@ template <typename T> __device__ __forceinline__ void store_out(void* base, long
     ((T*)base)[idx] = from_float<T>(v);
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int PRO>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmArgs g) {
     using S = GemmShape<BN>;
+    const int STAGES_RT = PRO ? g.stages : S::STAGES;       // with the NORM prologue the stages hold weights only
     extern __shared__ unsigned char smem_dyn[];
     const unsigned base = (smem_u32(smem_dyn) + 1023u) & ~1023u;          // tiles want 1024-byte alignment
     const unsigned a_base = base;
-    const unsigned b_base = base + S::STAGES * G_A_BYTES;
-    const unsigned bar_base = base + S::STAGES * S::STAGE_BYTES;
+    const unsigned b_base = base + STAGES_RT * G_A_BYTES;
+    // PRO: the whole activation operand stays resident, one [BN][64] tile per K block
+    const unsigned b_bytes_total = PRO ? (unsigned)g.k_blocks * S::B_BYTES : (unsigned)S::STAGES * S::B_BYTES;
+    const unsigned bar_off = STAGES_RT * G_A_BYTES + b_bytes_total;
+    const unsigned bar_base = base + bar_off;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (S::STAGES + s); };
     const unsigned accum_bar = bar_base + 8u * (2 * S::STAGES);
     const unsigned tmem_slot = bar_base + 8u * (2 * S::STAGES + 1);
+    const unsigned bready_bar = bar_base + 8u * (2 * S::STAGES + 2);
     unsigned char* smem_generic = smem_dyn + (base - smem_u32(smem_dyn));
-    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + S::STAGES * S::STAGE_BYTES + 8 * (2 * S::STAGES + 1));
-    int* tok_pos = reinterpret_cast<int*>(smem_generic + S::STAGES * S::STAGE_BYTES + 256);              // [BN]
+    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * (2 * S::STAGES + 1));
+    int* tok_pos = reinterpret_cast<int*>(smem_generic + bar_off + 256);              // [BN]
     long long* tok_off = reinterpret_cast<long long*>(tok_pos + BN);                                      // [BN], 8-byte aligned: BN*4 is a multiple of 8
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -173,6 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(accum_bar, 1);
+        mbar_init(bready_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -189,22 +273,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // ---------------- TMA producer.  The weights do not depend on the kernels before this one: the first
         // round of weight tiles is requested before the wait for those kernels, the activations after it.
         if (lane == 0) {
-            const int early = min(n_kb, S::STAGES);
+            const unsigned stage_tx = PRO ? (unsigned)G_A_BYTES : (unsigned)S::STAGE_BYTES;
+            const int early = min(n_kb, STAGES_RT);
             for (int i = 0; i < early; ++i) {
-                mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
+                mbar_expect_tx(full_bar(i), stage_tx);
                 tma_load_2d(a_base + i * G_A_BYTES, &map_w, (kb_begin + i) * G_BK, m0, full_bar(i));
             }
-            grid_dependency_wait();
-            for (int i = 0; i < early; ++i)
-                tma_load_2d(b_base + i * S::B_BYTES, &map_x, (kb_begin + i) * G_BK, n0, full_bar(i));
+            if (!PRO) {
+                grid_dependency_wait();
+                for (int i = 0; i < early; ++i)
+                    tma_load_2d(b_base + i * S::B_BYTES, &map_x, (kb_begin + i) * G_BK, n0, full_bar(i));
+            }
             for (int i = early; i < n_kb; ++i) {
-                const int s = i % S::STAGES;
-                const unsigned phase = (i / S::STAGES) & 1;
+                const int s = i % STAGES_RT;
+                const unsigned phase = (i / STAGES_RT) & 1;
                 if (!mbar_wait(empty_bar(s), phase ^ 1u, g.status, 1)) break;
-                mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+                mbar_expect_tx(full_bar(s), stage_tx);
                 const int k = (kb_begin + i) * G_BK;
                 tma_load_2d(a_base + s * G_A_BYTES, &map_w, k, m0, full_bar(s));
-                tma_load_2d(b_base + s * S::B_BYTES, &map_x, k, n0, full_bar(s));
+                if (!PRO) tma_load_2d(b_base + s * S::B_BYTES, &map_x, k, n0, full_bar(s));
             }
         }
     } else if (warp == 1) {
@@ -212,14 +299,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             constexpr unsigned idesc = umma_idesc(BN);
             bool ok = true;
+            if (PRO) ok = mbar_wait(bready_bar, 0, g.status, 2);       // the block's own activation operand is written
             for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % S::STAGES;
-                const unsigned phase = (i / S::STAGES) & 1;
+                const int s = i % STAGES_RT;
+                const unsigned phase = (i / STAGES_RT) & 1;
                 ok = mbar_wait(full_bar(s), phase, g.status, 2);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const unsigned long long a_desc = umma_desc_sw128(a_base + s * G_A_BYTES);
-                const unsigned long long b_desc = umma_desc_sw128(b_base + s * S::B_BYTES);
+                const unsigned long long b_desc = umma_desc_sw128(b_base + (PRO ? (kb_begin + i) : s) * S::B_BYTES);
 #pragma unroll
                 for (int k = 0; k < G_BK / 16; ++k) {
                     // 16 elements = 32 bytes further along K inside the swizzle span: +2 in address/16 units
@@ -233,6 +321,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // ---------------- epilogue: warp q reads tensor-memory lanes 32q .. 32q+31
         const int q = warp & 3;
         grid_dependency_wait();                // positions, page lists and the output buffers may come from earlier kernels
+        if (PRO) {
+            // RMSNorm of the tile's tokens into the shared-memory operand: warp w takes rows w, w + 4, ...;
+            // a lane takes 16-byte chunks (8 elements) lane, lane + 32, ... of a row.  Layout of a K block's
+            // tile: row r at r * 128 bytes, its 16-byte chunk c at position c ^ (r % 8)  (128-byte swizzle).
+            const int chunks = g.K >> 3;
+            const int ew = warp - 2;
+            unsigned char* b_tiles = smem_generic + STAGES_RT * G_A_BYTES;
+            if (chunks <= 4 * 32) {
+                norm_rows_to_smem<4>(g.x_f32, g.gain, g.eps, g.K, g.k_blocks, n0, g.n_tok, ew, lane, BN, S::B_BYTES, b_tiles);
+            } else {
+                for (int r = ew; r < BN; r += 4) {
+                    const int tok = n0 + r;
+                    const bool live = tok < g.n_tok;
+                    const float* xr = g.x_f32 + (long long)tok * g.K;
+                    float ss = 0.0f;
+                    if (live) {
+#pragma unroll 4
+                        for (int ch = lane; ch < chunks; ch += 32) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch);
+                            const float4 b = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch + 1);
+                            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+                        }
+                    }
+                    ss = warp_sum(ss);
+                    const float scale = 1.0f / sqrtf(ss / (float)g.K + g.eps);
+                    const int k_chunks = g.k_blocks * 8;                       // chunks including the zero tail of the last K block
+#pragma unroll 4
+                    for (int ch = lane; ch < k_chunks; ch += 32) {
+                        uint4 packed = make_uint4(0, 0, 0, 0);
+                        if (live && ch < chunks) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch);
+                            const float4 b = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch + 1);
+                            packed = scale_pack8(a, b, scale, g.gain, ch);
+                        }
+                        const int kb = ch >> 3, c = ch & 7;
+                        *reinterpret_cast<uint4*>(b_tiles + kb * S::B_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes become visible to the tensor cores
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bready_bar) : "memory");
+        }
         if (EPI == EPI_QKV) {
             for (int t = threadIdx.x - 64; t < BN; t += 128) {
                 int p = 0;
@@ -254,7 +385,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
                 tmem_load16(tmem_acc + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
-                if (EPI == EPI_STORE) {
+                if (EPI == EPI_ADD) {
+                    if (row < g.n_out) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int tok = n0 + c0 + j;
+                            if (tok < g.n_tok) atomicAdd((float*)g.out + (long long)tok * g.n_out + row, v[j]);
+                        }
+                    }
+                } else if (EPI == EPI_STORE) {
                     if (row < g.n_out) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
@@ -366,27 +505,43 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     return r == CUDA_SUCCESS ? 0 : MLC_ERR_BAD_SIZE;
 }
 
-template <int BN, int EPI>
-static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t s) {
+constexpr int G_SMEM_MAX = 227 * 1024;
+
+template <int BN, int EPI, int PRO>
+static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs g, dim3 grid, cudaStream_t s) {
     using S = GemmShape<BN>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
+    size_t smem = S::SMEM_BYTES;
+    if (PRO) {
+        // weights in as many stages as fit beside the resident activation operand
+        const size_t fixed = (size_t)g.k_blocks * S::B_BYTES + 1024 + 256 + S::META_BYTES;
+        int stages = S::STAGES;
+        while (stages > 2 && fixed + (size_t)stages * G_A_BYTES > (size_t)G_SMEM_MAX) --stages;
+        if (fixed + (size_t)stages * G_A_BYTES > (size_t)G_SMEM_MAX) return MLC_ERR_BAD_SIZE;
+        g.stages = stages;
+        smem = fixed + (size_t)stages * G_A_BYTES;
     }
-    cudaError_t e = launch_pdl(gemm_tcgen05_kernel<BN, EPI>, grid, dim3(G_THREADS), (size_t)S::SMEM_BYTES, s, mw, mx, g);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    cudaError_t e = launch_pdl(gemm_tcgen05_kernel<BN, EPI, PRO>, grid, dim3(G_THREADS), smem, s, mw, mx, g);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
 template <int EPI>
 static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t s) {
+    if (g.x_f32 != nullptr) {
+        if (bn != 16) return MLC_ERR_BAD_SIZE;              // the NORM prologue is for decode steps of up to 16 tokens
+        return launch_gemm<16, EPI, 1>(mw, mx, g, grid, s);
+    }
     switch (bn) {
-        case 16: return launch_gemm<16, EPI>(mw, mx, g, grid, s);
-        case 32: return launch_gemm<32, EPI>(mw, mx, g, grid, s);
-        case 64: return launch_gemm<64, EPI>(mw, mx, g, grid, s);
-        case 128: return launch_gemm<128, EPI>(mw, mx, g, grid, s);
-        case 256: return launch_gemm<256, EPI>(mw, mx, g, grid, s);
+        case 16: return launch_gemm<16, EPI, 0>(mw, mx, g, grid, s);
+        case 32: return launch_gemm<32, EPI, 0>(mw, mx, g, grid, s);
+        case 64: return launch_gemm<64, EPI, 0>(mw, mx, g, grid, s);
+        case 128: return launch_gemm<128, EPI, 0>(mw, mx, g, grid, s);
+        case 256: return launch_gemm<256, EPI, 0>(mw, mx, g, grid, s);
     }
     return MLC_ERR_BAD_SIZE;
 }
@@ -395,7 +550,9 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 
 using namespace mlc;
 
-// x: bfloat16 [n_tok][K]; w: bfloat16 [n_out][K] (K a multiple of 8, both 16-byte aligned).
+// x: bfloat16 [n_tok][K], or, with norm_gain given, the float32 residual stream [n_tok][K] that the kernel
+// normalises itself (eps, norm_gain [K]; block_tokens must be 16); w: bfloat16 [n_out][K] (K a multiple of 8,
+// both 16-byte aligned).  epilogue 3 adds into out (float32 [n_tok][n_out]) atomically, any n_splits.
 // epilogue 0: out [n_splits][n_tok][n_out] (float32 or bfloat16): with n_splits > 1 the K range is shared out over
 // blocks and each leaves its partial sums in its own slice for the consumer to add; 1: out [n_tok][n_out/2],
 // n_splits must be 1;
@@ -403,14 +560,17 @@ using namespace mlc;
 // block_tokens: 16, 32, 64, 128 or 256.  status: one int on the device, 0 before the call; a bounded
 // wait that ran out leaves 1 (loader), 2 (tensor cores) or 3 (epilogue) there.
 extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_tok, int n_out, int K,
-                                int block_tokens, int n_splits, int epilogue, int* status, const float* bias,
+                                int block_tokens, int n_splits, int epilogue, int* status, const float* norm_gain,
+                                float norm_eps, const float* bias,
                                 const int* positions, const int* tok_seq, const void* rope_table, int rope_positions,
                                 int q_heads, int kv_heads, int hd, void* k_pool, void* v_pool, const int* page_table,
                                 long long entry_offset, int pages_per_seq, int page_size, void* stream) {
     if (n_tok <= 0 || n_out <= 0) return 0;
     if (K <= 0 || (K & 7) || (((uintptr_t)x | (uintptr_t)w) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
-    if (n_splits < 1 || (epilogue != EPI_STORE && n_splits != 1) || status == nullptr) return MLC_ERR_BAD_SIZE;
+    if (n_splits < 1 || (epilogue != EPI_STORE && epilogue != EPI_ADD && n_splits != 1) || status == nullptr) return MLC_ERR_BAD_SIZE;
+    if (epilogue == EPI_ADD && out_dtype != MLC_DTYPE_F32) return MLC_ERR_BAD_DTYPE;
+    if (norm_gain != nullptr && (n_splits != 1 || block_tokens != 16 || (((uintptr_t)norm_gain) & 15))) return MLC_ERR_BAD_SIZE;
     GemmArgs g{};
     g.out = out;
     g.out_dtype = out_dtype;
@@ -421,6 +581,13 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     if ((long long)(n_splits - 1) * g.k_blocks_per_split >= g.k_blocks) return MLC_ERR_BAD_SIZE;   // an empty split
     g.split_stride = (long long)n_tok * n_out;
     g.status = status;
+    g.K = K;
+    g.stages = 0;
+    if (norm_gain != nullptr) {
+        g.x_f32 = (const float*)x;
+        g.gain = norm_gain;
+        g.eps = norm_eps;
+    }
     if (epilogue == EPI_SILU_MUL && (n_out & 1)) return MLC_ERR_BAD_SIZE;
     if (epilogue == EPI_QKV) {
         if (hd <= 0 || (hd & 1) || n_out != (q_heads + 2 * kv_heads) * hd || positions == nullptr) return MLC_ERR_BAD_SIZE;
@@ -438,13 +605,18 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, n_out, K, G_BM);
     if (rc) return rc;
-    rc = make_map(&mx, x, n_tok, K, block_tokens);
-    if (rc) return rc;
+    if (norm_gain == nullptr) {
+        rc = make_map(&mx, x, n_tok, K, block_tokens);
+        if (rc) return rc;
+    } else {
+        mx = mw;                                            // unused by the kernel in this mode
+    }
     dim3 grid((n_out + G_BM - 1) / G_BM, (n_tok + block_tokens - 1) / block_tokens, n_splits);
     if (grid.y > 65535 || grid.z > 65535) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (epilogue == EPI_STORE) return dispatch_bn<EPI_STORE>(block_tokens, mw, mx, g, grid, s);
     if (epilogue == EPI_SILU_MUL) return dispatch_bn<EPI_SILU_MUL>(block_tokens, mw, mx, g, grid, s);
     if (epilogue == EPI_QKV) return dispatch_bn<EPI_QKV>(block_tokens, mw, mx, g, grid, s);
+    if (epilogue == EPI_ADD) return dispatch_bn<EPI_ADD>(block_tokens, mw, mx, g, grid, s);
     return MLC_ERR_UNSUPPORTED;
 }

@@ -93,7 +93,11 @@ def bench_gemm(args) -> None:
     ws = [(torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV) for _ in range(C)]
     nbytes = N * K * 2 + T * K * 2
     flops = 2.0 * T * N * K
-    epi = {"store": 0, "silu": 1, "qkv": 2}[args.epilogue]
+    epi = {"store": 0, "silu": 1, "qkv": 2, "add": 3}[args.epilogue]
+    norm = {}
+    if args.norm:
+        x = torch.randn(T, K, device=DEV)
+        norm = dict(norm_gain=torch.ones(K, device=DEV), norm_eps=1e-6)
     if args.library:
         out = torch.empty(T, N, dtype=torch.float32, device=DEV)
         report(f"library product T={T} N={N} K={K}", lambda i: torch.mm(x, ws[i % C].t(), out_dtype=torch.float32, out=out),
@@ -101,11 +105,15 @@ def bench_gemm(args) -> None:
         return
     if epi == 0:
         out = torch.empty(args.splits, T, N, dtype=torch.float32, device=DEV)
-        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 0, args.splits, args.block_tokens)
+        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 0, args.splits, args.block_tokens, **norm)
         nbytes += args.splits * T * N * 4
+    elif epi == 3:
+        out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 3, args.splits, args.block_tokens)
+        nbytes += T * N * 4
     elif epi == 1:
         out = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
-        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 1, 1, args.block_tokens)
+        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 1, 1, args.block_tokens, **norm)
         nbytes += T * N
     else:
         hd, KV = args.head_dim, args.kv_heads
@@ -122,9 +130,9 @@ def bench_gemm(args) -> None:
         bias = torch.randn(N, device=DEV)
         out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
         fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 2, 1, args.block_tokens, bias=bias, positions=positions,
-                                            tok_seq=tok_seq, rope=rope, q_heads=H, kv_heads=KV, head_dim=hd, kv=kv)
+                                            tok_seq=tok_seq, rope=rope, q_heads=H, kv_heads=KV, head_dim=hd, kv=kv, **norm)
         nbytes += T * N * 2
-    report(f"tcgen05 product T={T} N={N} K={K} epilogue={args.epilogue} splits={args.splits}", fn, args, nbytes, flops)
+    report(f"tcgen05 product T={T} N={N} K={K} epilogue={args.epilogue} splits={args.splits} norm={bool(args.norm)}", fn, args, nbytes, flops)
 
 
 def bench_norm(args) -> None:
@@ -172,7 +180,8 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--rows", type=int, default=9728)
     ap.add_argument("--k", type=int, default=896)
-    ap.add_argument("--epilogue", default="store", choices=["store", "silu", "qkv"])
+    ap.add_argument("--epilogue", default="store", choices=["store", "silu", "qkv", "add"])
+    ap.add_argument("--norm", action="store_true", help="RMSNorm of a float32 input inside the product's prologue")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--slices", type=int, default=0)
     ap.add_argument("--block-tokens", type=int, default=None)

@@ -24,16 +24,17 @@ from .base import Runtime
 
 SMALL_BATCH = 64          # up to this many rows a plain product runs on the tcgen05 kernel with split K
 MAX_SPLITS = 8            # partial sums the consumer has to add
+ADD_MAX_SPLITS = 24       # splits of a product that adds into the stream atomically (nobody has to add them up)
 
 
-def split_count(n_out: int, k: int, n_tok: int, n_sms: int) -> int:
+def split_count(n_out: int, k: int, n_tok: int, n_sms: int, max_splits: int = 0) -> int:
     """How many blocks share the K range of a skinny product: enough to occupy the SMs, each
     with at least two 64-element K steps."""
     if n_tok > SMALL_BATCH:
         return 1
     row_tiles = (n_out + 127) // 128
     k_blocks = (k + 63) // 64
-    s = max(1, min(n_sms // max(1, row_tiles), k_blocks // 2, MAX_SPLITS))
+    s = max(1, min(n_sms // max(1, row_tiles), k_blocks // 2, max_splits or MAX_SPLITS))
     per = (k_blocks + s - 1) // s
     return (k_blocks + per - 1) // per
 
@@ -49,6 +50,16 @@ class Linear:
 
     def nbytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
+
+    def can_add_into_stream(self, n_rows: int) -> bool:
+        """Whether `add_into` has a kernel for this many rows (the tcgen05 product with atomic adds)."""
+        return self.tensor_core_ok and n_rows <= SMALL_BATCH
+
+    def add_into(self, x: torch.Tensor, stream: torch.Tensor) -> None:
+        """stream (float32 [n, out]) += x · Wᵀ, the K range shared out over as many blocks as is useful."""
+        m = x.shape[0]
+        splits = split_count(self.out_features, self.in_features, m, self.runtime.n_sms, max_splits=ADD_MAX_SPLITS)
+        kernels.gemm_tcgen05(x, self.weight, stream, kernels.bindings.EPI_ADD, splits, n_sms=self.runtime.n_sms)
 
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype = torch.float32, partial_ok: bool = False) -> torch.Tensor:
         """[n, out] in `out_dtype`; with `partial_ok` possibly float32 partial sums [slices, n, out]

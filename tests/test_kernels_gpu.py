@@ -299,6 +299,35 @@ def test_tcgen05_product_with_qkv_epilogue(H, KV, hd, T):
     assert torch.isnan(kv.k_pool[0].float()).all()
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 256, 64), (8, 1152, 896), (16, 300, 344), (5, 128, 1000)])
+def test_tcgen05_product_with_norm_prologue(T, N, K):
+    """The kernel normalises the float32 stream itself and writes its own swizzled operand."""
+    g = torch.Generator().manual_seed(T * N)
+    x = torch.randn(T, K, generator=g) * 2
+    gain = 1 + 0.2 * torch.randn(K, generator=g)
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+    out = torch.full((1, T, N), float("nan"), device=DEV)
+    kernels.gemm_tcgen05(x.to(DEV), w.to(DEV), out, 0, norm_gain=gain.to(DEV), norm_eps=1e-5)
+    kernels.check_gemm_status(DEV)
+    h = plain_impl.rmsnorm(x, gain, 1e-5).to(torch.bfloat16).float()
+    close(out[0], h.double() @ w.double().t(), 2e-3)             # bfloat16 rounding of h may differ in the last bit
+    with pytest.raises(kernels.KernelError, match="16 tokens"):
+        kernels.gemm_tcgen05(torch.zeros(17, K, device=DEV), w.to(DEV), torch.empty(1, 17, N, device=DEV), 0,
+                             norm_gain=gain.to(DEV), norm_eps=1e-5)
+
+
+@pytest.mark.parametrize("T,N,K,splits", [(8, 896, 4864, 19), (64, 896, 896, 7), (3, 200, 128, 1), (16, 130, 1000, 4)])
+def test_tcgen05_product_adding_into_the_stream(T, N, K, splits):
+    g = torch.Generator().manual_seed(N + K)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+    stream0 = torch.randn(T, N, generator=g)
+    stream = stream0.clone().to(DEV)
+    kernels.gemm_tcgen05(x.to(DEV), w.to(DEV), stream, 3, splits)
+    kernels.check_gemm_status(DEV)
+    close(stream, stream0.double() + x.double() @ w.double().t(), 3e-6)
+
+
 def test_tcgen05_product_refuses_what_it_cannot_take():
     x = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
