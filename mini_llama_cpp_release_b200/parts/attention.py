@@ -143,6 +143,7 @@ class GQAttention(Part):
             kernels.gemm_tcgen05(h, proj.weight, q, kernels.bindings.EPI_QKV, bias=bias, positions=step.positions,
                                  tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
                                  kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms,
+                                 block_tokens=16 if n <= 64 else None,     # short epilogues in more blocks beat one long one
                                  norm_gain=norm.gain if norm is not None else None,
                                  norm_eps=norm.eps if norm is not None else 0.0)
         else:
