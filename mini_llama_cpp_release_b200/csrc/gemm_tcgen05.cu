@@ -59,6 +59,7 @@ struct GemmArgs {
     float eps;
     int K;
     int stages;                // shared-memory stages in use (<= GemmShape::STAGES)
+    unsigned long long* timing;  // optional [blocks][8] nanosecond stamps of a block's phases (for tuning), or null
     // QKV epilogue
     const float* bias;         // [n_out] in the stored row order, or null
     const int* positions;      // [tokens]
@@ -246,6 +247,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * G_BM, n0 = blockIdx.y * BN, split = blockIdx.z;
+    unsigned long long* stamps = g.timing == nullptr ? nullptr
+        : g.timing + 8ull * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
+    if (stamps != nullptr && threadIdx.x == 0) stamps[0] = global_ns();                 // block start
     const int kb_begin = split * g.k_blocks_per_split;
     const int kb_end = min(g.k_blocks, kb_begin + g.k_blocks_per_split);
     const int n_kb = kb_end - kb_begin;
@@ -267,6 +271,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     tcgen05_fence_after();
     const unsigned tmem_acc = *tmem_slot_ptr;
+    if (stamps != nullptr && threadIdx.x == 0) stamps[1] = global_ns();                 // barriers and tensor memory ready
 
     grid_launch_dependents();                  // the next kernel may start its own set-up now
     if (warp == 0) {
@@ -305,6 +310,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const unsigned phase = (i / STAGES_RT) & 1;
                 ok = mbar_wait(full_bar(s), phase, g.status, 2);
                 if (!ok) break;
+                if (stamps != nullptr && i == 0) stamps[2] = global_ns();                // first tiles have landed
                 tcgen05_fence_after();
                 const unsigned long long a_desc = umma_desc_sw128(a_base + s * G_A_BYTES);
                 const unsigned long long b_desc = umma_desc_sw128(b_base + (PRO ? (kb_begin + i) : s) * S::B_BYTES);
@@ -315,6 +321,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
                 tcgen05_commit(empty_bar(s));          // the stage is free once these products have read it
             }
+            if (stamps != nullptr) stamps[3] = global_ns();                              // last product issued
             tcgen05_commit(accum_bar);                 // arrives when every product issued so far is done
         }
     } else {
@@ -379,7 +386,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         const bool ok = mbar_wait(accum_bar, 0, g.status, 3);
         tcgen05_fence_after();
+        if (stamps != nullptr && threadIdx.x == 64) stamps[4] = global_ns();             // accumulators complete
         const int row = m0 + q * 32 + lane;
+        // SiLU epilogue through shared memory: bfloat16 output, a full 16-output group inside the matrix, aligned rows
+        const bool silu_staged = EPI == EPI_SILU_MUL && g.out_dtype == MLC_DTYPE_BF16 && ((g.n_out >> 1) & 7) == 0 &&
+                                 (m0 + q * 32 + 32 <= g.n_out) && ((((uintptr_t)g.out) & 15) == 0);
         if (ok && n_kb > 0) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -408,16 +419,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 } else if (EPI == EPI_SILU_MUL) {
                     // even lane: gate_j, odd lane: up_j, j = row / 2
                     const int half_out = g.n_out >> 1;
+                    if (silu_staged) {
+                        // Two tokens per step so that every lane produces a value: the even lane of a pair takes
+                        // token j (its own gate, the neighbour's up), the odd lane token j+1.  Results go to a
+                        // per-warp staging tile [token][16 outputs] in shared memory and leave in 16-byte stores.
+                        bf16* stage = reinterpret_cast<bf16*>(smem_generic) + q * BN * 16;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                        const int tok = n0 + c0 + j;
-                        if ((lane & 1) == 0 && row < g.n_out && tok < g.n_tok) {
-                            const float gate = v[j], up = other;
+                        for (int j = 0; j < 16; j += 2) {
+                            const float send = (lane & 1) ? v[j] : v[j + 1];
+                            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                            const float gate = (lane & 1) ? recv : v[j];
+                            const float up = (lane & 1) ? v[j + 1] : recv;
                             const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
-                            const long long idx = (long long)tok * half_out + (row >> 1);
-                            if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, act);
-                            else store_out<bf16>(g.out, idx, act);
+                            stage[(c0 + j + (lane & 1)) * 16 + (lane >> 1)] = __float2bfloat16_rn(act);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                            const int tok = n0 + c0 + j;
+                            if ((lane & 1) == 0 && row < g.n_out && tok < g.n_tok) {
+                                const float gate = v[j], up = other;
+                                const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
+                                const long long idx = (long long)tok * half_out + (row >> 1);
+                                if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, act);
+                                else store_out<bf16>(g.out, idx, act);
+                            }
                         }
                     }
                 } else {
@@ -466,9 +493,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 }
             }
+            if (EPI == EPI_SILU_MUL && silu_staged) {
+                __syncwarp();
+                const int half_out = g.n_out >> 1;
+                const bf16* stage = reinterpret_cast<const bf16*>(smem_generic) + q * BN * 16;
+                for (int t = lane; t < BN; t += 32) {
+                    if (n0 + t < g.n_tok) {
+                        const uint4* src = reinterpret_cast<const uint4*>(stage + t * 16);
+                        uint4* dst = reinterpret_cast<uint4*>((bf16*)g.out + (long long)(n0 + t) * half_out + (m0 >> 1) + q * 16);
+                        dst[0] = src[0];
+                        dst[1] = src[1];
+                    }
+                }
+            }
         }
     }
 
+    if (stamps != nullptr && threadIdx.x == 64) stamps[5] = global_ns();                 // epilogue done
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -560,7 +601,7 @@ using namespace mlc;
 // block_tokens: 16, 32, 64, 128 or 256.  status: one int on the device, 0 before the call; a bounded
 // wait that ran out leaves 1 (loader), 2 (tensor cores) or 3 (epilogue) there.
 extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_tok, int n_out, int K,
-                                int block_tokens, int n_splits, int epilogue, int* status, const float* norm_gain,
+                                int block_tokens, int n_splits, int epilogue, int* status, unsigned long long* timing, const float* norm_gain,
                                 float norm_eps, const float* bias,
                                 const int* positions, const int* tok_seq, const void* rope_table, int rope_positions,
                                 int q_heads, int kv_heads, int hd, void* k_pool, void* v_pool, const int* page_table,
@@ -583,6 +624,7 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     g.status = status;
     g.K = K;
     g.stages = 0;
+    g.timing = timing;
     if (norm_gain != nullptr) {
         g.x_f32 = (const float*)x;
         g.gain = norm_gain;

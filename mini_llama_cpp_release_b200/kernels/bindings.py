@@ -94,7 +94,7 @@ def core() -> ctypes.CDLL:
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
-            "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, F, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
+            "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, P, F, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
@@ -415,7 +415,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
                  positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
                  rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
                  kv: Optional[KVView] = None, n_sms: int = 148, norm_gain: Optional[torch.Tensor] = None,
-                 norm_eps: float = 0.0) -> None:
+                 norm_eps: float = 0.0, timing: Optional[torch.Tensor] = None) -> None:
     """bfloat16 x [n, K] times bfloat16 w [rows, K] transposed on the tcgen05 tensor cores, with
     the epilogue done before anything is stored (see csrc/gemm_tcgen05.cu).  With `norm_gain`, x is
     the float32 residual stream [n <= 16, K] and the kernel applies RMSNorm(eps, gain) to it itself.
@@ -453,7 +453,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
         cache = (None, None, None, 0, 0, 1)
     status = gemm_status(x.device)
     _check(core().mlc_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
-                                   block_tokens, n_splits, epilogue, status.data_ptr(), _ptr(norm_gain), float(norm_eps),
+                                   block_tokens, n_splits, epilogue, status.data_ptr(), _ptr(timing), _ptr(norm_gain),
+                                   float(norm_eps),
                                    _ptr(bias), _ptr(positions),
                                    _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
                                    kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product")
