@@ -404,6 +404,10 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     grid_launch_dependents();
     grid_dependency_wait();                    // queries and the step's keys were written by the kernel before
     const int b = blockIdx.z;
+    // The sequence's page list is fetched at once, before its length is known: one trip to memory instead of
+    // two dependent ones (lengths, then pages).
+    for (int t = threadIdx.x; t < c.pages_per_seq && t < MAX_TILES_STAGED; t += DNW * 32)
+        tile_pages[t] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
     int y = blockIdx.y;
     const int split = y % a.n_splits;  y /= a.n_splits;
     const int chunk = y % a.head_chunks;  y /= a.head_chunks;
@@ -434,8 +438,6 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         }
         *reinterpret_cast<uint4*>(Qs + r * STRIDE + ch * 8) = v;
     }
-    for (int t = my_begin + tid; t < my_end && t - my_begin < MAX_TILES_STAGED; t += DNW * 32)
-        tile_pages[t - my_begin] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
     __syncthreads();
 
     int row_hi[2], row_lo[2];
@@ -464,8 +466,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     bf16* my_stages = KVs + warp * D_NSTAGE * 2 * D_STAGE;
     auto load_sub = [&](int stage, int st) {
         const int tile = st / SUB;
-        const int page = (tile - my_begin < MAX_TILES_STAGED) ? tile_pages[tile - my_begin]
-                                                              : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
+        const int page = (tile < MAX_TILES_STAGED) ? tile_pages[tile] : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
         const long long base = c.entry_offset + (((long long)max(page, 0) * c.kv_heads + kvh) * TILE + (st % SUB) * DKT) * HD;
         bf16* kd = my_stages + stage * 2 * D_STAGE;
         bf16* vd = kd + D_STAGE;

@@ -370,9 +370,9 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
     lib = attention_library(hd)
     _check(lib.mlc_attention_mma(q.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), start_pos.data_ptr(), n_seqs,
                                  n_tokens, max_q_len, q_heads, kv.kv_heads, hd, float(scale), int(window), row_tiles,
-                                 1 if warp_private else 0, n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(),
-                                 kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq, kv.page_size, _stream()),
-           "tensor-core attention")
+                                 1 if warp_private else 0, n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(),
+                                 kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq,
+                                 kv.page_size, _stream()), "tensor-core attention")
     if n_splits > 1:
         _check(core().mlc_attention_combine(part_ml.data_ptr(), part_o.data_ptr(), n_tokens * q_heads, n_splits, hd,
                                             out.data_ptr(), dtype_code(out.dtype), _stream()), "attention combine")
