@@ -175,28 +175,32 @@ class Context:
         step's inputs to the device and the chosen ids back; `last_copy_bytes` says how much."""
         self._check_decode(slots, tokens, 1)
         slots = list(slots)
-        with torch.cuda.device(self.model.runtime.device):
-            for s in slots:
-                self.cache.reserve(s, 1)
-            lengths = [self.cache.length[s] for s in slots]
-            runner = self._runner(len(slots), max(lengths) + 1, sampler)
-            h2d = 0
-            if runner.graph is None:
-                runner.load(slots, tokens, seq_ids)
-                runner.capture()
-                runner.loaded_slots = None
-            if runner.loaded_slots != slots or runner.loaded_ids != list(seq_ids):
-                runner.load(slots, tokens, seq_ids)
-                runner.loaded_ids = list(seq_ids)
-                h2d += runner.host_buf.numel() * 4
-            else:
-                h2d += runner.load_step(tokens, lengths)
-                h2d += runner.refresh_pages(slots)
-            runner.replay()
-            chosen = runner.read_chosen()
+        cache = self.cache
+        dev = self.model.runtime.device
+        if torch.cuda.current_device() != (dev.index or 0):
+            torch.cuda.set_device(dev)
+        for s in slots:
+            cache.reserve(s, 1)
+        lengths = [cache.length[s] for s in slots]
+        runner = self._runner(len(slots), max(lengths) + 1, sampler)
+        h2d = 0
+        if runner.graph is None:
+            runner.load(slots, tokens, seq_ids)
+            runner.capture()
+            runner.loaded_slots = None
+        if runner.loaded_slots != slots or runner.loaded_ids != list(seq_ids):
+            runner.load(slots, tokens, seq_ids)
+            runner.loaded_ids = list(seq_ids)
+            h2d += runner.host_buf.numel() * 4
+        else:
+            h2d += runner.load_step(tokens, lengths)
+            h2d += runner.refresh_pages(slots)
+        runner.replay()
+        chosen = runner.read_chosen()
+        history = self.token_history
         for s, t in zip(slots, tokens):
-            self.cache.commit(s, 1)
-            self.token_history[s].append(int(t))
+            cache.commit(s, 1)
+            history[s].append(int(t))
         self.n_steps += 1
         self.last_copy_bytes = (h2d, 4 * len(slots))
         return chosen, runner.logits

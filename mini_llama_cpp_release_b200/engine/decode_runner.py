@@ -59,6 +59,7 @@ class DecodeRunner:
             total += (n + 3) // 4 * 4
         self.dev_buf = torch.zeros(total, dtype=torch.int32, device=dev)
         self.host_buf = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host_buf.numpy()                       # the same pinned memory, for cheap writes from lists
         self.step_inputs = 4 * B                                    # ints copied to the device at every step
         self.history = torch.zeros(self.HISTORY_STEPS, B, dtype=torch.int32, device=dev)
         self.chosen_host = torch.zeros(B, dtype=torch.int32).pin_memory()
@@ -69,6 +70,8 @@ class DecodeRunner:
         h("want_rows")[:] = torch.arange(B, dtype=torch.int32)
         for g in range(n_groups):
             h(f"pages{g}")[:] = -1
+        self.chosen_dev = self.view("chosen")
+        self.sync_stream = torch.cuda.current_stream(dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.launches_per_step = 0
@@ -157,11 +160,16 @@ class DecodeRunner:
     def refresh_pages(self, slots: Sequence[int]) -> int:
         """Copy the page tables again if any sequence got or lost a page; returns bytes copied."""
         changed = False
-        for g in range(len(self.cache.groups)):
+        page_lists = self.cache.page_lists
+        for g, group in enumerate(self.cache.groups):
+            counts = self.page_counts[g]
+            if group.need.kind == "window":
+                changed = True
+                break
             for b, s in enumerate(slots):
-                pl = self.cache.page_lists[s][g]
-                if len(pl) != self.page_counts[g][b] or (self.cache.groups[g].need.kind == "window"):
+                if len(page_lists[s][g]) != counts[b]:
                     changed = True
+                    break
         if not changed:
             return 0
         self._fill_pages(slots)
@@ -174,13 +182,15 @@ class DecodeRunner:
 
     def load_step(self, tokens: Sequence[int], lengths: Sequence[int]) -> int:
         """The per-step inputs from the host: tokens and positions.  Returns bytes copied."""
-        h = self.host_view
-        pos = torch.tensor(list(lengths), dtype=torch.int32)
-        h("tokens")[:] = torch.tensor(list(tokens), dtype=torch.int32)
-        h("positions")[:] = pos
-        h("start_pos")[:] = pos
-        h("sample_pos")[:] = pos + 1
-        end = self.offsets["sample_pos"][0] + self.B              # the four segments lie first, in this order
+        B = self.B
+        np_buf = self.host_np
+        o_tok, o_pos, o_start, o_samp = (self.offsets[n][0] for n in ("tokens", "positions", "start_pos", "sample_pos"))
+        np_buf[o_tok:o_tok + B] = tokens
+        np_buf[o_pos:o_pos + B] = lengths
+        np_buf[o_start:o_start + B] = lengths
+        np_buf[o_samp:o_samp + B] = lengths
+        np_buf[o_samp:o_samp + B] += 1
+        end = o_samp + B                                          # the four segments lie first, in this order
         self.dev_buf[:end].copy_(self.host_buf[:end], non_blocking=True)
         return 4 * end
 
@@ -190,8 +200,8 @@ class DecodeRunner:
         kernels.count_library_launches(self.library_launches_per_step)
 
     def read_chosen(self) -> List[int]:
-        self.chosen_host.copy_(self.view("chosen"), non_blocking=True)
-        torch.cuda.current_stream(self.model.runtime.device).synchronize()
+        self.chosen_host.copy_(self.chosen_dev, non_blocking=True)
+        self.sync_stream.synchronize()
         self.reads = getattr(self, "reads", 0) + 1
         if self.reads % 64 == 1:
             kernels.check_gemm_status(self.model.runtime.device)
