@@ -8,7 +8,8 @@
 // 128-byte swizzle span per row) through a ring of shared-memory stages:
 //     warp 0   one thread issues the TMA loads of the W tile and the activation tile;
 //     warp 1   allocates tensor memory, one thread issues tcgen05.mma and commits;
-//     warps 2-5  read the accumulators with tcgen05.ld (each warp its 32 lanes) and run the epilogue.
+//     warps 2-5 (2-9 for tiles of 64 tokens and more) read the accumulators with tcgen05.ld (each warp its 32
+//                lanes) and run the epilogue.
 // A K range can be split over blocks (blockIdx.z); partial sums then go to separate slices of
 // the output and the consumer adds them.
 //
@@ -22,10 +23,9 @@
 //
 //   ADD       adds y into a float32 [token][row] tensor (the residual stream) with atomic adds,
 //             so that any number of K splits can feed it (src/forward.cpp:772, 779).
-// Prologue NORM (up to 16 tokens): instead of loading bfloat16 activations with TMA the block reads
-// the float32 residual stream itself, computes x·1/sqrt(mean(x²)+eps)·gain per token
-// (src/ops.cpp:19-41) and writes the bfloat16 operand into shared memory in the swizzled layout,
-// which saves the separate norm kernel of a decode step.
+// Blocks are persistent: at most one per SM, each walks output tiles t, t + blocks, ...; a block keeps two
+// accumulators in tensor memory, so the epilogue of one tile runs while the tensor cores fill the next.
+// Tiles of 64 tokens and more have two groups of four epilogue warps that share out the tokens.
 //
 // Every wait on an mbarrier is bounded by a clock; a wait that runs out records a code in
 // `status`, the block skips its stores, frees its tensor memory and returns.
@@ -38,7 +38,6 @@ namespace mlc {
 
 constexpr int G_BM = 128;
 constexpr int G_BK = 64;
-constexpr int G_THREADS = 192;
 constexpr int G_A_BYTES = G_BM * G_BK * 2;                 // 16 KiB per stage
 constexpr unsigned long long G_WAIT_NS = 2000000000ull;     // two seconds
 
@@ -53,12 +52,7 @@ struct GemmArgs {
     int k_blocks_per_split;
     long long split_stride;    // elements between the output slices of two splits
     int* status;
-    // NORM prologue
-    const float* x_f32;        // [tokens][K] float32, or null: activations come through the tensor map
-    const float* gain;         // [K]
-    float eps;
-    int K;
-    int stages;                // shared-memory stages in use (<= GemmShape::STAGES)
+    int m_tiles, n_tiles, n_splits;   // the grid of output tiles the persistent blocks walk
     unsigned long long* timing;  // optional [blocks][8] nanosecond stamps of a block's phases (for tuning), or null
     // QKV epilogue
     const float* bias;         // [n_out] in the stored row order, or null
@@ -145,122 +139,76 @@ __host__ __device__ constexpr unsigned umma_idesc(int bn) {
 }
 
 
-// ------------------------------------------------------------------ NORM prologue helpers
-// Eight stream values times scale times gain, rounded to bfloat16 and packed into 16 bytes.
-__device__ __forceinline__ uint4 scale_pack8(const float4& a, const float4& b, float scale, const float* __restrict__ gain, int ch) {
-    const float4 ga = __ldg(reinterpret_cast<const float4*>(gain) + 2 * ch);
-    const float4 gb = __ldg(reinterpret_cast<const float4*>(gain) + 2 * ch + 1);
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * scale * ga.x, a.y * scale * ga.y);
-    __nv_bfloat162 p1 = __floats2bfloat162_rn(a.z * scale * ga.z, a.w * scale * ga.w);
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x * scale * gb.x, b.y * scale * gb.y);
-    __nv_bfloat162 p3 = __floats2bfloat162_rn(b.z * scale * gb.z, b.w * scale * gb.w);
-    return make_uint4(*reinterpret_cast<unsigned*>(&p0), *reinterpret_cast<unsigned*>(&p1),
-                      *reinterpret_cast<unsigned*>(&p2), *reinterpret_cast<unsigned*>(&p3));
-}
-
-// RMSNorm of rows of up to CPL*256 elements straight into the swizzled shared-memory operand.  Warp `ew`
-// of four takes rows ew, ew+4, ...; two rows at a time, with every load of both rows issued before the
-// first use, so a pair of rows costs one trip to memory.  A lane owns 16-byte chunks lane, lane+32, ...
-template <int CPL>
-__device__ __forceinline__ void norm_rows_to_smem(const float* __restrict__ x, const float* __restrict__ gain, float eps, int K,
-                                                  int k_blocks, int n0, int n_tok, int ew, int lane, int rows, int tile_bytes,
-                                                  unsigned char* b_tiles) {
-    const int chunks = K >> 3, k_chunks = k_blocks * 8;
-    for (int r0 = ew; r0 < rows; r0 += 8) {
-        float4 va[2][CPL], vb[2][CPL];
-        bool live[2];
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            const int r = r0 + 4 * rr;
-            live[rr] = r < rows && n0 + r < n_tok;
-            const float* xr = x + (long long)(n0 + r) * K;
-#pragma unroll
-            for (int j = 0; j < CPL; ++j) {
-                const int ch = lane + 32 * j;
-                va[rr][j] = vb[rr][j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (live[rr] && ch < chunks) {
-                    va[rr][j] = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch);
-                    vb[rr][j] = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch + 1);
-                }
-            }
-        }
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            const int r = r0 + 4 * rr;
-            if (r >= rows) continue;
-            float ss = 0.0f;
-#pragma unroll
-            for (int j = 0; j < CPL; ++j) {
-                const float4 a = va[rr][j], b = vb[rr][j];
-                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
-            }
-            ss = warp_sum(ss);
-            const float scale = 1.0f / sqrtf(ss / (float)K + eps);
-#pragma unroll
-            for (int j = 0; j < CPL; ++j) {
-                const int ch = lane + 32 * j;
-                if (ch >= k_chunks) continue;
-                uint4 packed = make_uint4(0, 0, 0, 0);
-                if (live[rr] && ch < chunks) packed = scale_pack8(va[rr][j], vb[rr][j], scale, gain, ch);
-                const int kb = ch >> 3, c = ch & 7;
-                *reinterpret_cast<uint4*>(b_tiles + kb * tile_bytes + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
-            }
-        }
-    }
-}
-
-template <int BN> struct GemmShape {
+template <int BN, int EPI> struct GemmShape {
     static constexpr int B_BYTES = BN * G_BK * 2;
     static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN <= 64) ? 8 : (BN <= 128 ? 6 : 4);
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static constexpr int META_BYTES = BN * 16;      // per token: position, cache offset (QKV epilogue)
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + META_BYTES;
+    static constexpr int STAGES = (BN <= 64) ? 8 : (BN <= 128 ? 6 : (EPI == EPI_SILU_MUL ? 3 : 4));
+    static constexpr int EPI_GROUPS = (BN >= 64) ? 2 : 1;            // epilogue warps: four per group, groups share out the tokens
+    static constexpr int THREADS = 64 + 128 * EPI_GROUPS;
+    static constexpr int ACC_COLS = BN < 32 ? 32 : BN;                // tensor-memory columns of one accumulator
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;                    // two accumulators: one is read out while the other fills
+    static constexpr int META_BYTES = BN * 16;                        // per token: position, cache offset (QKV epilogue)
+    static constexpr int STAGING_BYTES = (EPI == EPI_SILU_MUL) ? 128 * BN : 0;   // [8 or 4 warps][tokens][16 outputs] bfloat16
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + META_BYTES + 1024 /* alignment slack */;
 };
 
 template <typename T> __device__ __forceinline__ void store_out(void* base, long long idx, float v) {
     ((T*)base)[idx] = from_float<T>(v);
 }
 
-template <int BN, int EPI, int PRO>
-__global__ void __launch_bounds__(G_THREADS, 1)
+// One output tile: 128 rows of W x BN tokens x one K range.
+struct TileCoord {
+    int m0, n0, split, kb_begin, n_kb;
+};
+__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& g, int t, int bn) {
+    TileCoord c;
+    const int m_tile = t % g.m_tiles;
+    const int r = t / g.m_tiles;
+    c.m0 = m_tile * G_BM;
+    c.n0 = (r % g.n_tiles) * bn;
+    c.split = r / g.n_tiles;
+    c.kb_begin = c.split * g.k_blocks_per_split;
+    c.n_kb = min(g.k_blocks, c.kb_begin + g.k_blocks_per_split) - c.kb_begin;
+    return c;
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(GemmShape<BN, EPI>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmArgs g) {
-    using S = GemmShape<BN>;
-    const int STAGES_RT = PRO ? g.stages : S::STAGES;       // with the NORM prologue the stages hold weights only
+    using S = GemmShape<BN, EPI>;
+    constexpr int EG = S::EPI_GROUPS;
     extern __shared__ unsigned char smem_dyn[];
     const unsigned base = (smem_u32(smem_dyn) + 1023u) & ~1023u;          // tiles want 1024-byte alignment
+    unsigned char* smem_generic = smem_dyn + (base - smem_u32(smem_dyn));
     const unsigned a_base = base;
-    const unsigned b_base = base + STAGES_RT * G_A_BYTES;
-    // PRO: the whole activation operand stays resident, one [BN][64] tile per K block
-    const unsigned b_bytes_total = PRO ? (unsigned)g.k_blocks * S::B_BYTES : (unsigned)S::STAGES * S::B_BYTES;
-    const unsigned bar_off = STAGES_RT * G_A_BYTES + b_bytes_total;
+    const unsigned b_base = base + S::STAGES * G_A_BYTES;
+    constexpr unsigned staging_off = S::STAGES * S::STAGE_BYTES;
+    constexpr unsigned bar_off = staging_off + S::STAGING_BYTES;
     const unsigned bar_base = base + bar_off;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (S::STAGES + s); };
-    const unsigned accum_bar = bar_base + 8u * (2 * S::STAGES);
-    const unsigned tmem_slot = bar_base + 8u * (2 * S::STAGES + 1);
-    const unsigned bready_bar = bar_base + 8u * (2 * S::STAGES + 2);
-    unsigned char* smem_generic = smem_dyn + (base - smem_u32(smem_dyn));
-    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * (2 * S::STAGES + 1));
-    int* tok_pos = reinterpret_cast<int*>(smem_generic + bar_off + 256);              // [BN]
-    long long* tok_off = reinterpret_cast<long long*>(tok_pos + BN);                                      // [BN], 8-byte aligned: BN*4 is a multiple of 8
+    auto empty_bar = [&](int s) { return bar_base + 8u * (8 + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (16 + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (18 + b); };
+    const unsigned tmem_slot = bar_base + 8u * 20;
+    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 20);
+    int* tok_pos = reinterpret_cast<int*>(smem_generic + bar_off + S::BAR_BYTES);                         // [BN]
+    long long* tok_off = reinterpret_cast<long long*>(tok_pos + BN);                                      // [BN]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * G_BM, n0 = blockIdx.y * BN, split = blockIdx.z;
-    unsigned long long* stamps = g.timing == nullptr ? nullptr
-        : g.timing + 8ull * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
+    const int n_tiles_total = g.m_tiles * g.n_tiles * g.n_splits;
+    unsigned long long* stamps = g.timing == nullptr ? nullptr : g.timing + 8ull * blockIdx.x;
     if (stamps != nullptr && threadIdx.x == 0) stamps[0] = global_ns();                 // block start
-    const int kb_begin = split * g.k_blocks_per_split;
-    const int kb_end = min(g.k_blocks, kb_begin + g.k_blocks_per_split);
-    const int n_kb = kb_end - kb_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(accum_bar, 1);
-        mbar_init(bready_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 128 * EG);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -270,149 +218,134 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    const unsigned tmem_acc = *tmem_slot_ptr;
+    const unsigned tmem_base = *tmem_slot_ptr;
     if (stamps != nullptr && threadIdx.x == 0) stamps[1] = global_ns();                 // barriers and tensor memory ready
 
     grid_launch_dependents();                  // the next kernel may start its own set-up now
     if (warp == 0) {
-        // ---------------- TMA producer.  The weights do not depend on the kernels before this one: the first
-        // round of weight tiles is requested before the wait for those kernels, the activations after it.
+        // ---------------- TMA producer: one stream of (tile, K block) pairs through the stage ring.  The weights do
+        // not depend on the kernels before this one: the first ring of weight tiles is requested before the wait for
+        // those kernels, the activations after it.
         if (lane == 0) {
-            const unsigned stage_tx = PRO ? (unsigned)G_A_BYTES : (unsigned)S::STAGE_BYTES;
-            const int early = min(n_kb, STAGES_RT);
-            for (int i = 0; i < early; ++i) {
-                mbar_expect_tx(full_bar(i), stage_tx);
-                tma_load_2d(a_base + i * G_A_BYTES, &map_w, (kb_begin + i) * G_BK, m0, full_bar(i));
-            }
-            if (!PRO) {
-                grid_dependency_wait();
-                for (int i = 0; i < early; ++i)
-                    tma_load_2d(b_base + i * S::B_BYTES, &map_x, (kb_begin + i) * G_BK, n0, full_bar(i));
-            }
-            for (int i = early; i < n_kb; ++i) {
-                const int s = i % STAGES_RT;
-                const unsigned phase = (i / STAGES_RT) & 1;
-                if (!mbar_wait(empty_bar(s), phase ^ 1u, g.status, 1)) break;
-                mbar_expect_tx(full_bar(s), stage_tx);
-                const int k = (kb_begin + i) * G_BK;
-                tma_load_2d(a_base + s * G_A_BYTES, &map_w, k, m0, full_bar(s));
-                if (!PRO) tma_load_2d(b_base + s * S::B_BYTES, &map_x, k, n0, full_bar(s));
+            int it = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; t < n_tiles_total && alive; t += gridDim.x) {
+                const TileCoord c = tile_coord(g, t, BN);
+                int i = 0;
+                if (it == 0) {
+                    const int early = min(c.n_kb, S::STAGES);
+                    for (; i < early; ++i) {
+                        mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
+                        tma_load_2d(a_base + i * G_A_BYTES, &map_w, (c.kb_begin + i) * G_BK, c.m0, full_bar(i));
+                    }
+                    grid_dependency_wait();
+                    for (int e = 0; e < early; ++e)
+                        tma_load_2d(b_base + e * S::B_BYTES, &map_x, (c.kb_begin + e) * G_BK, c.n0, full_bar(e));
+                    it = early;
+                }
+                for (; i < c.n_kb; ++i, ++it) {
+                    const int s = it % S::STAGES;
+                    const unsigned phase = (it / S::STAGES) & 1;
+                    if (!mbar_wait(empty_bar(s), phase ^ 1u, g.status, 1)) { alive = false; break; }
+                    mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+                    const int k = (c.kb_begin + i) * G_BK;
+                    tma_load_2d(a_base + s * G_A_BYTES, &map_w, k, c.m0, full_bar(s));
+                    tma_load_2d(b_base + s * S::B_BYTES, &map_x, k, c.n0, full_bar(s));
+                }
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer: tile j accumulates in buffer j % 2 once the epilogue has emptied it
         if (lane == 0) {
             constexpr unsigned idesc = umma_idesc(BN);
+            int it = 0, j = 0;
             bool ok = true;
-            if (PRO) ok = mbar_wait(bready_bar, 0, g.status, 2);       // the block's own activation operand is written
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES_RT;
-                const unsigned phase = (i / STAGES_RT) & 1;
-                ok = mbar_wait(full_bar(s), phase, g.status, 2);
+            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
+                const TileCoord c = tile_coord(g, t, BN);
+                const int buf = j & 1;
+                ok = mbar_wait(acc_empty_bar(buf), (((unsigned)j >> 1) & 1u) ^ 1u, g.status, 2);
                 if (!ok) break;
-                if (stamps != nullptr && i == 0) stamps[2] = global_ns();                // first tiles have landed
                 tcgen05_fence_after();
-                const unsigned long long a_desc = umma_desc_sw128(a_base + s * G_A_BYTES);
-                const unsigned long long b_desc = umma_desc_sw128(b_base + (PRO ? (kb_begin + i) : s) * S::B_BYTES);
+                const unsigned d_tmem = tmem_base + (unsigned)(buf * S::ACC_COLS);
+                for (int i = 0; i < c.n_kb; ++i, ++it) {
+                    const int s = it % S::STAGES;
+                    const unsigned phase = (it / S::STAGES) & 1;
+                    ok = mbar_wait(full_bar(s), phase, g.status, 2);
+                    if (!ok) break;
+                    if (stamps != nullptr && it == 0) stamps[2] = global_ns();            // first tiles have landed
+                    tcgen05_fence_after();
+                    const unsigned long long a_desc = umma_desc_sw128(a_base + s * G_A_BYTES);
+                    const unsigned long long b_desc = umma_desc_sw128(b_base + s * S::B_BYTES);
 #pragma unroll
-                for (int k = 0; k < G_BK / 16; ++k) {
-                    // 16 elements = 32 bytes further along K inside the swizzle span: +2 in address/16 units
-                    tcgen05_mma_f16(tmem_acc, a_desc + 2ull * k, b_desc + 2ull * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < G_BK / 16; ++k) {
+                        // 16 elements = 32 bytes further along K inside the swizzle span: +2 in address/16 units
+                        tcgen05_mma_f16(d_tmem, a_desc + 2ull * k, b_desc + 2ull * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty_bar(s));      // the stage is free once these products have read it
                 }
-                tcgen05_commit(empty_bar(s));          // the stage is free once these products have read it
+                if (!ok) break;
+                if (stamps != nullptr && j == 0) stamps[3] = global_ns();                 // first tile's last product issued
+                tcgen05_commit(acc_full_bar(buf));     // arrives when every product issued so far is done
             }
-            if (stamps != nullptr) stamps[3] = global_ns();                              // last product issued
-            tcgen05_commit(accum_bar);                 // arrives when every product issued so far is done
         }
     } else {
-        // ---------------- epilogue: warp q reads tensor-memory lanes 32q .. 32q+31
+        // ---------------- epilogue: warp q of a group reads tensor-memory lanes 32q .. 32q+31; the groups share out
+        // the tile's tokens
         const int q = warp & 3;
+        const int eg = (warp - 2) >> 2;
+        const int et = threadIdx.x - 64;                               // 0 .. 128*EG-1
+        constexpr int COLS_PER_GROUP = BN / EG;
         grid_dependency_wait();                // positions, page lists and the output buffers may come from earlier kernels
-        if (PRO) {
-            // RMSNorm of the tile's tokens into the shared-memory operand: warp w takes rows w, w + 4, ...;
-            // a lane takes 16-byte chunks (8 elements) lane, lane + 32, ... of a row.  Layout of a K block's
-            // tile: row r at r * 128 bytes, its 16-byte chunk c at position c ^ (r % 8)  (128-byte swizzle).
-            const int chunks = g.K >> 3;
-            const int ew = warp - 2;
-            unsigned char* b_tiles = smem_generic + STAGES_RT * G_A_BYTES;
-            if (chunks <= 4 * 32) {
-                norm_rows_to_smem<4>(g.x_f32, g.gain, g.eps, g.K, g.k_blocks, n0, g.n_tok, ew, lane, BN, S::B_BYTES, b_tiles);
-            } else {
-                for (int r = ew; r < BN; r += 4) {
-                    const int tok = n0 + r;
-                    const bool live = tok < g.n_tok;
-                    const float* xr = g.x_f32 + (long long)tok * g.K;
-                    float ss = 0.0f;
-                    if (live) {
-#pragma unroll 4
-                        for (int ch = lane; ch < chunks; ch += 32) {
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch);
-                            const float4 b = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch + 1);
-                            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
-                        }
+        int j = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
+            const TileCoord c = tile_coord(g, t, BN);
+            const int m0 = c.m0, n0 = c.n0, split = c.split;
+            const int buf = j & 1;
+            if (EPI == EPI_QKV) {
+                for (int tt = et; tt < BN; tt += 128 * EG) {
+                    int p = 0;
+                    long long off = 0;
+                    if (n0 + tt < g.n_tok) {
+                        p = __ldg(g.positions + n0 + tt);
+                        if (g.kv_heads > 0) off = paged_offset(g.cache, __ldg(g.tok_seq + n0 + tt), p, 0);
                     }
-                    ss = warp_sum(ss);
-                    const float scale = 1.0f / sqrtf(ss / (float)g.K + g.eps);
-                    const int k_chunks = g.k_blocks * 8;                       // chunks including the zero tail of the last K block
-#pragma unroll 4
-                    for (int ch = lane; ch < k_chunks; ch += 32) {
-                        uint4 packed = make_uint4(0, 0, 0, 0);
-                        if (live && ch < chunks) {
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch);
-                            const float4 b = __ldcg(reinterpret_cast<const float4*>(xr) + 2 * ch + 1);
-                            packed = scale_pack8(a, b, scale, g.gain, ch);
-                        }
-                        const int kb = ch >> 3, c = ch & 7;
-                        *reinterpret_cast<uint4*>(b_tiles + kb * S::B_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) = packed;
-                    }
+                    tok_pos[tt] = p;
+                    tok_off[tt] = off;
                 }
+                asm volatile("bar.sync 1, %0;" ::"n"(128 * EG) : "memory");          // the epilogue warps only
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes become visible to the tensor cores
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bready_bar) : "memory");
-        }
-        if (EPI == EPI_QKV) {
-            for (int t = threadIdx.x - 64; t < BN; t += 128) {
-                int p = 0;
-                long long off = 0;
-                if (n0 + t < g.n_tok) {
-                    p = __ldg(g.positions + n0 + t);
-                    if (g.kv_heads > 0) off = paged_offset(g.cache, __ldg(g.tok_seq + n0 + t), p, 0);
-                }
-                tok_pos[t] = p;
-                tok_off[t] = off;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps only
-        }
-        const bool ok = mbar_wait(accum_bar, 0, g.status, 3);
-        tcgen05_fence_after();
-        if (stamps != nullptr && threadIdx.x == 64) stamps[4] = global_ns();             // accumulators complete
-        const int row = m0 + q * 32 + lane;
-        // SiLU epilogue through shared memory: bfloat16 output, a full 16-output group inside the matrix, aligned rows
-        const bool silu_staged = EPI == EPI_SILU_MUL && g.out_dtype == MLC_DTYPE_BF16 && ((g.n_out >> 1) & 7) == 0 &&
-                                 (m0 + q * 32 + 32 <= g.n_out) && ((((uintptr_t)g.out) & 15) == 0);
-        if (ok && n_kb > 0) {
+            ok = mbar_wait(acc_full_bar(buf), ((unsigned)j >> 1) & 1u, g.status, 3);
+            if (!ok) break;
+            tcgen05_fence_after();
+            if (stamps != nullptr && et == 0 && j == 0) stamps[4] = global_ns();         // first accumulator complete
+            const unsigned d_tmem = tmem_base + (unsigned)(buf * S::ACC_COLS);
+            const int row = m0 + q * 32 + lane;
+            // SiLU epilogue through shared memory: bfloat16 output, a full 16-output group inside the matrix, aligned rows
+            const bool silu_staged = EPI == EPI_SILU_MUL && g.out_dtype == MLC_DTYPE_BF16 && ((g.n_out >> 1) & 7) == 0 &&
+                                     (m0 + q * 32 + 32 <= g.n_out) && ((((uintptr_t)g.out) & 15) == 0);
+            bf16* stage = reinterpret_cast<bf16*>(smem_generic + staging_off) + (eg * 4 + q) * COLS_PER_GROUP * 16;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = eg * COLS_PER_GROUP; c0 < (eg + 1) * COLS_PER_GROUP; c0 += 16) {
                 float v[16];
-                tmem_load16(tmem_acc + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+                tmem_load16(d_tmem + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
                 if (EPI == EPI_ADD) {
                     if (row < g.n_out) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int tok = n0 + c0 + j;
-                            if (tok < g.n_tok) atomicAdd((float*)g.out + (long long)tok * g.n_out + row, v[j]);
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const int tok = n0 + c0 + jj;
+                            if (tok < g.n_tok) atomicAdd((float*)g.out + (long long)tok * g.n_out + row, v[jj]);
                         }
                     }
                 } else if (EPI == EPI_STORE) {
                     if (row < g.n_out) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int tok = n0 + c0 + j;
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const int tok = n0 + c0 + jj;
                             if (tok < g.n_tok) {
                                 const long long idx = (long long)split * g.split_stride + (long long)tok * g.n_out + row;
-                                if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, v[j]);
-                                else store_out<bf16>(g.out, idx, v[j]);
+                                if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, v[jj]);
+                                else store_out<bf16>(g.out, idx, v[jj]);
                             }
                         }
                     }
@@ -423,23 +356,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         // Two tokens per step so that every lane produces a value: the even lane of a pair takes
                         // token j (its own gate, the neighbour's up), the odd lane token j+1.  Results go to a
                         // per-warp staging tile [token][16 outputs] in shared memory and leave in 16-byte stores.
-                        bf16* stage = reinterpret_cast<bf16*>(smem_generic) + q * BN * 16;
+                        const int cl = c0 - eg * COLS_PER_GROUP;
 #pragma unroll
-                        for (int j = 0; j < 16; j += 2) {
-                            const float send = (lane & 1) ? v[j] : v[j + 1];
+                        for (int jj = 0; jj < 16; jj += 2) {
+                            const float send = (lane & 1) ? v[jj] : v[jj + 1];
                             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-                            const float gate = (lane & 1) ? recv : v[j];
-                            const float up = (lane & 1) ? v[j + 1] : recv;
-                            const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
-                            stage[(c0 + j + (lane & 1)) * 16 + (lane >> 1)] = __float2bfloat16_rn(act);
+                            const float gate = (lane & 1) ? recv : v[jj];
+                            const float up = (lane & 1) ? v[jj + 1] : recv;
+                            const float act = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                            stage[(cl + jj + (lane & 1)) * 16 + (lane >> 1)] = __float2bfloat16_rn(act);
                         }
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                            const int tok = n0 + c0 + j;
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const float other = __shfl_xor_sync(0xffffffffu, v[jj], 1);
+                            const int tok = n0 + c0 + jj;
                             if ((lane & 1) == 0 && row < g.n_out && tok < g.n_tok) {
-                                const float gate = v[j], up = other;
+                                const float gate = v[jj], up = other;
                                 const float act = gate * (1.0f / (1.0f + expf(-gate))) * up;
                                 const long long idx = (long long)tok * half_out + (row >> 1);
                                 if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, act);
@@ -466,54 +399,59 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     // rotation factors of the 16 tokens first (independent loads), then arithmetic and stores
                     float2 cs[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = c0 + j;
-                        cs[j] = make_float2(1.0f, 0.0f);
-                        if (rotate && row_ok && n0 + t < g.n_tok)
-                            cs[j] = __ldg(g.rope + (long long)min(tok_pos[t], g.rope_positions - 1) * half + i);
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const int tt = c0 + jj;
+                        cs[jj] = make_float2(1.0f, 0.0f);
+                        if (rotate && row_ok && n0 + tt < g.n_tok)
+                            cs[jj] = __ldg(g.rope + (long long)min(tok_pos[tt], g.rope_positions - 1) * half + i);
                     }
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = c0 + j;
-                        const float mine = v[j] + b;
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const int tt = c0 + jj;
+                        const float mine = v[jj] + b;
                         const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
                         // first half: x0·c − x1·s; second half: x0·s + x1·c, with (x0, x1) = (dim i, dim i + hd/2)
-                        const float y = second ? (other * cs[j].y + mine * cs[j].x) : (mine * cs[j].x - other * cs[j].y);
-                        if (!row_ok || n0 + t >= g.n_tok) continue;
+                        const float y = second ? (other * cs[jj].y + mine * cs[jj].x) : (mine * cs[jj].x - other * cs[jj].y);
+                        if (!row_ok || n0 + tt >= g.n_tok) continue;
                         if (is_q) {
-                            const long long idx = ((long long)(n0 + t) * g.q_heads + head) * hd + d;
+                            const long long idx = ((long long)(n0 + tt) * g.q_heads + head) * hd + d;
                             if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(g.out, idx, y);
                             else store_out<bf16>(g.out, idx, y);
                         } else {
                             void* pool = is_k ? g.cache.k_pool : g.cache.v_pool;
-                            const long long off = tok_off[t] + head_off;
+                            const long long off = tok_off[tt] + head_off;
                             if (g.out_dtype == MLC_DTYPE_F32) store_out<float>(pool, off, y);
                             else store_out<bf16>(pool, off, y);
                         }
                     }
                 }
             }
+            // the accumulator has been read: the tensor cores may fill it again
+            tcgen05_fence_before();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty_bar(buf)) : "memory");
             if (EPI == EPI_SILU_MUL && silu_staged) {
                 __syncwarp();
                 const int half_out = g.n_out >> 1;
-                const bf16* stage = reinterpret_cast<const bf16*>(smem_generic) + q * BN * 16;
-                for (int t = lane; t < BN; t += 32) {
-                    if (n0 + t < g.n_tok) {
-                        const uint4* src = reinterpret_cast<const uint4*>(stage + t * 16);
-                        uint4* dst = reinterpret_cast<uint4*>((bf16*)g.out + (long long)(n0 + t) * half_out + (m0 >> 1) + q * 16);
+                for (int tl = lane; tl < COLS_PER_GROUP; tl += 32) {
+                    const int tok = n0 + eg * COLS_PER_GROUP + tl;
+                    if (tok < g.n_tok) {
+                        const uint4* src = reinterpret_cast<const uint4*>(stage + tl * 16);
+                        uint4* dst = reinterpret_cast<uint4*>((bf16*)g.out + (long long)tok * half_out + (m0 >> 1) + q * 16);
                         dst[0] = src[0];
                         dst[1] = src[1];
                     }
                 }
+                __syncwarp();                  // the staging tile is free for the warp's next tile
             }
+            if (EPI == EPI_QKV) asm volatile("bar.sync 1, %0;" ::"n"(128 * EG) : "memory");   // before the next tile's positions
         }
+        if (stamps != nullptr && et == 0) stamps[5] = global_ns();                       // epilogues done
     }
 
-    if (stamps != nullptr && threadIdx.x == 64) stamps[5] = global_ns();                 // epilogue done
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((unsigned)S::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS) : "memory");
     }
 }
 
@@ -546,43 +484,31 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     return r == CUDA_SUCCESS ? 0 : MLC_ERR_BAD_SIZE;
 }
 
-constexpr int G_SMEM_MAX = 227 * 1024;
-
-template <int BN, int EPI, int PRO>
-static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs g, dim3 grid, cudaStream_t s) {
-    using S = GemmShape<BN>;
-    size_t smem = S::SMEM_BYTES;
-    if (PRO) {
-        // weights in as many stages as fit beside the resident activation operand
-        const size_t fixed = (size_t)g.k_blocks * S::B_BYTES + 1024 + 256 + S::META_BYTES;
-        int stages = S::STAGES;
-        while (stages > 2 && fixed + (size_t)stages * G_A_BYTES > (size_t)G_SMEM_MAX) --stages;
-        if (fixed + (size_t)stages * G_A_BYTES > (size_t)G_SMEM_MAX) return MLC_ERR_BAD_SIZE;
-        g.stages = stages;
-        smem = fixed + (size_t)stages * G_A_BYTES;
-    }
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int BN, int EPI>
+static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, int n_sms, cudaStream_t s) {
+    using S = GemmShape<BN, EPI>;
+    static_assert(S::SMEM_BYTES <= 227 * 1024, "shared memory of a block");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        configured = smem;
+        configured = true;
     }
-    cudaError_t e = launch_pdl(gemm_tcgen05_kernel<BN, EPI, PRO>, grid, dim3(G_THREADS), smem, s, mw, mx, g);
+    // persistent blocks: one per SM at most, each walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+    const long long tiles = (long long)g.m_tiles * g.n_tiles * g.n_splits;
+    const unsigned blocks = (unsigned)(tiles < n_sms ? tiles : n_sms);
+    cudaError_t e = launch_pdl(gemm_tcgen05_kernel<BN, EPI>, dim3(blocks), dim3(S::THREADS), (size_t)S::SMEM_BYTES, s, mw, mx, g);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
 template <int EPI>
-static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t s) {
-    if (g.x_f32 != nullptr) {
-        if (bn != 16) return MLC_ERR_BAD_SIZE;              // the NORM prologue is for decode steps of up to 16 tokens
-        return launch_gemm<16, EPI, 1>(mw, mx, g, grid, s);
-    }
+static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, int n_sms, cudaStream_t s) {
     switch (bn) {
-        case 16: return launch_gemm<16, EPI, 0>(mw, mx, g, grid, s);
-        case 32: return launch_gemm<32, EPI, 0>(mw, mx, g, grid, s);
-        case 64: return launch_gemm<64, EPI, 0>(mw, mx, g, grid, s);
-        case 128: return launch_gemm<128, EPI, 0>(mw, mx, g, grid, s);
-        case 256: return launch_gemm<256, EPI, 0>(mw, mx, g, grid, s);
+        case 16: return launch_gemm<16, EPI>(mw, mx, g, n_sms, s);
+        case 32: return launch_gemm<32, EPI>(mw, mx, g, n_sms, s);
+        case 64: return launch_gemm<64, EPI>(mw, mx, g, n_sms, s);
+        case 128: return launch_gemm<128, EPI>(mw, mx, g, n_sms, s);
+        case 256: return launch_gemm<256, EPI>(mw, mx, g, n_sms, s);
     }
     return MLC_ERR_BAD_SIZE;
 }
@@ -591,27 +517,27 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 
 using namespace mlc;
 
-// x: bfloat16 [n_tok][K], or, with norm_gain given, the float32 residual stream [n_tok][K] that the kernel
-// normalises itself (eps, norm_gain [K]; block_tokens must be 16); w: bfloat16 [n_out][K] (K a multiple of 8,
-// both 16-byte aligned).  epilogue 3 adds into out (float32 [n_tok][n_out]) atomically, any n_splits.
+// x: bfloat16 [n_tok][K]; w: bfloat16 [n_out][K] (K a multiple of 8, both 16-byte aligned).
 // epilogue 0: out [n_splits][n_tok][n_out] (float32 or bfloat16): with n_splits > 1 the K range is shared out over
 // blocks and each leaves its partial sums in its own slice for the consumer to add; 1: out [n_tok][n_out/2],
 // n_splits must be 1;
-// 2: out = q [n_tok][q_heads*hd], k and v go to the cache, n_splits must be 1.
+// 2: out = q [n_tok][q_heads*hd], k and v go to the cache, n_splits must be 1; 3: adds into out (float32
+// [n_tok][n_out]) atomically, any n_splits.
 // block_tokens: 16, 32, 64, 128 or 256.  status: one int on the device, 0 before the call; a bounded
-// wait that ran out leaves 1 (loader), 2 (tensor cores) or 3 (epilogue) there.
+// wait that ran out leaves 1 (loader), 2 (tensor cores) or 3 (epilogue) there.  timing: null, or
+// [blocks][8] uint64 that receive nanosecond stamps of each block's phases.  n_sms: blocks to launch at most.
 extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out_dtype, int n_tok, int n_out, int K,
-                                int block_tokens, int n_splits, int epilogue, int* status, unsigned long long* timing, const float* norm_gain,
-                                float norm_eps, const float* bias,
-                                const int* positions, const int* tok_seq, const void* rope_table, int rope_positions,
-                                int q_heads, int kv_heads, int hd, void* k_pool, void* v_pool, const int* page_table,
-                                long long entry_offset, int pages_per_seq, int page_size, void* stream) {
+                                int block_tokens, int n_splits, int epilogue, int* status, unsigned long long* timing,
+                                int n_sms, const float* bias, const int* positions, const int* tok_seq,
+                                const void* rope_table, int rope_positions, int q_heads, int kv_heads, int hd,
+                                void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
+                                int pages_per_seq, int page_size, void* stream) {
     if (n_tok <= 0 || n_out <= 0) return 0;
     if (K <= 0 || (K & 7) || (((uintptr_t)x | (uintptr_t)w) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
     if (n_splits < 1 || (epilogue != EPI_STORE && epilogue != EPI_ADD && n_splits != 1) || status == nullptr) return MLC_ERR_BAD_SIZE;
     if (epilogue == EPI_ADD && out_dtype != MLC_DTYPE_F32) return MLC_ERR_BAD_DTYPE;
-    if (norm_gain != nullptr && (n_splits != 1 || block_tokens != 16 || (((uintptr_t)norm_gain) & 15))) return MLC_ERR_BAD_SIZE;
+    if (n_sms < 1) return MLC_ERR_BAD_SIZE;
     GemmArgs g{};
     g.out = out;
     g.out_dtype = out_dtype;
@@ -622,14 +548,10 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     if ((long long)(n_splits - 1) * g.k_blocks_per_split >= g.k_blocks) return MLC_ERR_BAD_SIZE;   // an empty split
     g.split_stride = (long long)n_tok * n_out;
     g.status = status;
-    g.K = K;
-    g.stages = 0;
     g.timing = timing;
-    if (norm_gain != nullptr) {
-        g.x_f32 = (const float*)x;
-        g.gain = norm_gain;
-        g.eps = norm_eps;
-    }
+    g.m_tiles = (n_out + G_BM - 1) / G_BM;
+    g.n_tiles = (n_tok + block_tokens - 1) / block_tokens;
+    g.n_splits = n_splits;
     if (epilogue == EPI_SILU_MUL && (n_out & 1)) return MLC_ERR_BAD_SIZE;
     if (epilogue == EPI_QKV) {
         if (hd <= 0 || (hd & 1) || n_out != (q_heads + 2 * kv_heads) * hd || positions == nullptr) return MLC_ERR_BAD_SIZE;
@@ -647,18 +569,12 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, n_out, K, G_BM);
     if (rc) return rc;
-    if (norm_gain == nullptr) {
-        rc = make_map(&mx, x, n_tok, K, block_tokens);
-        if (rc) return rc;
-    } else {
-        mx = mw;                                            // unused by the kernel in this mode
-    }
-    dim3 grid((n_out + G_BM - 1) / G_BM, (n_tok + block_tokens - 1) / block_tokens, n_splits);
-    if (grid.y > 65535 || grid.z > 65535) return MLC_ERR_BAD_SIZE;
+    rc = make_map(&mx, x, n_tok, K, block_tokens);
+    if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (epilogue == EPI_STORE) return dispatch_bn<EPI_STORE>(block_tokens, mw, mx, g, grid, s);
-    if (epilogue == EPI_SILU_MUL) return dispatch_bn<EPI_SILU_MUL>(block_tokens, mw, mx, g, grid, s);
-    if (epilogue == EPI_QKV) return dispatch_bn<EPI_QKV>(block_tokens, mw, mx, g, grid, s);
-    if (epilogue == EPI_ADD) return dispatch_bn<EPI_ADD>(block_tokens, mw, mx, g, grid, s);
+    if (epilogue == EPI_STORE) return dispatch_bn<EPI_STORE>(block_tokens, mw, mx, g, n_sms, s);
+    if (epilogue == EPI_SILU_MUL) return dispatch_bn<EPI_SILU_MUL>(block_tokens, mw, mx, g, n_sms, s);
+    if (epilogue == EPI_QKV) return dispatch_bn<EPI_QKV>(block_tokens, mw, mx, g, n_sms, s);
+    if (epilogue == EPI_ADD) return dispatch_bn<EPI_ADD>(block_tokens, mw, mx, g, n_sms, s);
     return MLC_ERR_UNSUPPORTED;
 }

@@ -94,7 +94,7 @@ def core() -> ctypes.CDLL:
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
-            "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, P, F, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
+            "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
@@ -403,6 +403,16 @@ def check_gemm_status(device: torch.device) -> None:
             raise KernelError(f"a tcgen05 matrix product gave up waiting on a barrier ({who}); its output is not valid")
 
 
+_sm_counts = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_counts[key]
+
+
 def gemm_block_tokens(n_tok: int, row_tiles: int, n_sms: int) -> int:
     for bn in (16, 32, 64, 128):
         if n_tok <= bn:
@@ -414,21 +424,15 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
                  block_tokens: Optional[int] = None, bias: Optional[torch.Tensor] = None,
                  positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
                  rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
-                 kv: Optional[KVView] = None, n_sms: int = 148, norm_gain: Optional[torch.Tensor] = None,
-                 norm_eps: float = 0.0, timing: Optional[torch.Tensor] = None) -> None:
+                 kv: Optional[KVView] = None, n_sms: int = 0, timing: Optional[torch.Tensor] = None) -> None:
     """bfloat16 x [n, K] times bfloat16 w [rows, K] transposed on the tcgen05 tensor cores, with
-    the epilogue done before anything is stored (see csrc/gemm_tcgen05.cu).  With `norm_gain`, x is
-    the float32 residual stream [n <= 16, K] and the kernel applies RMSNorm(eps, gain) to it itself.
-    Epilogue EPI_ADD adds the product into `out` (float32 [n, rows]) with atomic adds."""
-    require_cuda(x, w, out, bias, positions, tok_seq, rope, norm_gain)
-    if norm_gain is not None:
-        if x.dtype != torch.float32 or norm_gain.dtype != torch.float32 or x.shape[0] > 16:
-            raise KernelError("the fused norm takes the float32 stream of at most 16 tokens and a float32 gain")
-        block_tokens = 16
-    elif x.dtype != torch.bfloat16:
+    the epilogue done before anything is stored (see csrc/gemm_tcgen05.cu).  Epilogue EPI_ADD adds the
+    product into `out` (float32 [n, rows]) with atomic adds.  `n_sms` bounds the number of (persistent) blocks."""
+    require_cuda(x, w, out, bias, positions, tok_seq, rope)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("the tcgen05 matrix product takes bfloat16 operands")
-    if w.dtype != torch.bfloat16:
-        raise KernelError("the tcgen05 matrix product takes bfloat16 operands")
+    if n_sms <= 0:
+        n_sms = _sm_count(x.device)
     n_tok, K = x.shape
     n_out = w.shape[0]
     if w.shape[1] != K:
@@ -453,8 +457,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
         cache = (None, None, None, 0, 0, 1)
     status = gemm_status(x.device)
     _check(core().mlc_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
-                                   block_tokens, n_splits, epilogue, status.data_ptr(), _ptr(timing), _ptr(norm_gain),
-                                   float(norm_eps),
+                                   block_tokens, n_splits, epilogue, status.data_ptr(), _ptr(timing), n_sms,
                                    _ptr(bias), _ptr(positions),
                                    _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
                                    kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product")

@@ -95,9 +95,6 @@ def bench_gemm(args) -> None:
     flops = 2.0 * T * N * K
     epi = {"store": 0, "silu": 1, "qkv": 2, "add": 3}[args.epilogue]
     norm = {}
-    if args.norm:
-        x = torch.randn(T, K, device=DEV)
-        norm = dict(norm_gain=torch.ones(K, device=DEV), norm_eps=1e-6)
     if args.library:
         out = torch.empty(T, N, dtype=torch.float32, device=DEV)
         report(f"library product T={T} N={N} K={K}", lambda i: torch.mm(x, ws[i % C].t(), out_dtype=torch.float32, out=out),
@@ -132,7 +129,7 @@ def bench_gemm(args) -> None:
         fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 2, 1, args.block_tokens, bias=bias, positions=positions,
                                             tok_seq=tok_seq, rope=rope, q_heads=H, kv_heads=KV, head_dim=hd, kv=kv, **norm)
         nbytes += T * N * 2
-    report(f"tcgen05 product T={T} N={N} K={K} epilogue={args.epilogue} splits={args.splits} norm={bool(args.norm)}", fn, args, nbytes, flops)
+    report(f"tcgen05 product T={T} N={N} K={K} epilogue={args.epilogue} splits={args.splits}", fn, args, nbytes, flops)
 
 
 def bench_norm(args) -> None:
@@ -181,7 +178,6 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", type=int, default=9728)
     ap.add_argument("--k", type=int, default=896)
     ap.add_argument("--epilogue", default="store", choices=["store", "silu", "qkv", "add"])
-    ap.add_argument("--norm", action="store_true", help="RMSNorm of a float32 input inside the product's prologue")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--slices", type=int, default=0)
     ap.add_argument("--block-tokens", type=int, default=None)

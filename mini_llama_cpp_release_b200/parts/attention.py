@@ -24,11 +24,6 @@ from .base import CacheNeed, MixerMemory, Part, TensorSpec
 from .linear import Linear
 
 
-# The projection kernel can apply the preceding RMSNorm itself (csrc/gemm_tcgen05.cu, NORM prologue).  Measured on
-# a B200 the separate norm kernel is the faster pair today (the prologue is repeated in every block), so it is off.
-FUSE_NORM_PROLOGUE = False
-
-
 @register_part("mixer", "gqa_attention")
 class GQAttention(Part):
     graph_safe = True
@@ -111,21 +106,7 @@ class GQAttention(Part):
     # ---- the step
     accumulates = True        # forward(..., residual=x) may add the branch into the float32 stream and return None
 
-    def can_fuse_norm(self, step, norm) -> bool:
-        """Whether `forward_fused` applies: a decode step of up to 16 tokens on the tcgen05 path, behind an
-        RMSNorm whose gain and eps the projection kernel can apply itself."""
-        return (FUSE_NORM_PROLOGUE and self.fused and step.n_tokens <= 16 and hasattr(norm, "gain") and hasattr(norm, "eps")
-                and self.hidden * 2 * 16 + 64 * 1024 <= 200 * 1024 and self.o.can_add_into_stream(step.n_tokens))
-
-    def forward_fused(self, x: torch.Tensor, norm, step, memory: MixerMemory) -> None:
-        """x += attention(norm(x)): the norm rides in the Q/K/V product's prologue, the residual addition in the
-        output projection's epilogue."""
-        self._project_and_attend(x, step, memory, norm=norm, residual=x)
-
     def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
-        return self._project_and_attend(h, step, memory, norm=None, residual=residual)
-
-    def _project_and_attend(self, h, step, memory, norm, residual):
         rt = self.runtime
         n = h.shape[0]
         self.position.prepare(step.max_kv_len)
@@ -143,9 +124,7 @@ class GQAttention(Part):
             kernels.gemm_tcgen05(h, proj.weight, q, kernels.bindings.EPI_QKV, bias=bias, positions=step.positions,
                                  tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
                                  kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms,
-                                 block_tokens=16 if n <= 64 else None,     # short epilogues in more blocks beat one long one
-                                 norm_gain=norm.gain if norm is not None else None,
-                                 norm_eps=norm.eps if norm is not None else 0.0)
+                                 block_tokens=16 if n <= 64 else None)     # short epilogues in more blocks beat one long one
         else:
             kernels.qkv_post(proj(h, torch.float32), bias, step.positions, step.tok_seq, table, self.H, kv_heads,
                              self.hd, q, memory.kv if memory.writes_cache else None)

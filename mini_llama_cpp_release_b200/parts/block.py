@@ -3,9 +3,8 @@
 Pre-norm: x ← x + mixer(norm(x)); x ← x + feed_forward(norm(x)) (src/forward.cpp:726-780).
 The additions are deferred: a branch's output travels as `pending` and is added, in
 float32, by the next norm's kernel — the block's own second norm, the next block's first
-norm, or the model's final norm.  On the tensor-core path of small steps the parts go further: the
-norm moves into the following product's prologue and the addition into the preceding product's
-epilogue, and nothing is pending at all."""
+norm, or the model's final norm.  On the tensor-core path of small steps the addition moves into
+the preceding product's epilogue (atomic adds into the stream) and nothing is pending at all."""
 from __future__ import annotations
 
 from typing import Optional, Tuple
@@ -35,21 +34,11 @@ class PreNormBlock(Part):
 
     def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], step, memory: MixerMemory
                 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-        """A part may (a) fuse the norm before it and the residual addition after it into its own kernels
-        (`can_fuse_norm` / `forward_fused`: it then works on the stream x in place), (b) add its output into x
-        itself (`accumulates`, asked through `residual=x`), or (c) return its output, which then waits in
-        `pending` for the next norm to add it."""
+        """A part either adds its output into the stream x itself (`accumulates`, asked through `residual=x`;
+        it then returns None) or returns its output, which waits in `pending` for the next norm to add it."""
         mixer, ffn = self.mixer, self.feed_forward
-        if pending is None and hasattr(mixer, "can_fuse_norm") and mixer.can_fuse_norm(step, self.mixer_norm):
-            mixer.forward_fused(x, self.mixer_norm, step, memory)
-            a = None
-        else:
-            h = self.mixer_norm.forward(x, pending)
-            a = mixer.forward(h, step, memory, residual=x) if getattr(mixer, "accumulates", False) else mixer.forward(h, step, memory)
-        if a is None and hasattr(ffn, "can_fuse_norm") and ffn.can_fuse_norm(step, self.feed_forward_norm):
-            ffn.forward_fused(x, self.feed_forward_norm, step)
-            f = None
-        else:
-            h2 = self.feed_forward_norm.forward(x, a)
-            f = ffn.forward(h2, step, residual=x) if getattr(ffn, "accumulates", False) else ffn.forward(h2, step)
+        h = self.mixer_norm.forward(x, pending)
+        a = mixer.forward(h, step, memory, residual=x) if getattr(mixer, "accumulates", False) else mixer.forward(h, step, memory)
+        h2 = self.feed_forward_norm.forward(x, a)
+        f = ffn.forward(h2, step, residual=x) if getattr(ffn, "accumulates", False) else ffn.forward(h2, step)
         return x, f

@@ -11,8 +11,6 @@ from .base import Part, TensorSpec
 from .linear import Linear
 
 
-FUSED_MAX_ROWS = 64
-from .attention import FUSE_NORM_PROLOGUE  # noqa: E402  (one switch for both parts)
 
 
 @register_part("feed_forward", "swiglu")
@@ -46,9 +44,6 @@ class SwiGLU(Part):
         else:
             w = torch.cat([gate, up], dim=0)
         self.gate_up = Linear(w, runtime)
-        # Above this many rows the plain product followed by the activation kernel is still the faster
-        # pair: the fused epilogue stores two bytes per lane and does not overlap with the next tile.
-        self.fused_max_rows = FUSED_MAX_ROWS
         self.down = Linear(get(n + "down_proj.weight"), runtime)
 
     def weight_bytes(self) -> int:
@@ -56,23 +51,10 @@ class SwiGLU(Part):
 
     accumulates = True        # forward(..., residual=x) may add the branch into the float32 stream and return None
 
-    def can_fuse_norm(self, step, norm) -> bool:
-        return (FUSE_NORM_PROLOGUE and self.fused and step.n_tokens <= 16 and hasattr(norm, "gain") and hasattr(norm, "eps")
-                and self.hidden * 2 * 16 + 64 * 1024 <= 200 * 1024 and self.down.can_add_into_stream(step.n_tokens))
-
-    def forward_fused(self, x: torch.Tensor, norm, step=None) -> None:
-        """x += feed_forward(norm(x)): the norm in the gate/up product's prologue, SiLU·mul in its epilogue, the
-        residual addition in the down product's epilogue."""
-        rt = self.runtime
-        a = rt.empty(x.shape[0], self.inter)
-        kernels.gemm_tcgen05(x, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms,
-                             norm_gain=norm.gain, norm_eps=norm.eps)
-        self.down.add_into(a, x)
-
     def forward(self, h: torch.Tensor, step=None, residual=None):
         rt = self.runtime
         a = rt.empty(h.shape[0], self.inter)
-        if self.fused and h.shape[0] <= self.fused_max_rows:
+        if self.fused:
             kernels.gemm_tcgen05(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
         else:
             kernels.silu_mul(self.gate_up(h, rt.dtype), a, interleaved=self.fused)

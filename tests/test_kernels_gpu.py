@@ -238,7 +238,8 @@ def test_float32_linear_takes_any_size_and_gives_each_row_the_same_sum(M, N, K, 
 
 @pytest.mark.parametrize("T,N,K,bn,splits", [(16, 128, 64, 16, 1), (1, 1000, 344, None, 1), (8, 896, 4864, 16, 19),
                                               (64, 1152, 896, 64, 1), (200, 300, 72, None, 1), (33, 130, 176, 64, 2),
-                                              (600, 264, 128, 256, 1), (300, 777, 200, 128, 1)])
+                                              (600, 264, 128, 256, 1), (300, 777, 200, 128, 1), (700, 40000, 72, 64, 1),
+                                              (40, 30000, 136, 16, 2)])
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 def test_tcgen05_product_plain_store(T, N, K, bn, splits, out_dtype):
     g = torch.Generator().manual_seed(T + N)
@@ -297,23 +298,6 @@ def test_tcgen05_product_with_qkv_epilogue(H, KV, hd, T):
     close(k_got, k_want, 8e-3)
     close(v_got, v_want, 8e-3)
     assert torch.isnan(kv.k_pool[0].float()).all()
-
-
-@pytest.mark.parametrize("T,N,K", [(1, 256, 64), (8, 1152, 896), (16, 300, 344), (5, 128, 1000)])
-def test_tcgen05_product_with_norm_prologue(T, N, K):
-    """The kernel normalises the float32 stream itself and writes its own swizzled operand."""
-    g = torch.Generator().manual_seed(T * N)
-    x = torch.randn(T, K, generator=g) * 2
-    gain = 1 + 0.2 * torch.randn(K, generator=g)
-    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
-    out = torch.full((1, T, N), float("nan"), device=DEV)
-    kernels.gemm_tcgen05(x.to(DEV), w.to(DEV), out, 0, norm_gain=gain.to(DEV), norm_eps=1e-5)
-    kernels.check_gemm_status(DEV)
-    h = plain_impl.rmsnorm(x, gain, 1e-5).to(torch.bfloat16).float()
-    close(out[0], h.double() @ w.double().t(), 2e-3)             # bfloat16 rounding of h may differ in the last bit
-    with pytest.raises(kernels.KernelError, match="16 tokens"):
-        kernels.gemm_tcgen05(torch.zeros(17, K, device=DEV), w.to(DEV), torch.empty(1, 17, N, device=DEV), 0,
-                             norm_gain=gain.to(DEV), norm_eps=1e-5)
 
 
 @pytest.mark.parametrize("T,N,K,splits", [(8, 896, 4864, 19), (64, 896, 896, 7), (3, 200, 128, 1), (16, 130, 1000, 4)])
