@@ -38,6 +38,7 @@ class Context:
         self.max_position = model.config.max_position_embeddings
         self.token_history: Dict[int, List[int]] = {}
         self.n_steps = 0
+        self._pinned: Optional[torch.Tensor] = None            # host staging buffer of `describe`
         # decoding through captured graphs needs every part to be free of host round trips
         self.use_graphs = all(getattr(p, "graph_safe", False) for p in model.graph_relevant_parts())
         self._runners: Dict[tuple, DecodeRunner] = {}
@@ -102,16 +103,26 @@ class Context:
                 flat.extend(pl)
                 flat.extend([-1] * (width - len(pl)))
             tables.append(flat)
-        # one host buffer, one copy
+        # one host buffer (pinned once and reused; an event says when the last copy out of it is done), one copy
         segments = [tokens, positions, tok_seq, cu, start_pos, slots, want_rows, *tables]
         offsets = []
-        flat_all: List[int] = []
-        for seg in segments:
-            offsets.append(len(flat_all))
-            flat_all.extend(seg)
-            flat_all.extend([0] * ((-len(flat_all)) % 4))        # keep every segment 16-byte aligned
-        host = torch.tensor(flat_all, dtype=torch.int32).pin_memory()
-        dev = host.to(self.model.runtime.device, non_blocking=True)
+        total = 0
+        for seg_list in segments:
+            offsets.append(total)
+            total += (len(seg_list) + 3) // 4 * 4                # keep every segment 16-byte aligned
+        if getattr(self, "_pinned", None) is None or self._pinned.numel() < total:
+            self._pinned = torch.empty(max(total, 4096) * 2, dtype=torch.int32).pin_memory()
+            self._pinned_np = self._pinned.numpy()
+            self._pinned_event = None
+        if self._pinned_event is not None:
+            self._pinned_event.synchronize()
+        host_np = self._pinned_np
+        for off, seg_list in zip(offsets, segments):
+            host_np[off:off + len(seg_list)] = seg_list
+        dev = torch.empty(total, dtype=torch.int32, device=self.model.runtime.device)
+        dev.copy_(self._pinned[:total], non_blocking=True)
+        self._pinned_event = torch.cuda.Event()
+        self._pinned_event.record()
 
         def seg(i: int, n: int) -> torch.Tensor:
             return dev[offsets[i]: offsets[i] + n]
