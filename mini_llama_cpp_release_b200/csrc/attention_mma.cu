@@ -174,6 +174,8 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     const int warp_hi = start + tok0 + warp_t_last;
     const int warp_lo = (a.window > 0) ? max(0, start + tok0 + warp_t_first - a.window + 1) : 0;
     const bool warp_has_rows = warp_t_first < n_tok;
+    const int warp_first_pos = start + tok0 + warp_t_first;                       // keys up to here are visible to every row of the warp
+    const int warp_lo_last = (a.window > 0) ? max(0, warp_hi - a.window + 1) : 0;   // keys from here on are inside every row's window
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
     float o[NT_O][4];
@@ -227,18 +229,28 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
                     mma_bf16(s[2 * jp + 1], af, bfr[2], bfr[3]);
                 }
             }
-            // scale, mask, running maximum
+            // mask (only where the tile meets the diagonal, a window's edge or the sequence's end), running maximum.
+            // Scores stay unscaled; the scale rides in the exponent's multiply-add.
             float mx[2] = {-INFINITY, -INFINITY};
+            const bool interior = key0 + KEYS_W - 1 <= warp_first_pos && key0 >= warp_lo_last;   // the same for the whole warp
+            if (interior) {
 #pragma unroll
-            for (int j = 0; j < NT_S; ++j) {
+                for (int j = 0; j < NT_S; ++j) {
+                    mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+                    mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
+                }
+            } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int kpos = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
-                    const int rr = e >> 1;
-                    const bool in_range = kpos >= row_lo[rr] && kpos <= row_hi[rr];
-                    const float v = in_range ? s[j][e] * a.scale_log2 : -INFINITY;
-                    s[j][e] = v;
-                    mx[rr] = fmaxf(mx[rr], v);
+                for (int j = 0; j < NT_S; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int kpos = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
+                        const int rr = e >> 1;
+                        const bool in_range = kpos >= row_lo[rr] && kpos <= row_hi[rr];
+                        const float v = in_range ? s[j][e] : -INFINITY;
+                        s[j][e] = v;
+                        mx[rr] = fmaxf(mx[rr], v);
+                    }
                 }
             }
             float corr[2];
@@ -246,18 +258,18 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
             for (int rr = 0; rr < 2; ++rr) {
                 mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
                 mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
-                const float m_new = fmaxf(m[rr], mx[rr]);
+                const float m_new = fmaxf(m[rr], mx[rr] * a.scale_log2);     // the scale is positive: it commutes with max
                 const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
                 corr[rr] = exp2f(m[rr] - m_use);             // 0 when nothing was seen before
                 m[rr] = m_new;
-                mx[rr] = m_use;
+                mx[rr] = -m_use;
             }
             float ls[2] = {0.0f, 0.0f};
 #pragma unroll
             for (int j = 0; j < NT_S; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p = exp2f(s[j][e] - mx[e >> 1]);
+                    const float p = exp2f(fmaf(s[j][e], a.scale_log2, mx[e >> 1]));
                     s[j][e] = p;
                     ls[e >> 1] += p;
                 }
@@ -701,6 +713,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     if (hd != HD || page_size != TILE) return MLC_ERR_BAD_SIZE;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
     if (row_tiles != 1 && row_tiles != 2 && row_tiles != 4) return MLC_ERR_BAD_SIZE;
+    if (!(scale > 0.0f)) return MLC_ERR_BAD_SIZE;                     // the kernels move the scale past a maximum
     if (n_splits < 1 || (n_splits > 1 && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
     MmaArgs a;
     a.q = (const bf16*)q;
