@@ -1,0 +1,420 @@
+// Prompt attention on the fifth-generation tensor cores: softmax(q·kᵀ·scale)·v of many tokens over
+// a paged bfloat16 cache (src/ops.cpp:143-196 gives the arithmetic), scores and outputs accumulated in
+// tensor memory, operands staged in shared memory by TMA.
+//
+// A block owns 128 rows of one key/value head: the group's query heads of 128 / group successive
+// tokens (one row per token and head, so keys are read once for the whole group), and walks the
+// keys the rows may see in tiles of 64, which is one page of the cache.  Roles:
+//     warp 0     one thread issues the TMA loads: the query rows once, then a ring of K and V pages;
+//     warp 1     allocates tensor memory; one thread issues tcgen05.mma: S_j = Q·K_jᵀ into one of two
+//                score buffers, and O += P_j·V_j (V is the MN-major operand, read as the cache holds it);
+//     warps 2-5  one thread per row: reads the row's 64 scores from tensor memory, masks where the tile
+//                meets the diagonal, a window's edge or padding rows, keeps the running maximum and sum
+//                in float32, writes P_j = exp2(s·scale·log2e − m) as bfloat16 into shared memory for the
+//                tensor cores.  The output accumulates in tensor memory; when a row's maximum rises by more than
+//                2^8 the row's thread rescales its lane of the output there before O_j is added.
+// The tensor cores compute S_{j+1} and O_j while the rows work on tile j.  With a head size of 64 two
+// blocks share an SM, so one block's exponentials overlap the other's products.
+//
+// Pages are handed out dirty.  Keys beyond a row's range give scores that are replaced, not multiplied; values
+// beyond the sequence's last key would meet probabilities of exactly zero, but 0 x NaN is NaN, so the rows of
+// the last page's V tile that lie beyond the sequence are zeroed in shared memory before the product reads them.
+//
+// Every wait on an mbarrier is bounded by a clock; a wait that runs out records a code in `status`
+// (11 loader, 12 tensor cores, 13 softmax rows), the block skips its stores, frees its tensor memory
+// and returns.
+#include "tcgen05.cuh"
+
+#ifndef MLC_HEAD_DIM
+#define MLC_HEAD_DIM 64
+#endif
+
+#if MLC_HEAD_DIM == 64 || MLC_HEAD_DIM == 128
+#define MLC_ATTENTION_TCGEN05 1
+#else
+#define MLC_ATTENTION_TCGEN05 0
+#endif
+
+namespace mlc {
+
+struct TcAttnArgs {
+    void* out;                  // bfloat16 [tokens][q_heads*hd]
+    const int* cu_seqlens;      // [n_seqs + 1] first token of each sequence in the step
+    const int* start_pos;       // [n_seqs] position of each sequence's first token of the step
+    const int* page_table;      // [n_seqs][pages_per_seq]
+    int pages_per_seq;
+    int q_heads, kv_heads, group;
+    int heads_per_block, tokens_per_block, head_chunks;
+    int window;
+    float scale_log2;
+    int* status;
+};
+
+#if MLC_ATTENTION_TCGEN05
+
+constexpr int A_HD = MLC_HEAD_DIM;
+constexpr int A_BM = 128;                              // rows of a block
+constexpr int A_BN = 64;                               // keys of a tile: one page
+constexpr int A_KB = A_HD / 64;                        // 64-element spans of the head size
+constexpr int A_STAGES = 3;
+constexpr int A_Q_BYTES = A_KB * A_BM * 128;
+constexpr int A_TILE_BYTES = A_KB * A_BN * 128;        // one K or V page of one head
+constexpr int A_P_BYTES = A_BM * 128;
+constexpr int A_BAR_BYTES = 256;
+constexpr int A_SMEM_BYTES = A_Q_BYTES + 2 * A_STAGES * A_TILE_BYTES + 2 * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
+constexpr int A_TMEM_COLS = 256;                       // two score buffers of 64 columns, the output's A_HD
+static_assert(2 * A_BN + A_HD <= A_TMEM_COLS, "tensor memory of a block");
+constexpr int A_BLOCKS_PER_SM = (A_HD == 64) ? 2 : 1;
+static_assert(A_SMEM_BYTES * A_BLOCKS_PER_SM <= 226 * 1024, "shared memory of the blocks of one SM");
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(192, A_BLOCKS_PER_SM)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, TcAttnArgs a) {
+    // ---- which rows: heavy blocks (late tokens see the most keys) first
+    const int b = blockIdx.z;
+    const int kvh = blockIdx.y / a.head_chunks, chunk = blockIdx.y % a.head_chunks;
+    const int tok0 = (gridDim.x - 1 - blockIdx.x) * a.tokens_per_block;
+
+    extern __shared__ unsigned char smem_dyn[];
+    const unsigned base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char* smem_generic = smem_dyn + (base - smem_u32(smem_dyn));
+    const unsigned q_base = base;
+    const unsigned k_base = q_base + A_Q_BYTES;
+    const unsigned v_base = k_base + A_STAGES * A_TILE_BYTES;
+    const unsigned p_base = v_base + A_STAGES * A_TILE_BYTES;
+    constexpr unsigned v_off = A_Q_BYTES + A_STAGES * A_TILE_BYTES;
+    constexpr unsigned p_off = A_Q_BYTES + 2 * A_STAGES * A_TILE_BYTES;
+    const unsigned bar_base = p_base + 2 * A_P_BYTES;
+    constexpr unsigned bar_off = p_off + 2 * A_P_BYTES;
+    auto k_full = [&](int s) { return bar_base + 8u * s; };
+    auto v_full = [&](int s) { return bar_base + 8u * (4 + s); };
+    auto kv_empty = [&](int s) { return bar_base + 8u * (8 + s); };
+    auto s_full = [&](int i) { return bar_base + 8u * (12 + i); };
+    auto s_empty = [&](int i) { return bar_base + 8u * (14 + i); };
+    auto p_full = [&](int i) { return bar_base + 8u * (16 + i); };
+    auto p_empty = [&](int i) { return bar_base + 8u * (18 + i); };
+    const unsigned o_full = bar_base + 8u * 20;
+    const unsigned q_full = bar_base + 8u * 24;
+    const unsigned tmem_slot = bar_base + 8u * 25;
+    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 25);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < A_STAGES; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full(i), 1);
+            mbar_init(s_empty(i), 128);
+            mbar_init(p_full(i), 128);
+            mbar_init(p_empty(i), 1);
+        }
+        mbar_init(q_full, 1);
+        mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((unsigned)A_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const unsigned tmem_base = *tmem_slot_ptr;
+    grid_launch_dependents();
+    grid_dependency_wait();                    // the queries and the step's keys come from the kernel before
+
+    const int seq_tok0 = a.cu_seqlens[b];
+    const int q_len = a.cu_seqlens[b + 1] - seq_tok0;
+    const int n_tok = min(a.tokens_per_block, q_len - tok0);          // <= 0: nothing to do for this block
+    const int start = a.start_pos[b];
+    const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
+    const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
+    const int tile_begin = lo_block / A_BN;
+    const int n_tiles = (n_tok > 0) ? p_last / A_BN + 1 - tile_begin : 0;
+    const int* pages = a.page_table + (long long)b * a.pages_per_seq;
+    const int seq_last = start + q_len - 1;                          // the sequence's last key
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0 && n_tiles > 0) {
+            // a box is heads_per_block x tokens_per_block rows whatever part of it lies outside the tensor; rows of the
+            // tile past the box are not written, and nothing reads their results
+            mbar_expect_tx(q_full, (unsigned)(A_KB * a.heads_per_block * a.tokens_per_block * 128));
+            for (int kb = 0; kb < A_KB; ++kb)
+                tma_load_3d(q_base + kb * A_BM * 128, &map_q, kb * 64, kvh * a.group + chunk * a.heads_per_block,
+                            seq_tok0 + tok0, q_full);
+            int page = __ldg(pages + tile_begin);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % A_STAGES;
+                const unsigned phase = (j / A_STAGES) & 1;
+                const int page_next = (j + 1 < n_tiles) ? __ldg(pages + tile_begin + j + 1) : 0;
+                if (!mbar_wait(kv_empty(s), phase ^ 1u, a.status, 11)) break;
+                const int row = (page * a.kv_heads + kvh) * A_BN;       // a missing page (-1) reads as zeros
+                mbar_expect_tx(k_full(s), A_TILE_BYTES);
+                for (int kb = 0; kb < A_KB; ++kb)
+                    tma_load_2d(k_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_k, kb * 64, row, k_full(s));
+                mbar_expect_tx(v_full(s), A_TILE_BYTES);
+                for (int kb = 0; kb < A_KB; ++kb)
+                    tma_load_2d(v_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_v, kb * 64, row, v_full(s));
+                page = page_next;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- tensor-core issuer
+        if (lane == 0 && n_tiles > 0) {
+            constexpr unsigned idesc_s = umma_idesc(A_BN);
+            constexpr unsigned idesc_o = umma_idesc(A_HD, true);
+            bool ok = mbar_wait(q_full, 0, a.status, 12);
+            auto issue_scores = [&](int j) -> bool {
+                const int s = j % A_STAGES, i = j & 1;
+                if (!mbar_wait(k_full(s), (j / A_STAGES) & 1, a.status, 12)) return false;
+                if (!mbar_wait(s_empty(i), (((unsigned)j >> 1) & 1u) ^ 1u, a.status, 12)) return false;
+                tcgen05_fence_after();
+                const unsigned d = tmem_base + (unsigned)(i * A_BN);
+#pragma unroll
+                for (int kb = 0; kb < A_KB; ++kb) {
+                    const unsigned long long qd = umma_desc_sw128(q_base + kb * A_BM * 128);
+                    const unsigned long long kd = umma_desc_sw128(k_base + s * A_TILE_BYTES + kb * A_BN * 128);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tcgen05_mma_f16(d, qd + 2ull * k, kd + 2ull * k, idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(s_full(i));
+                return true;
+            };
+            if (ok) ok = issue_scores(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    ok = issue_scores(j + 1);
+                    if (!ok) break;
+                }
+                const int s = j % A_STAGES, i = j & 1;
+                ok = mbar_wait(v_full(s), (j / A_STAGES) & 1, a.status, 12) &&
+                     mbar_wait(p_full(i), ((unsigned)j >> 1) & 1u, a.status, 12);      // P_j written, the output rescaled
+                if (!ok) break;
+                tcgen05_fence_after();
+                const unsigned d = tmem_base + (unsigned)(2 * A_BN);
+                const unsigned long long pd = umma_desc_sw128(p_base + i * A_P_BYTES);
+                const unsigned long long vd = umma_desc_sw128_mn(v_base + s * A_TILE_BYTES, A_BN * 128);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)      // 16 keys a step: 32 bytes along a row of P, two 8-key groups of V
+                    tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                tcgen05_commit(o_full);
+                tcgen05_commit(kv_empty(s));
+                tcgen05_commit(p_empty(i));
+            }
+        }
+    } else if (n_tiles > 0) {
+        // ---------------- one row per thread
+        const int q4 = warp & 3;
+        const int r = q4 * 32 + lane;
+        const int t = r / a.heads_per_block, hg = chunk * a.heads_per_block + r % a.heads_per_block;
+        const bool row_ok = t < n_tok && hg < a.group && r < a.heads_per_block * a.tokens_per_block;
+        const int hi = row_ok ? start + tok0 + t : -1;
+        const int lo = (a.window > 0) ? max(0, hi - a.window + 1) : 0;
+        const unsigned lane_base = (unsigned)(q4 * 32) << 16;
+        // m is the maximum the row's probabilities and output are scaled by.  It follows the true maximum lazily: only
+        // when a tile's maximum exceeds it by more than 8 (probabilities up to 2^8, harmless in float32 and bfloat16)
+        // is the output in tensor memory rescaled, so that after the first tiles the rescaling almost never runs.
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        const unsigned o_taddr = tmem_base + lane_base + (unsigned)(2 * A_BN);
+
+        for (int j = 0; j < n_tiles; ++j) {
+            const int i = j & 1;
+            ok = mbar_wait(s_full(i), ((unsigned)j >> 1) & 1u, a.status, 13);
+            if (!ok) break;
+            tcgen05_fence_after();
+            float s[64];
+            tmem_load64(tmem_base + lane_base + (unsigned)(i * A_BN), s);
+            tcgen05_fence_before();
+            mbar_arrive(s_empty(i));
+
+            const int key0 = (tile_begin + j) * A_BN;
+            if (!(key0 + A_BN - 1 <= hi && key0 >= lo)) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const int kpos = key0 + c;
+                    s[c] = (kpos >= lo && kpos <= hi) ? s[c] : -INFINITY;
+                }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one of 64 links
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+                mx4[0] = fmaxf(mx4[0], s[c]);
+                mx4[1] = fmaxf(mx4[1], s[c + 1]);
+                mx4[2] = fmaxf(mx4[2], s[c + 2]);
+                mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;   // the scale is positive
+            const bool raise = mx > m + 8.0f;                         // false while nothing has been seen (-inf > -inf)
+            const float m_new = raise ? mx : m;
+            const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+            const float corr = raise ? fast_exp2(m - m_use) : 1.0f;   // 0 when nothing was seen before
+            m = m_new;
+            float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            unsigned pk[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float p0 = fast_exp2(fmaf(s[2 * c], a.scale_log2, -m_use));
+                const float p1 = fast_exp2(fmaf(s[2 * c + 1], a.scale_log2, -m_use));
+                ls4[(2 * c) & 3] += p0;
+                ls4[(2 * c + 1) & 3] += p1;
+                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                pk[c] = *reinterpret_cast<unsigned*>(&h);
+            }
+            const float ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+            l = l * corr + ls;
+
+            if (key0 + A_BN - 1 > seq_last) {
+                // the tile reaches past the sequence's last key: zero those rows of V (whole 128-byte rows, so the
+                // swizzle does not matter) once TMA has delivered the tile
+                const int st = j % A_STAGES;
+                ok = mbar_wait(v_full(st), (j / A_STAGES) & 1, a.status, 13);
+                if (!ok) break;
+                const int first = max(seq_last + 1 - key0, 0), n_rows = A_BN - first;
+                for (int idx = r; idx < n_rows * 8 * A_KB; idx += 128) {
+                    const int kb = idx / (n_rows * 8), rem = idx % (n_rows * 8);
+                    *reinterpret_cast<uint4*>(smem_generic + v_off + st * A_TILE_BYTES + kb * A_BN * 128 + (first + rem / 8) * 128 +
+                                              (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            ok = mbar_wait(p_empty(i), (((unsigned)j >> 1) & 1u) ^ 1u, a.status, 13);
+            if (!ok) break;
+            unsigned char* prow = smem_generic + p_off + i * A_P_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            fence_async_shared();
+
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                // Rescale this warp's rows of the output before P_j·V_j is added to them.  O_{j-1} is complete: S_j, which
+                // this thread has read, was issued after it and the tensor cores finish in order; the wait confirms it.
+                ok = mbar_wait(o_full, (unsigned)(j - 1) & 1u, a.status, 13);
+                if (!ok) break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < A_HD; c0 += 32) {
+                    float v[32];
+                    tmem_load32(o_taddr + (unsigned)c0, v);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] *= corr;
+                    tmem_store32(o_taddr + (unsigned)c0, v);
+                }
+                tmem_store_wait();
+                tcgen05_fence_before();
+            }
+            mbar_arrive(p_full(i));
+        }
+        // A parity wait tells phases k and k + 2 apart only if the barrier is known to be within one phase of k.  After the
+        // loop it is only known that O_{last-2} is complete, so wait for O_{last-1} first and then for O_last.
+        if (ok && n_tiles >= 2) ok = mbar_wait(o_full, (unsigned)(n_tiles - 2) & 1u, a.status, 13);
+        if (ok) ok = mbar_wait(o_full, (unsigned)(n_tiles - 1) & 1u, a.status, 13);
+        if (ok) {
+            tcgen05_fence_after();
+            const float inv = 1.0f / l;
+            bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD;
+#pragma unroll
+            for (int c0 = 0; c0 < A_HD; c0 += 32) {
+                float v[32];
+                tmem_load32(o_taddr + (unsigned)c0, v);          // every lane of the warp takes part in the load
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        unsigned w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(v[c + 2 * e] * inv, v[c + 2 * e + 1] * inv);
+                            w[e] = *reinterpret_cast<unsigned*>(&h);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)A_TMEM_COLS) : "memory");
+    }
+}
+
+#endif  // MLC_ATTENTION_TCGEN05
+
+}  // namespace mlc
+
+using namespace mlc;
+
+// q, out: bfloat16 [n_tokens][q_heads*hd], 16-byte aligned; the cache entry starts `entry_offset` elements into the
+// pools and holds `pool_pages` pages of 64 tokens, [page][kv_head][64][hd].  hd is the head size the library was
+// built for (64 or 128; other sizes and pages of another length are refused with MLC_ERR_UNSUPPORTED).  status: one int on the device, 0 before the call; a bounded wait that
+// ran out leaves 11, 12 or 13 there.
+extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
+                                     int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
+                                     int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
+                                     int pages_per_seq, int page_size, long long pool_pages, void* stream) {
+#if MLC_ATTENTION_TCGEN05
+    if (hd != A_HD || page_size != A_BN) return MLC_ERR_UNSUPPORTED;
+    if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return 0;
+    if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || status == nullptr || pool_pages <= 0) return MLC_ERR_BAD_SIZE;
+    if (!(scale > 0.0f) || window < 0) return MLC_ERR_BAD_SIZE;
+    if ((((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) || (entry_offset & 7)) return MLC_ERR_BAD_SIZE;
+    const int group = q_heads / kv_heads;
+    TcAttnArgs a{};
+    a.out = out;
+    a.cu_seqlens = cu_seqlens;
+    a.start_pos = start_pos;
+    a.page_table = page_table;
+    a.pages_per_seq = pages_per_seq;
+    a.q_heads = q_heads;
+    a.kv_heads = kv_heads;
+    a.group = group;
+    a.heads_per_block = group < A_BM ? group : A_BM;
+    a.tokens_per_block = A_BM / a.heads_per_block;
+    a.head_chunks = (group + a.heads_per_block - 1) / a.heads_per_block;
+    a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.status = status;
+    if (a.tokens_per_block > 256 || a.heads_per_block > 256) return MLC_ERR_BAD_SIZE;
+
+    CUtensorMap mq, mk, mv;
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)q_heads, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_heads * hd * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)a.heads_per_block, (cuuint32_t)a.tokens_per_block};
+        int rc = make_tensor_map(&mq, q, 3, dims, strides, box);
+        if (rc) return rc;
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)pool_pages * kv_heads * A_BN};
+        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)A_BN};
+        int rc = make_tensor_map(&mk, (const bf16*)k_pool + entry_offset, 2, dims, strides, box);
+        if (rc) return rc;
+        rc = make_tensor_map(&mv, (const bf16*)v_pool + entry_offset, 2, dims, strides, box);
+        if (rc) return rc;
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A_SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const dim3 grid((max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, kv_heads * a.head_chunks, n_seqs);
+    cudaError_t e = launch_pdl(attention_tcgen05_kernel, grid, dim3(192), (size_t)A_SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, a);
+    return e == cudaSuccess ? 0 : (int)e;
+#else
+    return MLC_ERR_UNSUPPORTED;
+#endif
+}

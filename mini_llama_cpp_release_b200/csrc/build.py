@@ -34,6 +34,8 @@ NVCC_FLAGS = [
 
 # library name → (sources, extra -D flags may be added per variant)
 CORE_SOURCES = ["elementwise.cu", "attention_simt.cu", "sampling.cu", "linear_simt.cu", "gemm_tcgen05.cu"]
+# compiled once per head size (-DMLC_HEAD_DIM=...): the mma.sync kernels for every size, the tcgen05 kernel for 64 and 128
+ATTENTION_SOURCES = ["attention_mma.cu", "attention_tcgen05.cu"]
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
@@ -162,7 +164,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     """The tensor-core attention kernels, compiled for one head size."""
     if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
         raise BuildError(f"the tensor-core attention kernels take head sizes 16, 32, ..., 256; got {head_dim}")
-    return load_library(f"mlc_attn_hd{head_dim}", ["attention_mma.cu"], [f"-DMLC_HEAD_DIM={head_dim}"])
+    return load_library(f"mlc_attn_hd{head_dim}", ATTENTION_SOURCES, [f"-DMLC_HEAD_DIM={head_dim}"])
 
 
 def noalloc_library() -> ctypes.CDLL:
@@ -176,5 +178,5 @@ def build_everything(head_dims: Iterable[int] = (16, 64, 128)) -> List[str]:
     paths = [build_library("mlc_core", CORE_SOURCES), build_library("mlc_noalloc", ["attention_noalloc.cu"])]
     if os.path.exists(os.path.join(_HERE, "attention_mma.cu")):
         for hd in head_dims:
-            paths.append(build_library(f"mlc_attn_hd{hd}", ["attention_mma.cu"], [f"-DMLC_HEAD_DIM={hd}"]))
+            paths.append(build_library(f"mlc_attn_hd{hd}", ATTENTION_SOURCES, [f"-DMLC_HEAD_DIM={hd}"]))
     return paths

@@ -29,17 +29,13 @@
 //
 // Every wait on an mbarrier is bounded by a clock; a wait that runs out records a code in
 // `status`, the block skips its stores, frees its tensor memory and returns.
-#include "common.cuh"
-
-#include <cuda.h>
-#include <cudaTypedefs.h>
+#include "tcgen05.cuh"
 
 namespace mlc {
 
 constexpr int G_BM = 128;
 constexpr int G_BK = 64;
 constexpr int G_A_BYTES = G_BM * G_BK * 2;                 // 16 KiB per stage
-constexpr unsigned long long G_WAIT_NS = 2000000000ull;     // two seconds
 
 enum { EPI_STORE = 0, EPI_SILU_MUL = 1, EPI_QKV = 2, EPI_ADD = 3 };
 
@@ -63,81 +59,6 @@ struct GemmArgs {
     int q_heads, kv_heads, hd;
     PagedKV cache;
 };
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Wait for the phase with the given parity; false (and a code in *status) if two seconds pass.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
-    unsigned long long deadline = 0;
-    for (unsigned spin = 0;; ++spin) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((spin & 1023u) == 1023u) {
-            const unsigned long long now = global_ns();
-            if (deadline == 0) deadline = now + G_WAIT_NS;
-            else if (now > deadline) {
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                                unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_load16(unsigned taddr, float (&v)[16]) {
-    unsigned r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
-// 128-byte spans: start address, 1024 bytes between groups of eight rows, descriptor version 1.
-__device__ __forceinline__ unsigned long long umma_desc_sw128(unsigned smem_addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);            // bits 0-13: address / 16
-    d |= (unsigned long long)(1024u >> 4) << 32;                       // bits 32-45: stride between 8-row groups / 16
-    d |= 1ull << 46;                                                   // bits 46-47: version
-    d |= 2ull << 61;                                                   // bits 61-63: 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = BN.
-__host__ __device__ constexpr unsigned umma_idesc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(G_BM >> 4) << 24);
-}
-
 
 template <int BN, int EPI> struct GemmShape {
     static constexpr int B_BYTES = BN * G_BK * 2;
@@ -456,32 +377,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 // ------------------------------------------------------------------ host side
-static PFN_cuTensorMapEncodeTiled encode_tiled() {
-    static PFN_cuTensorMapEncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        fn = (PFN_cuTensorMapEncodeTiled)p;
-    }
-    return fn;
-}
-
-// A row-major bfloat16 matrix [rows][cols] read in boxes of box_rows x 64 columns with the 128-byte swizzle;
-// reads outside the matrix give zeros.
+// A row-major bfloat16 matrix [rows][cols] read in boxes of box_rows x 64 columns.
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
-    PFN_cuTensorMapEncodeTiled fn = encode_tiled();
-    if (fn == nullptr) return MLC_ERR_UNSUPPORTED;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
     cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : MLC_ERR_BAD_SIZE;
+    return make_tensor_map(map, ptr, 2, dims, strides, box);
 }
 
 template <int BN, int EPI>

@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -327,6 +327,8 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
         lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, P]
         lib.mlc_attention_mma.restype = c_int
         lib.mlc_attention_mma_head_dim.restype = c_int
+        lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P]
+        lib.mlc_attention_tcgen05.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
         _attn_libs[head_dim] = lib
@@ -352,6 +354,38 @@ def attention_mma_plan(max_q_len: int, n_seqs: int, max_kv_len: int, q_heads: in
         by_len = max(1, max_kv_len // 256)              # at least four 64-key tiles per split
         n_splits = max(1, min(by_fill, by_len, 32))
     return row_tiles, n_splits
+
+
+TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
+
+
+def attention_tcgen05_takes(head_dim: int, page_size: int, q_heads: int, kv_heads: int) -> bool:
+    """Whether the tcgen05 prompt attention kernel exists for these sizes (else the mma.sync kernels run)."""
+    return head_dim in TCGEN05_ATTENTION_HEAD_DIMS and page_size == 64 and q_heads % kv_heads == 0
+
+
+def attention_tcgen05_blocks(max_q_len: int, n_seqs: int, q_heads: int, kv_heads: int) -> int:
+    """Blocks the tcgen05 attention kernel would launch: 128 rows (tokens x heads of a group) each."""
+    group = q_heads // kv_heads
+    heads = min(group, 128)
+    tokens = 128 // heads
+    return ((max_q_len + tokens - 1) // tokens) * kv_heads * ((group + heads - 1) // heads) * n_seqs
+
+
+def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
+                      max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int) -> None:
+    """Prompt attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry on the tcgen05 tensor cores
+    (head sizes 64 and 128, pages of 64 tokens).  Keys are not split: meant for steps whose rows fill the GPU."""
+    require_cuda(q, out, cu_seqlens, start_pos)
+    if q.dtype != torch.bfloat16 or kv.k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 attention takes bfloat16 queries, cache and output")
+    lib = attention_library(kv.head_dim)
+    status = gemm_status(q.device)
+    _check(lib.mlc_attention_tcgen05(q.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), start_pos.data_ptr(), n_seqs,
+                                     q.shape[0], max_q_len, q_heads, kv.kv_heads, kv.head_dim, float(scale), int(window),
+                                     status.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
+                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, kv.k_pool.shape[1], _stream()),
+           "tcgen05 attention")
 
 
 def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
@@ -399,8 +433,10 @@ def check_gemm_status(device: torch.device) -> None:
         code = int(t.item())
         if code:
             t.zero_()
-            who = {1: "the TMA loader", 2: "the tensor-core issuer", 3: "the epilogue"}.get(code, str(code))
-            raise KernelError(f"a tcgen05 matrix product gave up waiting on a barrier ({who}); its output is not valid")
+            who = {1: "the matrix product's TMA loader", 2: "the matrix product's tensor-core issuer",
+                   3: "the matrix product's epilogue", 11: "the attention kernel's TMA loader",
+                   12: "the attention kernel's tensor-core issuer", 13: "the attention kernel's softmax rows"}.get(code, str(code))
+            raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier ({who}); its output is not valid")
 
 
 _sm_counts = {}

@@ -163,11 +163,14 @@ def bench_attention(args) -> None:
 
     def fn(i):
         kv = bindings.KVView(k_pool, v_pool, (i % C) * per, table, 64, KV, hd)
+        if args.impl == "tcgen05":
+            kernels.attention_tcgen05(q, out, cu, start, B, q_len, H, kv, 1 / math.sqrt(hd), 0)
+            return
         kernels.attention_mma(q, out, cu, start, B, q_len, H, kv, 1 / math.sqrt(hd), 0, row_tiles, n_splits, part_ml, part_o)
 
     nbytes = 2.0 * B * L * KV * hd * 2
     flops = 4.0 * B * H * hd * (q_len * L - q_len * (q_len - 1) / 2)
-    report(f"attention seqs={B} q_len={q_len} context={L} H={H} KV={KV} hd={hd} row_tiles={row_tiles} splits={n_splits}",
+    report(f"attention impl={args.impl} seqs={B} q_len={q_len} context={L} H={H} KV={KV} hd={hd} row_tiles={row_tiles} splits={n_splits}",
            fn, args, nbytes, flops)
 
 
@@ -191,6 +194,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=14)
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--impl", default="mma", choices=["mma", "tcgen05"], help="attention kernel")
     args = ap.parse_args(argv)
     kernels.set_pdl(not args.no_pdl)
     if args.kernel == "gemm":

@@ -142,6 +142,12 @@ class GQAttention(Part):
         if self.use_tensor_cores:
             row_tiles, n_splits = kernels.attention_mma_plan(step.max_q_len, step.n_seqs, step.max_kv_len, self.H,
                                                              self.KV, rt.n_sms)
+            if (step.max_q_len >= 16 and n_splits == 1
+                    and kernels.attention_tcgen05_takes(self.hd, kv.page_size, self.H, self.KV)):
+                # prompts whose rows fill the GPU without sharing out the keys: the tcgen05 kernel
+                kernels.attention_tcgen05(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
+                                          self.scale, window)
+                return
             part_ml = part_o = None
             if n_splits > 1:
                 part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)

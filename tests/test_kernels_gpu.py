@@ -106,7 +106,12 @@ def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0,
     N = q.shape[0]
     part_ml = torch.empty(N * H * n_splits * 2, device=DEV) if n_splits > 1 else None
     part_o = torch.empty(N * H * n_splits * hd, device=DEV) if n_splits > 1 else None
-    if impl == "mma":
+    if impl == "tcgen05":
+        kernels.attention_tcgen05(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
+                                  1.0 / math.sqrt(hd), window)
+        torch.cuda.synchronize()
+        kernels.check_gemm_status(DEV)
+    elif impl == "mma":
         kernels.attention_mma(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
                               1.0 / math.sqrt(hd), window, row_tiles, n_splits, part_ml, part_o, warp_private)
     else:
@@ -400,6 +405,77 @@ def test_tensor_core_attention_ignores_what_lies_beyond_a_sequences_end():
     got, want, _ = attention_case([70, 5], [70, 1], 4, 2, 64, "bfloat16", impl="mma", row_tiles=4)
     assert torch.isfinite(got).all()
     close(got, want, 1e-2)
+
+
+@pytest.mark.parametrize("H,KV,hd", [(14, 2, 64), (12, 2, 128), (3, 3, 64), (5, 1, 128), (140, 1, 64), (16, 1, 64)])
+def test_tcgen05_attention_prompts_chunks_and_single_tokens(H, KV, hd):
+    got, want, _ = attention_case([7, 1, 130, 64], [7, 1, 130, 64], H, KV, hd, "bfloat16", impl="tcgen05")
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([200, 65, 3, 64, 128, 129], [1, 1, 1, 1, 1, 1], H, KV, hd, "bfloat16", seed=1, impl="tcgen05")
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([150, 90, 300], [22, 90, 2], H, KV, hd, "bfloat16", seed=2, impl="tcgen05")
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([700, 257], [700, 130], H, KV, hd, "bfloat16", seed=3, impl="tcgen05")
+    close(got, want, 1e-2)
+
+
+@pytest.mark.parametrize("window", [1, 24, 64, 65, 130])
+def test_tcgen05_attention_window_edge_and_far_key(window):
+    def prefer_outside(qs, ks, vs):
+        for q, k, v in zip(qs, ks, vs):
+            n = len(k)
+            if n - 1 - window >= 0:
+                k[n - 1 - window] = 0
+                k[n - 1 - window, :, 0] = 30.0
+                q[n - 1, :, 0] = 30.0
+                v[n - 1 - window] = 100.0
+    got, want, _ = attention_case([200, 66, 25], [1, 1, 1], 6, 3, 64, "bfloat16", window=window, scale_up=prefer_outside,
+                                  impl="tcgen05")
+    assert float(want.abs().max()) < 50
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([200, 66], [200, 30], 6, 3, 64, "bfloat16", window=window, seed=4, impl="tcgen05")
+    close(got, want, 1e-2)
+
+    def one_far_key(qs, ks, vs):
+        q, k, v = qs[0], ks[0], vs[0]
+        k[3] = 0; k[3, :, 5] = 16.0
+        q[-1] = 0; q[-1, :, 5] = 16.0
+        v[3] = 7.0
+    got, want, _ = attention_case([900], [40], 14, 2, 64, "bfloat16", scale_up=one_far_key, impl="tcgen05")
+    close(got, want, 1e-2)
+    assert float((got[-1] - 7.0).abs().max()) < 0.2
+
+
+def test_tcgen05_attention_rescales_when_the_maximum_keeps_rising():
+    """One key per page scores far above everything before it, so every row's running maximum jumps by more than
+    the lazy-rescaling threshold page after page; the value at that key is the page's number."""
+    def rising(qs, ks, vs):
+        q, k, v = qs[0], ks[0], vs[0]
+        q[:, :, 0] = 8.0
+        k[:, :, 0] = 0.0
+        for page in range(len(k) // 64):
+            k[64 * page + 5, :, 0] = 8.0 * (page + 1)
+            v[64 * page + 5] = float(page)
+    got, want, _ = attention_case([640], [640], 14, 2, 64, "bfloat16", scale_up=rising, impl="tcgen05")
+    close(got, want, 1e-2)
+    assert abs(float(got[-1].mean()) - 9.0) < 0.05 and abs(float(got[200].mean()) - 3.0) < 0.05
+    got, want, _ = attention_case([640], [640], 8, 2, 128, "bfloat16", scale_up=rising, impl="tcgen05")
+    close(got, want, 1e-2)
+
+
+def test_tcgen05_attention_ignores_what_lies_beyond_a_sequences_end():
+    got, want, _ = attention_case([70, 5, 64], [70, 1, 64], 4, 2, 64, "bfloat16", impl="tcgen05")
+    assert torch.isfinite(got).all()
+    close(got, want, 1e-2)
+
+
+def test_tcgen05_attention_refuses_other_head_sizes():
+    q = torch.zeros(4, 4 * 32, dtype=torch.bfloat16, device=DEV)
+    kv = make_paged([torch.zeros(4, 1, 32)], [torch.zeros(4, 1, 32)], torch.bfloat16)
+    z = torch.tensor([0, 4], dtype=torch.int32, device=DEV)
+    assert not kernels.attention_tcgen05_takes(32, 64, 4, 1)
+    with pytest.raises(kernels.KernelError, match="does not support"):
+        kernels.attention_tcgen05(q, torch.empty_like(q), z, z[:1], 1, 4, 4, kv, 1.0, 0)
 
 
 def test_refusals_are_errors_not_wrong_results():
