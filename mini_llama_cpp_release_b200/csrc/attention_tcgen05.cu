@@ -48,6 +48,8 @@ struct TcAttnArgs {
     int window;
     float scale_log2;
     int* status;
+    long long* timing;          // optional [blocks][16] clock cycles spent in each phase by the first softmax warp (0-7)
+                                // and by the issuing thread (8-15), for tuning; or null
 };
 
 #if MLC_ATTENTION_TCGEN05
@@ -76,6 +78,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __global__ void __launch_bounds__(192, A_BLOCKS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, TcAttnArgs a) {
+    const long long t_entry = clock64();
+    const unsigned long long g_entry = global_ns();
     // ---- which rows: heavy blocks (late tokens see the most keys) first
     const int b = blockIdx.z;
     const int kvh = blockIdx.y / a.head_chunks, chunk = blockIdx.y % a.head_chunks;
@@ -94,12 +98,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     constexpr unsigned bar_off = p_off + 2 * A_P_BYTES;
     auto k_full = [&](int s) { return bar_base + 8u * s; };
     auto v_full = [&](int s) { return bar_base + 8u * (4 + s); };
-    auto kv_empty = [&](int s) { return bar_base + 8u * (8 + s); };
+    auto k_empty = [&](int s) { return bar_base + 8u * (8 + s); };
+    auto v_empty = [&](int s) { return bar_base + 8u * (26 + s); };
     auto s_full = [&](int i) { return bar_base + 8u * (12 + i); };
-    auto s_empty = [&](int i) { return bar_base + 8u * (14 + i); };
     auto p_full = [&](int i) { return bar_base + 8u * (16 + i); };
-    auto p_empty = [&](int i) { return bar_base + 8u * (18 + i); };
-    const unsigned o_full = bar_base + 8u * 20;
+    auto o_full = [&](int i) { return bar_base + 8u * (20 + i); };       // O_j complete: barrier j & 1
     const unsigned q_full = bar_base + 8u * 24;
     const unsigned tmem_slot = bar_base + 8u * 25;
     volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 25);
@@ -109,16 +112,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int s = 0; s < A_STAGES; ++s) {
             mbar_init(k_full(s), 1);
             mbar_init(v_full(s), 1);
-            mbar_init(kv_empty(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_empty(s), 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full(i), 1);
-            mbar_init(s_empty(i), 128);
             mbar_init(p_full(i), 128);
-            mbar_init(p_empty(i), 1);
         }
         mbar_init(q_full, 1);
-        mbar_init(o_full, 1);
+        mbar_init(o_full(0), 1);
+        mbar_init(o_full(1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -152,20 +155,35 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int kb = 0; kb < A_KB; ++kb)
                 tma_load_3d(q_base + kb * A_BM * 128, &map_q, kb * 64, kvh * a.group + chunk * a.heads_per_block,
                             seq_tok0 + tok0, q_full);
-            int page = __ldg(pages + tile_begin);
-            for (int j = 0; j < n_tiles; ++j) {
+            // K_j is wanted one tile before V_j (the scores run a tile ahead), and its stage is free as soon as S_j is done:
+            // the order is K_0, K_1, V_0, K_2, V_1, ...
+            auto load_k = [&](int j, int page) -> bool {
                 const int s = j % A_STAGES;
-                const unsigned phase = (j / A_STAGES) & 1;
-                const int page_next = (j + 1 < n_tiles) ? __ldg(pages + tile_begin + j + 1) : 0;
-                if (!mbar_wait(kv_empty(s), phase ^ 1u, a.status, 11)) break;
+                if (!mbar_wait(k_empty(s), ((j / A_STAGES) & 1) ^ 1u, a.status, 11)) return false;
                 const int row = (page * a.kv_heads + kvh) * A_BN;       // a missing page (-1) reads as zeros
                 mbar_expect_tx(k_full(s), A_TILE_BYTES);
                 for (int kb = 0; kb < A_KB; ++kb)
                     tma_load_2d(k_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_k, kb * 64, row, k_full(s));
+                return true;
+            };
+            auto load_v = [&](int j, int page) -> bool {
+                const int s = j % A_STAGES;
+                if (!mbar_wait(v_empty(s), ((j / A_STAGES) & 1) ^ 1u, a.status, 11)) return false;
+                const int row = (page * a.kv_heads + kvh) * A_BN;
                 mbar_expect_tx(v_full(s), A_TILE_BYTES);
                 for (int kb = 0; kb < A_KB; ++kb)
                     tma_load_2d(v_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_v, kb * 64, row, v_full(s));
-                page = page_next;
+                return true;
+            };
+            int page_v = __ldg(pages + tile_begin);                                     // page of tile j
+            int page_k = (n_tiles > 1) ? __ldg(pages + tile_begin + 1) : 0;              // page of tile j + 1
+            bool alive = load_k(0, page_v);
+            for (int j = 0; j < n_tiles && alive; ++j) {
+                const int page_next = (j + 2 < n_tiles) ? __ldg(pages + tile_begin + j + 2) : 0;
+                if (j + 1 < n_tiles) alive = load_k(j + 1, page_k);
+                if (alive) alive = load_v(j, page_v);
+                page_v = page_k;
+                page_k = page_next;
             }
         }
     } else if (warp == 1) {
@@ -173,11 +191,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (lane == 0 && n_tiles > 0) {
             constexpr unsigned idesc_s = umma_idesc(A_BN);
             constexpr unsigned idesc_o = umma_idesc(A_HD, true);
+            const bool stamp = a.timing != nullptr;
+            long long ph[6] = {0, 0, 0, 0, 0, 0}, t0 = 0, t1;
+#define MLC_PHASE(k) if (stamp) { t1 = clock64(); ph[k] += t1 - t0; t0 = t1; }
             bool ok = mbar_wait(q_full, 0, a.status, 12);
+            if (stamp) t0 = clock64();
             auto issue_scores = [&](int j) -> bool {
                 const int s = j % A_STAGES, i = j & 1;
                 if (!mbar_wait(k_full(s), (j / A_STAGES) & 1, a.status, 12)) return false;
-                if (!mbar_wait(s_empty(i), (((unsigned)j >> 1) & 1u) ^ 1u, a.status, 12)) return false;
+                MLC_PHASE(0)                                   // waiting for K
+                // the score buffer is free: the rows handed over P_{j-2} (seen in the last round) after reading S_{j-2}
                 tcgen05_fence_after();
                 const unsigned d = tmem_base + (unsigned)(i * A_BN);
 #pragma unroll
@@ -188,7 +211,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     for (int k = 0; k < 4; ++k)
                         tcgen05_mma_f16(d, qd + 2ull * k, kd + 2ull * k, idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
                 }
-                tcgen05_commit(s_full(i));
+                tcgen05_commit(s_full(i));      // arrives when S_j and everything issued before it (O_{j-2} too) is complete
+                MLC_PHASE(2)                                   // issuing S
                 return true;
             };
             if (ok) ok = issue_scores(0);
@@ -198,9 +222,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (!ok) break;
                 }
                 const int s = j % A_STAGES, i = j & 1;
-                ok = mbar_wait(v_full(s), (j / A_STAGES) & 1, a.status, 12) &&
-                     mbar_wait(p_full(i), ((unsigned)j >> 1) & 1u, a.status, 12);      // P_j written, the output rescaled
+                ok = mbar_wait(v_full(s), (j / A_STAGES) & 1, a.status, 12);
+                MLC_PHASE(3)                                   // waiting for V
+                ok = ok && mbar_wait(p_full(i), ((unsigned)j >> 1) & 1u, a.status, 12);      // P_j written, the output rescaled
                 if (!ok) break;
+                MLC_PHASE(4)                                   // waiting for P
                 tcgen05_fence_after();
                 const unsigned d = tmem_base + (unsigned)(2 * A_BN);
                 const unsigned long long pd = umma_desc_sw128(p_base + i * A_P_BYTES);
@@ -208,10 +234,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                 for (int k = 0; k < 4; ++k)      // 16 keys a step: 32 bytes along a row of P, two 8-key groups of V
                     tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                tcgen05_commit(o_full);
-                tcgen05_commit(kv_empty(s));
-                tcgen05_commit(p_empty(i));
+                tcgen05_commit(o_full(i));
+                MLC_PHASE(5)                                   // issuing O
             }
+            if (stamp) {
+                long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) + 8;
+                for (int k = 0; k < 6; ++k) dst[k] = ph[k];
+            }
+#undef MLC_PHASE
         }
     } else if (n_tiles > 0) {
         // ---------------- one row per thread
@@ -219,7 +249,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int r = q4 * 32 + lane;
         const int t = r / a.heads_per_block, hg = chunk * a.heads_per_block + r % a.heads_per_block;
         const bool row_ok = t < n_tok && hg < a.group && r < a.heads_per_block * a.tokens_per_block;
-        const int hi = row_ok ? start + tok0 + t : -1;
+        // Rows that do not exist take the range of the block's last token: they then mask exactly when their neighbours
+        // do, whatever lies in their part of the query tile, and nothing of theirs is stored.
+        const int hi = start + tok0 + min(t, n_tok - 1);
         const int lo = (a.window > 0) ? max(0, hi - a.window + 1) : 0;
         const unsigned lane_base = (unsigned)(q4 * 32) << 16;
         // m is the maximum the row's probabilities and output are scaled by.  It follows the true maximum lazily: only
@@ -227,20 +259,34 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // is the output in tensor memory rescaled, so that after the first tiles the rescaling almost never runs.
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
+        const bool stamp = a.timing != nullptr && warp == 2;      // the whole warp keeps time, so that it stays converged
+        long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t0 = 0, t1;
+#define MLC_PHASE(k) if (stamp) { t1 = clock64(); ph[k] += t1 - t0; t0 = t1; }
+        if (stamp) t0 = clock64();
+        const long long t_role = t0;
         const unsigned o_taddr = tmem_base + lane_base + (unsigned)(2 * A_BN);
 
         for (int j = 0; j < n_tiles; ++j) {
             const int i = j & 1;
             ok = mbar_wait(s_full(i), ((unsigned)j >> 1) & 1u, a.status, 13);
             if (!ok) break;
+            MLC_PHASE(0)                                   // waiting for the scores
             tcgen05_fence_after();
             float s[64];
             tmem_load64(tmem_base + lane_base + (unsigned)(i * A_BN), s);
             tcgen05_fence_before();
-            mbar_arrive(s_empty(i));
+            if (threadIdx.x == 64) {
+                // S_j is complete, and with it everything the issuing thread had issued before: O_{j-2}.  Their K and V
+                // stages are free for the loader.
+                mbar_arrive(k_empty(j % A_STAGES));
+                if (j >= 2) mbar_arrive(v_empty((j - 2) % A_STAGES));
+            }
+            __syncwarp();
+            MLC_PHASE(1)                                   // reading them
 
             const int key0 = (tile_begin + j) * A_BN;
-            if (!(key0 + A_BN - 1 <= hi && key0 >= lo)) {
+            // decided for the warp as a whole: lanes that went separate ways here would run everything below twice
+            if (!__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo)) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int kpos = key0 + c;
@@ -274,6 +320,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             const float ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
             l = l * corr + ls;
+            MLC_PHASE(2)                                   // mask, maximum, exponentials
 
             if (key0 + A_BN - 1 > seq_last) {
                 // the tile reaches past the sequence's last key: zero those rows of V (whole 128-byte rows, so the
@@ -288,18 +335,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                                               (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
-            ok = mbar_wait(p_empty(i), (((unsigned)j >> 1) & 1u) ^ 1u, a.status, 13);
-            if (!ok) break;
+            // the P buffer is free: O_{j-2}, which read it, was complete when S_j was
             unsigned char* prow = smem_generic + p_off + i * A_P_BYTES + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             fence_async_shared();
+            MLC_PHASE(4)                                   // writing P
 
             if (j > 0 && __any_sync(0xffffffffu, raise)) {
-                // Rescale this warp's rows of the output before P_j·V_j is added to them.  O_{j-1} is complete: S_j, which
-                // this thread has read, was issued after it and the tensor cores finish in order; the wait confirms it.
-                ok = mbar_wait(o_full, (unsigned)(j - 1) & 1u, a.status, 13);
+                // Rescale this warp's rows of the output before P_j·V_j is added to them; O_{j-1} must be complete.  (A parity
+                // wait tells a barrier's phases k and k + 2 apart only if the barrier is known to be within one phase of k.
+                // O_j completes barrier j & 1; this thread has read S_j, which was issued after O_{j-2}, and O_{j+1} cannot
+                // be issued before this thread hands over P_{j+1}: so barrier (j-1) & 1 is at O_{j-1} or just before it.)
+                ok = mbar_wait(o_full((j - 1) & 1), ((unsigned)(j - 1) >> 1) & 1u, a.status, 13);
                 if (!ok) break;
                 tcgen05_fence_after();
 #pragma unroll
@@ -314,11 +363,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tcgen05_fence_before();
             }
             mbar_arrive(p_full(i));
+            MLC_PHASE(5)                                   // rescaling
         }
-        // A parity wait tells phases k and k + 2 apart only if the barrier is known to be within one phase of k.  After the
-        // loop it is only known that O_{last-2} is complete, so wait for O_{last-1} first and then for O_last.
-        if (ok && n_tiles >= 2) ok = mbar_wait(o_full, (unsigned)(n_tiles - 2) & 1u, a.status, 13);
-        if (ok) ok = mbar_wait(o_full, (unsigned)(n_tiles - 1) & 1u, a.status, 13);
+        if (ok) ok = mbar_wait(o_full((n_tiles - 1) & 1), ((unsigned)(n_tiles - 1) >> 1) & 1u, a.status, 13);
+        MLC_PHASE(6)                                       // waiting for the last product
+        if (stamp && lane == 0) {
+            long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+            for (int k = 0; k < 7; ++k) dst[k] = ph[k];
+            dst[7] = n_tiles;
+        }
+#undef MLC_PHASE
         if (ok) {
             tcgen05_fence_after();
             const float inv = 1.0f / l;
@@ -341,6 +395,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
         }
+        if (stamp && lane == 0) {
+            long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+            dst[14] = t_role - t_entry;
+            dst[15] = clock64() - t_entry;
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            dst[6] = smid;
+            dst[12] = (long long)g_entry;
+            dst[13] = (long long)global_ns();
+        }
     }
 
     tcgen05_fence_before();
@@ -359,11 +423,12 @@ using namespace mlc;
 // q, out: bfloat16 [n_tokens][q_heads*hd], 16-byte aligned; the cache entry starts `entry_offset` elements into the
 // pools and holds `pool_pages` pages of 64 tokens, [page][kv_head][64][hd].  hd is the head size the library was
 // built for (64 or 128; other sizes and pages of another length are refused with MLC_ERR_UNSUPPORTED).  status: one int on the device, 0 before the call; a bounded wait that
-// ran out leaves 11, 12 or 13 there.
+// ran out leaves 11, 12 or 13 there.  timing: null, or [blocks][16] int64 that receive the clock cycles one softmax
+// warp (0-6; 7 is the block's number of tiles) and the issuing thread (8-13) of each block spent in their phases.
 extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
                                      int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
                                      int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
-                                     int pages_per_seq, int page_size, long long pool_pages, void* stream) {
+                                     int pages_per_seq, int page_size, long long pool_pages, long long* timing, void* stream) {
 #if MLC_ATTENTION_TCGEN05
     if (hd != A_HD || page_size != A_BN) return MLC_ERR_UNSUPPORTED;
     if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return 0;
@@ -386,6 +451,7 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
     a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.status = status;
+    a.timing = timing;
     if (a.tokens_per_block > 256 || a.heads_per_block > 256) return MLC_ERR_BAD_SIZE;
 
     CUtensorMap mq, mk, mv;
