@@ -8,7 +8,7 @@
 //     warp 0     one thread issues the TMA loads: the query rows once, then a ring of K and V pages;
 //     warp 1     allocates tensor memory; one thread issues tcgen05.mma: S_j = Q·K_jᵀ into one of two
 //                score buffers, and O += P_j·V_j (V is the MN-major operand, read as the cache holds it);
-//     warps 2-5  one thread per row: reads the row's 64 scores from tensor memory, masks where the tile
+//     warps 2-9  two threads per row (each 32 of a tile's keys): read the row's 64 scores from tensor memory, mask where the tile
 //                meets the diagonal, a window's edge or padding rows, keeps the running maximum and sum
 //                in float32, writes P_j = exp2(s·scale·log2e − m) as bfloat16 into shared memory for the
 //                tensor cores.  The output accumulates in tensor memory; when a row's maximum rises by more than
@@ -62,7 +62,8 @@ constexpr int A_STAGES = 3;
 constexpr int A_Q_BYTES = A_KB * A_BM * 128;
 constexpr int A_TILE_BYTES = A_KB * A_BN * 128;        // one K or V page of one head
 constexpr int A_P_BYTES = A_BM * 128;
-constexpr int A_BAR_BYTES = 256;
+constexpr int A_BAR_BYTES = 256 + 1024;                // barriers, then the row sums' exchange [2][128] floats
+constexpr int A_THREADS = 64 + 256;
 constexpr int A_SMEM_BYTES = A_Q_BYTES + 2 * A_STAGES * A_TILE_BYTES + 2 * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
 constexpr int A_TMEM_COLS = 256;                       // two score buffers of 64 columns, the output's A_HD
 static_assert(2 * A_BN + A_HD <= A_TMEM_COLS, "tensor memory of a block");
@@ -75,15 +76,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-__global__ void __launch_bounds__(192, A_BLOCKS_PER_SM)
+__global__ void __launch_bounds__(A_THREADS, A_BLOCKS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, TcAttnArgs a) {
-    const long long t_entry = clock64();
+    const int t_entry = (int)clock();
     const unsigned long long g_entry = global_ns();
     // ---- which rows: heavy blocks (late tokens see the most keys) first
-    const int b = blockIdx.z;
-    const int kvh = blockIdx.y / a.head_chunks, chunk = blockIdx.y % a.head_chunks;
-    const int tok0 = (gridDim.x - 1 - blockIdx.x) * a.tokens_per_block;
+    // blocks are handed out x first: every sequence's and head's last rows before anyone's earlier rows
+    const int heads_y = a.kv_heads * a.head_chunks;
+    const int b = blockIdx.x / heads_y;
+    const int kvh = (blockIdx.x % heads_y) / a.head_chunks, chunk = blockIdx.x % a.head_chunks;
+    const int tok0 = (gridDim.y - 1 - blockIdx.y) * a.tokens_per_block;
 
     extern __shared__ unsigned char smem_dyn[];
     const unsigned base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -117,7 +120,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full(i), 1);
-            mbar_init(p_full(i), 128);
+            mbar_init(p_full(i), 256);
         }
         mbar_init(q_full, 1);
         mbar_init(o_full(0), 1);
@@ -192,10 +195,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             constexpr unsigned idesc_s = umma_idesc(A_BN);
             constexpr unsigned idesc_o = umma_idesc(A_HD, true);
             const bool stamp = a.timing != nullptr;
-            long long ph[6] = {0, 0, 0, 0, 0, 0}, t0 = 0, t1;
-#define MLC_PHASE(k) if (stamp) { t1 = clock64(); ph[k] += t1 - t0; t0 = t1; }
+            int ph[6] = {0, 0, 0, 0, 0, 0}, t0 = 0, t1;
+#define MLC_PHASE(k) if (stamp) { t1 = (int)clock(); ph[k] += t1 - t0; t0 = t1; }
             bool ok = mbar_wait(q_full, 0, a.status, 12);
-            if (stamp) t0 = clock64();
+            if (stamp) t0 = (int)clock();
             auto issue_scores = [&](int j) -> bool {
                 const int s = j % A_STAGES, i = j & 1;
                 if (!mbar_wait(k_full(s), (j / A_STAGES) & 1, a.status, 12)) return false;
@@ -244,8 +247,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #undef MLC_PHASE
         }
     } else if (n_tiles > 0) {
-        // ---------------- one row per thread
+        // ---------------- two threads per row: warps 2-5 take keys 0-31 of every tile and the first half of the output's
+        // columns, warps 6-9 keys 32-63 and the second half.  Both read all 64 scores for the maximum, so they agree on
+        // the scale without exchanging anything; only the row sums meet at the end.
         const int q4 = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int st_id = threadIdx.x - 64;                 // 0 .. 255
         const int r = q4 * 32 + lane;
         const int t = r / a.heads_per_block, hg = chunk * a.heads_per_block + r % a.heads_per_block;
         const bool row_ok = t < n_tok && hg < a.group && r < a.heads_per_block * a.tokens_per_block;
@@ -260,11 +267,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
         const bool stamp = a.timing != nullptr && warp == 2;      // the whole warp keeps time, so that it stays converged
-        long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t0 = 0, t1;
-#define MLC_PHASE(k) if (stamp) { t1 = clock64(); ph[k] += t1 - t0; t0 = t1; }
-        if (stamp) t0 = clock64();
-        const long long t_role = t0;
-        const unsigned o_taddr = tmem_base + lane_base + (unsigned)(2 * A_BN);
+        int ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t0 = 0, t1;        // 32-bit clocks: differences survive the wrap
+#define MLC_PHASE(k) if (stamp) { t1 = (int)clock(); ph[k] += t1 - t0; t0 = t1; }
+        if (stamp) t0 = (int)clock();
+        const int t_role = t0;
+        constexpr int O_COLS = A_HD / 2;                    // output columns of one thread
+        const unsigned o_taddr = tmem_base + lane_base + (unsigned)(2 * A_BN + half * O_COLS);
 
         for (int j = 0; j < n_tiles; ++j) {
             const int i = j & 1;
@@ -272,8 +280,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!ok) break;
             MLC_PHASE(0)                                   // waiting for the scores
             tcgen05_fence_after();
-            float s[64];
-            tmem_load64(tmem_base + lane_base + (unsigned)(i * A_BN), s);
+            float s[32], u[32];                            // this thread's keys, and the other half's (for the maximum)
+            tmem_load32(tmem_base + lane_base + (unsigned)(i * A_BN + half * 32), s);
+            tmem_load32(tmem_base + lane_base + (unsigned)(i * A_BN + (half ^ 1) * 32), u);
             tcgen05_fence_before();
             if (threadIdx.x == 64) {
                 // S_j is complete, and with it everything the issuing thread had issued before: O_{j-2}.  Their K and V
@@ -287,19 +296,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int key0 = (tile_begin + j) * A_BN;
             // decided for the warp as a whole: lanes that went separate ways here would run everything below twice
             if (!__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo)) {
+                const int ks = key0 + half * 32, ku = key0 + (half ^ 1) * 32;
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const int kpos = key0 + c;
-                    s[c] = (kpos >= lo && kpos <= hi) ? s[c] : -INFINITY;
+                for (int c = 0; c < 32; ++c) {
+                    s[c] = (ks + c >= lo && ks + c <= hi) ? s[c] : -INFINITY;
+                    u[c] = (ku + c >= lo && ku + c <= hi) ? u[c] : -INFINITY;
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one of 64 links
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
-                mx4[0] = fmaxf(mx4[0], s[c]);
-                mx4[1] = fmaxf(mx4[1], s[c + 1]);
-                mx4[2] = fmaxf(mx4[2], s[c + 2]);
-                mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            for (int c = 0; c < 32; c += 4) {
+                mx4[0] = fmaxf(mx4[0], fmaxf(s[c], u[c]));
+                mx4[1] = fmaxf(mx4[1], fmaxf(s[c + 1], u[c + 1]));
+                mx4[2] = fmaxf(mx4[2], fmaxf(s[c + 2], u[c + 2]));
+                mx4[3] = fmaxf(mx4[3], fmaxf(s[c + 3], u[c + 3]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;   // the scale is positive
             const bool raise = mx > m + 8.0f;                         // false while nothing has been seen (-inf > -inf)
@@ -308,9 +318,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float corr = raise ? fast_exp2(m - m_use) : 1.0f;   // 0 when nothing was seen before
             m = m_new;
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            unsigned pk[32];
+            unsigned pk[16];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
+            for (int c = 0; c < 16; ++c) {
                 const float p0 = fast_exp2(fmaf(s[2 * c], a.scale_log2, -m_use));
                 const float p1 = fast_exp2(fmaf(s[2 * c + 1], a.scale_log2, -m_use));
                 ls4[(2 * c) & 3] += p0;
@@ -329,7 +339,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 ok = mbar_wait(v_full(st), (j / A_STAGES) & 1, a.status, 13);
                 if (!ok) break;
                 const int first = max(seq_last + 1 - key0, 0), n_rows = A_BN - first;
-                for (int idx = r; idx < n_rows * 8 * A_KB; idx += 128) {
+                for (int idx = st_id; idx < n_rows * 8 * A_KB; idx += 256) {
                     const int kb = idx / (n_rows * 8), rem = idx % (n_rows * 8);
                     *reinterpret_cast<uint4*>(smem_generic + v_off + st * A_TILE_BYTES + kb * A_BN * 128 + (first + rem / 8) * 128 +
                                               (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
@@ -338,13 +348,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // the P buffer is free: O_{j-2}, which read it, was complete when S_j was
             unsigned char* prow = smem_generic + p_off + i * A_P_BYTES + r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             fence_async_shared();
             MLC_PHASE(4)                                   // writing P
 
             if (j > 0 && __any_sync(0xffffffffu, raise)) {
-                // Rescale this warp's rows of the output before P_j·V_j is added to them; O_{j-1} must be complete.  (A parity
+                // Rescale this warp's part of the output before P_j·V_j is added to it; O_{j-1} must be complete.  (A parity
                 // wait tells a barrier's phases k and k + 2 apart only if the barrier is known to be within one phase of k.
                 // O_j completes barrier j & 1; this thread has read S_j, which was issued after O_{j-2}, and O_{j+1} cannot
                 // be issued before this thread hands over P_{j+1}: so barrier (j-1) & 1 is at O_{j-1} or just before it.)
@@ -352,7 +362,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (!ok) break;
                 tcgen05_fence_after();
 #pragma unroll
-                for (int c0 = 0; c0 < A_HD; c0 += 32) {
+                for (int c0 = 0; c0 < O_COLS; c0 += 32) {
                     float v[32];
                     tmem_load32(o_taddr + (unsigned)c0, v);
 #pragma unroll
@@ -373,12 +383,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             dst[7] = n_tiles;
         }
 #undef MLC_PHASE
+        // the two halves of a row add up their sums
+        float* l_part = reinterpret_cast<float*>(smem_generic + bar_off + 256);       // [2][128]
+        l_part[half * 128 + r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");                                 // the softmax warps only
+        l += l_part[(half ^ 1) * 128 + r];
         if (ok) {
             tcgen05_fence_after();
             const float inv = 1.0f / l;
-            bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD;
+            bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD + half * O_COLS;
 #pragma unroll
-            for (int c0 = 0; c0 < A_HD; c0 += 32) {
+            for (int c0 = 0; c0 < O_COLS; c0 += 32) {
                 float v[32];
                 tmem_load32(o_taddr + (unsigned)c0, v);          // every lane of the warp takes part in the load
                 if (row_ok) {
@@ -398,7 +413,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (stamp && lane == 0) {
             long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
             dst[14] = t_role - t_entry;
-            dst[15] = clock64() - t_entry;
+            dst[15] = (int)clock() - t_entry;
             unsigned smid;
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
             dst[6] = smid;
@@ -477,8 +492,9 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const dim3 grid((max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, kv_heads * a.head_chunks, n_seqs);
-    cudaError_t e = launch_pdl(attention_tcgen05_kernel, grid, dim3(192), (size_t)A_SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, a);
+    const dim3 grid(kv_heads * a.head_chunks * n_seqs, (max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, 1);
+    if (grid.y > 65535) return MLC_ERR_BAD_SIZE;
+    cudaError_t e = launch_pdl(attention_tcgen05_kernel, grid, dim3(A_THREADS), (size_t)A_SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, a);
     return e == cudaSuccess ? 0 : (int)e;
 #else
     return MLC_ERR_UNSUPPORTED;
