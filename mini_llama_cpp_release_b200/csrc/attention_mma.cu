@@ -52,6 +52,8 @@ struct MmaArgs {
     int heads_per_block;
     int head_chunks;
     int n_splits;
+    int cluster_merge;        // decode kernel: the blocks of one row tile form a cluster and merge their key splits through
+                              // distributed shared memory instead of part_ml / part_o and a second kernel
 };
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
@@ -620,7 +622,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     __syncthreads();
     float* Oc = reinterpret_cast<float*>(KVs);                      // [DNW warps][16][HD]
     float* MLc = Oc + DNW * 16 * HD;                                // [DNW warps][16][2]
-    static_assert(DNW * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (DNW * 16 * HD + DNW * 16 * 2) * sizeof(float), "merge buffer");
+    static_assert(DNW * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (DNW * 16 * HD + DNW * 16 * 2 + 16 * HD + 32) * sizeof(float), "merge buffer");
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         const int r16 = (lane >> 2) + 8 * rr;
@@ -637,10 +639,12 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     }
     __syncthreads();
     constexpr float LN2 = 0.6931471805599453f;
+    float* Pc = MLc + DNW * 16 * 2;                                 // [16][HD] this block's merged output (cluster merge)
+    float* PMLc = Pc + 16 * HD;                                     // [16][2] and its maximum and sum
     for (int idx = tid; idx < 16 * HD; idx += DNW * 32) {
         const int r = idx / HD, d = idx % HD;
         const int t = r / GH, hg = chunk * GH + r % GH;
-        if (!(t < n_tok && hg < a.group)) continue;
+        if (!(t < n_tok && hg < a.group) && !a.cluster_merge) continue;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DNW; ++w) M = fmaxf(M, MLc[(w * 16 + r) * 2]);
@@ -655,7 +659,13 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
             }
         }
         const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
-        if (a.n_splits == 1) {
+        if (a.cluster_merge) {
+            Pc[idx] = acc;
+            if (d == 0) {
+                PMLc[2 * r] = M;
+                PMLc[2 * r + 1] = L;
+            }
+        } else if (a.n_splits == 1) {
             a.out[row * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
             const long long pr = row * a.n_splits + split;
@@ -666,6 +676,73 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
             }
         }
     }
+    if (a.cluster_merge) {
+        // The n_splits blocks of this row tile are one cluster (rank = split).  Each takes a share of the 16 x HD outputs
+        // and reads every block's partial result for them out of that block's shared memory.
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int S = a.n_splits;
+        const int per = (16 * HD + S - 1) / S;
+        const unsigned pc_local = (unsigned)__cvta_generic_to_shared(Pc), pml_local = (unsigned)__cvta_generic_to_shared(PMLc);
+        for (int idx = split * per + tid; idx < min(16 * HD, (split + 1) * per); idx += DNW * 32) {
+            const int r = idx / HD, d = idx % HD;
+            const int t = r / GH, hg = chunk * GH + r % GH;
+            if (!(t < n_tok && hg < a.group)) continue;
+            float M = -INFINITY, L = 0.0f, acc = 0.0f;
+            for (int k = 0; k < S; ++k) {                 // running merge: one pass over the blocks
+                unsigned pc_r, pml_r;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(pc_r) : "r"(pc_local), "r"(k));
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(pml_r) : "r"(pml_local), "r"(k));
+                float mk, lk, ok;
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mk) : "r"(pml_r + 8u * r));
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lk) : "r"(pml_r + 8u * r + 4u));
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ok) : "r"(pc_r + 4u * idx));
+                if (mk != -INFINITY) {
+                    const float Mn = fmaxf(M, mk);
+                    const float f_old = exp2f(M - Mn), f_new = exp2f(mk - Mn);      // exp2f(-inf) = 0 for the first
+                    L = L * f_old + lk * f_new;
+                    acc = acc * f_old + ok * f_new;
+                    M = Mn;
+                }
+            }
+            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+            a.out[row * HD + d] = __float2bfloat16_rn(acc / L);
+        }
+        // nobody leaves while its shared memory may still be read
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+}
+
+// How many clusters of `size` blocks of the decode kernel the GPU can hold at once (0: that size cannot be launched).
+// 8 is the portable limit; 16 needs the opt-in and enough SMs per GPC.
+static int decode_clusters_resident(int size) {
+    static int cached[17] = {0};
+    static bool known[17] = {false};
+    if (size < 1 || size > 16) return 0;
+    if (!known[size]) {
+        const size_t smem = (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
+        int n = 0;
+        bool can = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        if (can && size > 8)
+            can = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        if (can) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1, (unsigned)size, 1);
+            cfg.blockDim = dim3(DNW * 32);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = (unsigned)size;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel, &cfg) != cudaSuccess) n = 0;
+        }
+        (void)cudaGetLastError();
+        cached[size] = n;
+        known[size] = true;
+    }
+    return cached[size];
 }
 
 static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_t s) {
@@ -676,7 +753,26 @@ static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStre
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(DNW * 32), smem, s, a, c);
+    if (!a.cluster_merge) {
+        cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(DNW * 32), smem, s, a, c);
+        return e == cudaSuccess ? 0 : (int)e;
+    }
+    if (decode_clusters_resident(a.n_splits) < 1) return MLC_ERR_UNSUPPORTED;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DNW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;       // blockIdx.y = (head, split): the splits of a head are neighbours
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)a.n_splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel, a, c);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
@@ -700,6 +796,10 @@ using namespace mlc;
 
 extern "C" int mlc_attention_mma_head_dim() { return HD; }
 
+// How many clusters of `size` blocks of the single-token kernel fit on the GPU at once; 0 if clusters of that size
+// cannot be launched.  Key splits merged inside a cluster (n_splits > 1 without part_ml / part_o) need at least 1.
+extern "C" int mlc_attention_decode_clusters_resident(int size) { return decode_clusters_resident(size); }
+
 // q, out: bfloat16 [n_tokens][q_heads][HD]; the cache pools hold bfloat16 in pages of 64 tokens.
 // row_tiles: 1, 2 or 4 (16, 32 or 64 rows per block); with row_tiles 1, warp_private != 0 picks the
 // kernel whose warps each stream their own sub-tiles (the decode form).  n_splits > 1 writes partial results to
@@ -714,7 +814,11 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
     if (row_tiles != 1 && row_tiles != 2 && row_tiles != 4) return MLC_ERR_BAD_SIZE;
     if (!(scale > 0.0f)) return MLC_ERR_BAD_SIZE;                     // the kernels move the scale past a maximum
-    if (n_splits < 1 || (n_splits > 1 && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
+    // key splits without partial-result buffers: the decode kernel merges them inside a cluster (up to
+    // mlc_attention_decode_cluster_limit() splits)
+    const bool cluster_merge = n_splits > 1 && part_ml == nullptr && part_o == nullptr;
+    if (n_splits < 1 || (n_splits > 1 && !cluster_merge && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
+    if (cluster_merge && !(row_tiles == 1 && warp_private && max_q_len == 1)) return MLC_ERR_UNSUPPORTED;
     MmaArgs a;
     a.q = (const bf16*)q;
     a.out = (bf16*)out;
@@ -731,6 +835,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     a.tokens_per_block = rows / a.heads_per_block;
     a.head_chunks = (a.group + a.heads_per_block - 1) / a.heads_per_block;
     a.n_splits = n_splits;
+    a.cluster_merge = cluster_merge ? 1 : 0;
     const long long gy = (long long)kv_heads * a.head_chunks * n_splits;
     if (gy > 65535) return MLC_ERR_BAD_SIZE;
     PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, kv_heads, hd};

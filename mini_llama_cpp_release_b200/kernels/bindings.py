@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -327,12 +327,45 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
         lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, P]
         lib.mlc_attention_mma.restype = c_int
         lib.mlc_attention_mma_head_dim.restype = c_int
+        lib.mlc_attention_decode_clusters_resident.argtypes = [I]
+        lib.mlc_attention_decode_clusters_resident.restype = c_int
         lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P]
         lib.mlc_attention_tcgen05.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
         _attn_libs[head_dim] = lib
     return lib
+
+
+_clusters_resident = {}
+
+
+def attention_decode_clusters_resident(head_dim: int, size: int) -> int:
+    """How many thread-block clusters of `size` blocks of the single-token attention kernel the GPU holds at once
+    (0: clusters of that size cannot be launched)."""
+    key = (head_dim, size)
+    n = _clusters_resident.get(key)
+    if n is None:
+        n = int(attention_library(head_dim).mlc_attention_decode_clusters_resident(size))
+        _clusters_resident[key] = n
+    return n
+
+
+def attention_decode_splits(head_dim: int, blocks: int, max_kv_len: int, keys_per_split: int = 256) -> int:
+    """Key splits for a step of single tokens: the largest cluster that still lets all of the step's `blocks` (sequences
+    x kv heads x head chunks) clusters run at once, with at least `keys_per_split` keys each.  A cluster that does not
+    fit waits for a second wave, which costs more than the split saves."""
+    by_len = max(1, max_kv_len // keys_per_split)
+    best = 1
+    for size in range(2, 17):
+        if size <= by_len and attention_decode_clusters_resident(head_dim, size) >= blocks:
+            best = size
+    return best
+
+
+def attention_decode_cluster_limit(head_dim: int) -> int:
+    """The largest cluster the single-token attention kernel can merge key splits in."""
+    return max(s for s in range(1, 17) if s == 1 or attention_decode_clusters_resident(head_dim, s) > 0)
 
 
 def attention_mma_plan(max_q_len: int, n_seqs: int, max_kv_len: int, q_heads: int, kv_heads: int, n_sms: int):
@@ -399,7 +432,8 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
         raise KernelError("the tensor-core attention takes bfloat16 queries and cache")
     n_tokens = q.shape[0]
     hd = kv.head_dim
-    if n_splits > 1:
+    in_cluster = n_splits > 1 and part_ml is None and part_o is None      # merged inside the kernel, no second launch
+    if n_splits > 1 and not in_cluster:
         assert part_ml is not None and part_ml.numel() >= n_tokens * q_heads * n_splits * 2
         assert part_o is not None and part_o.numel() >= n_tokens * q_heads * n_splits * hd
     lib = attention_library(hd)
@@ -408,7 +442,7 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
                                  1 if warp_private else 0, n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(),
                                  kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq,
                                  kv.page_size, _stream()), "tensor-core attention")
-    if n_splits > 1:
+    if n_splits > 1 and not in_cluster:
         _check(core().mlc_attention_combine(part_ml.data_ptr(), part_o.data_ptr(), n_tokens * q_heads, n_splits, hd,
                                             out.data_ptr(), dtype_code(out.dtype), _stream()), "attention combine")
 

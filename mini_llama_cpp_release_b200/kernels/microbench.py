@@ -157,8 +157,10 @@ def bench_attention(args) -> None:
     row_tiles, n_splits = kernels.attention_mma_plan(q_len, B, L, H, KV, props.multi_processor_count)
     if args.splits:
         n_splits = args.splits
-    part_ml = torch.empty(B * q_len * H * n_splits * 2, device=DEV)
-    part_o = torch.empty(B * q_len * H * n_splits * hd, device=DEV)
+    if args.cluster and q_len == 1:
+        n_splits = args.splits or kernels.attention_decode_splits(hd, B * KV * max(1, (H // KV + 15) // 16), L)
+    part_ml = torch.empty(B * q_len * H * n_splits * 2, device=DEV) if not args.cluster else None
+    part_o = torch.empty(B * q_len * H * n_splits * hd, device=DEV) if not args.cluster else None
     per = pages_per * B * KV * 64 * hd
 
     def fn(i):
@@ -194,6 +196,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=14)
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--cluster", action="store_true", help="single tokens: merge key splits inside a thread-block cluster")
     ap.add_argument("--impl", default="mma", choices=["mma", "tcgen05"], help="attention kernel")
     args = ap.parse_args(argv)
     kernels.set_pdl(not args.no_pdl)

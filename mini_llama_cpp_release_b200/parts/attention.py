@@ -149,7 +149,11 @@ class GQAttention(Part):
                                           self.scale, window)
                 return
             part_ml = part_o = None
-            if n_splits > 1:
+            if step.max_q_len == 1 and row_tiles == 1:
+                # single tokens: the blocks that share out a head's keys form a cluster and merge among themselves
+                blocks = step.n_seqs * self.KV * max(1, (self.H // self.KV + 15) // 16)
+                n_splits = kernels.attention_decode_splits(self.hd, blocks, step.max_kv_len)
+            elif n_splits > 1:
                 part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
                 part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
             kernels.attention_mma(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,

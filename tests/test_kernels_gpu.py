@@ -87,7 +87,7 @@ def make_paged(ks, vs, dtype, page_size=64, entries=2, entry=1, spare=3, seed=0)
 
 
 def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0, scale_up=None, impl="simt", row_tiles=4,
-                   warp_private=True):
+                   warp_private=True, in_cluster=False):
     """Sequences of `lens` cached tokens of which the last `q_lens` are this step's; compare
     with the plain attention of each whole sequence."""
     g = torch.Generator().manual_seed(seed)
@@ -104,8 +104,8 @@ def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0,
     cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
     start = torch.tensor([n - m for n, m in zip(lens, q_lens)], dtype=torch.int32, device=DEV)
     N = q.shape[0]
-    part_ml = torch.empty(N * H * n_splits * 2, device=DEV) if n_splits > 1 else None
-    part_o = torch.empty(N * H * n_splits * hd, device=DEV) if n_splits > 1 else None
+    part_ml = torch.empty(N * H * n_splits * 2, device=DEV) if n_splits > 1 and not in_cluster else None
+    part_o = torch.empty(N * H * n_splits * hd, device=DEV) if n_splits > 1 and not in_cluster else None
     if impl == "tcgen05":
         kernels.attention_tcgen05(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
                                   1.0 / math.sqrt(hd), window)
@@ -369,6 +369,34 @@ def test_tensor_core_attention_key_splits(n_splits, row_tiles):
     close(got, want, 1e-2)
     got, want, _ = attention_case([300, 40], [40, 3], 4, 2, 16, "bfloat16", seed=3, **kw)
     close(got, want, 1e-2)
+
+
+@pytest.mark.parametrize("H,KV,hd", [(14, 2, 64), (4, 2, 16), (12, 2, 128), (3, 1, 256), (40, 1, 48)])
+@pytest.mark.parametrize("n_splits", [2, 5, 8])
+def test_single_token_attention_merges_key_splits_inside_a_cluster(n_splits, H, KV, hd):
+    kw = dict(impl="mma", row_tiles=1, n_splits=n_splits, in_cluster=True)
+    got, want, _ = attention_case([700, 33, 1, 64, 1000], [1, 1, 1, 1, 1], H, KV, hd, "bfloat16", **kw)
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([300, 129], [1, 1], H, KV, hd, "bfloat16", window=70, seed=5, **kw)
+    close(got, want, 1e-2)
+
+    def one_far_key(qs, ks, vs):
+        q, k, v = qs[0], ks[0], vs[0]
+        k[3] = 0; k[3, :, 5] = 16.0
+        q[-1] = 0; q[-1, :, 5] = 16.0
+        v[3] = 7.0
+    got, want, _ = attention_case([900], [1], H, KV, hd, "bfloat16", scale_up=one_far_key, **kw)
+    close(got, want, 1e-2)
+    assert float((got - 7.0).abs().max()) < 0.2
+
+
+def test_cluster_merge_is_refused_for_prompts_and_too_many_splits():
+    limit = kernels.attention_decode_cluster_limit(64)
+    assert limit in (8, 16)
+    with pytest.raises(kernels.KernelError, match="does not support"):
+        attention_case([300], [40], 4, 2, 64, "bfloat16", impl="mma", row_tiles=1, n_splits=4, in_cluster=True)
+    with pytest.raises(kernels.KernelError, match="does not support"):
+        attention_case([3000], [1], 4, 2, 64, "bfloat16", impl="mma", row_tiles=1, n_splits=limit + 1, in_cluster=True)
 
 
 @pytest.mark.parametrize("row_tiles", [0, 1, 4])
