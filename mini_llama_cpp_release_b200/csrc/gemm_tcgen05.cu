@@ -63,15 +63,22 @@ struct GemmArgs {
 template <int BN, int EPI> struct GemmShape {
     static constexpr int B_BYTES = BN * G_BK * 2;
     static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN <= 64) ? 8 : (BN <= 128 ? 6 : (EPI == EPI_SILU_MUL ? 3 : 4));
     static constexpr int EPI_GROUPS = (BN >= 64) ? 2 : 1;            // epilogue warps: four per group, groups share out the tokens
     static constexpr int THREADS = 64 + 128 * EPI_GROUPS;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;                // tensor-memory columns of one accumulator
     static constexpr int TMEM_COLS = 2 * ACC_COLS;                    // two accumulators: one is read out while the other fills
     static constexpr int META_BYTES = BN * 16;                        // per token: position, cache offset (QKV epilogue)
-    static constexpr int STAGING_BYTES = (EPI == EPI_SILU_MUL) ? 128 * BN : 0;   // [8 or 4 warps][tokens][16 outputs] bfloat16
+    // SILU_MUL: [8 or 4 warps][tokens][16 outputs] bfloat16; QKV: [8 or 4 warps][2 buffers][16 tokens][32 outputs] bfloat16
+    static constexpr int STAGING_BYTES = (EPI == EPI_SILU_MUL) ? 128 * BN : (EPI == EPI_QKV ? EPI_GROUPS * 4 * 2048 : 0);
+    // QKV: cos and sin of each warp's 16 rotation pairs for the tokens of its group, [warps][tokens][16] float2
+    static constexpr int ROPE_BYTES = (EPI == EPI_QKV && BN <= 128) ? 4 * BN * 128 : 0;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + META_BYTES + 1024 /* alignment slack */;
+    static constexpr int FIXED_BYTES = STAGING_BYTES + ROPE_BYTES + BAR_BYTES + META_BYTES + 1024 /* alignment slack */;
+    static constexpr int STAGES_FIT = (227 * 1024 - FIXED_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES_WANTED = (BN <= 64) ? 8 : (BN <= 128 ? 6 : (EPI == EPI_SILU_MUL ? 3 : 4));
+    static constexpr int STAGES = STAGES_FIT < STAGES_WANTED ? STAGES_FIT : STAGES_WANTED;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIXED_BYTES;
+    static_assert(STAGES >= 2, "stage ring");
 };
 
 template <typename T> __device__ __forceinline__ void store_out(void* base, long long idx, float v) {
@@ -105,7 +112,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const unsigned a_base = base;
     const unsigned b_base = base + S::STAGES * G_A_BYTES;
     constexpr unsigned staging_off = S::STAGES * S::STAGE_BYTES;
-    constexpr unsigned bar_off = staging_off + S::STAGING_BYTES;
+    constexpr unsigned rope_off = staging_off + S::STAGING_BYTES;
+    constexpr unsigned bar_off = rope_off + S::ROPE_BYTES;
     const unsigned bar_base = base + bar_off;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (8 + s); };
@@ -217,6 +225,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int et = threadIdx.x - 64;                               // 0 .. 128*EG-1
         constexpr int COLS_PER_GROUP = BN / EG;
         grid_dependency_wait();                // positions, page lists and the output buffers may come from earlier kernels
+        // QKV through shared memory: when a warp's 32 rows are 16 rotation pairs of one head (head sizes in steps of 32)
+        // and everything is bfloat16 and 16-byte aligned, results leave in 16-byte stores
+        const bool qkv_fast = EPI == EPI_QKV && g.out_dtype == MLC_DTYPE_BF16 && (g.hd & 31) == 0 &&
+                              ((((uintptr_t)g.out) | ((uintptr_t)g.cache.k_pool) | ((uintptr_t)g.cache.v_pool)) & 15) == 0 &&
+                              (g.cache.entry_offset & 7) == 0;
         int j = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
@@ -235,18 +248,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     tok_off[tt] = off;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(128 * EG) : "memory");          // the epilogue warps only
+                if (S::ROPE_BYTES > 0 && qkv_fast) {
+                    // cos and sin of this warp's 16 rotation pairs for its group's tokens, fetched while the products run
+                    const int row0 = m0 + q * 32;
+                    const int head0 = row0 / g.hd, i0 = (row0 % g.hd) >> 1, half = g.hd >> 1;
+                    if (row0 < g.n_out && head0 < g.q_heads + g.kv_heads && g.rope != nullptr) {
+                        float2* rs = reinterpret_cast<float2*>(smem_generic + rope_off) + (eg * 4 + q) * COLS_PER_GROUP * 16;
+                        // eight loads in flight per lane: the loop is a chain of memory latencies otherwise
+                        constexpr int PER_LANE = COLS_PER_GROUP * 16 / 32, BATCH = PER_LANE < 8 ? PER_LANE : 8;
+#pragma unroll 1
+                        for (int it = 0; it < PER_LANE; it += BATCH) {
+                            float2 cs[BATCH];
+#pragma unroll
+                            for (int u = 0; u < BATCH; ++u) {
+                                const int idx = lane + 32 * (it + u);
+                                const int tt = eg * COLS_PER_GROUP + (idx >> 4);
+                                cs[u] = make_float2(1.0f, 0.0f);
+                                if (n0 + tt < g.n_tok)
+                                    cs[u] = __ldg(g.rope + (long long)min(tok_pos[tt], g.rope_positions - 1) * half + i0 + (idx & 15));
+                            }
+#pragma unroll
+                            for (int u = 0; u < BATCH; ++u) rs[lane + 32 * (it + u)] = cs[u];
+                        }
+                    }
+                    __syncwarp();
+                }
             }
             ok = mbar_wait(acc_full_bar(buf), ((unsigned)j >> 1) & 1u, g.status, 3);
             if (!ok) break;
             tcgen05_fence_after();
-            if (stamps != nullptr && et == 0 && j == 0) stamps[4] = global_ns();         // first accumulator complete
+            if (stamps != nullptr && et == 0 && j == 0) { stamps[4] = global_ns(); stamps[6] = -clock64(); }
             const unsigned d_tmem = tmem_base + (unsigned)(buf * S::ACC_COLS);
             const int row = m0 + q * 32 + lane;
+            const float bias_row = (EPI == EPI_QKV && g.bias != nullptr && row < g.n_out) ? __ldg(g.bias + row) : 0.0f;
             // SiLU epilogue through shared memory: bfloat16 output, a full 16-output group inside the matrix, aligned rows
             const bool silu_staged = EPI == EPI_SILU_MUL && g.out_dtype == MLC_DTYPE_BF16 && ((g.n_out >> 1) & 7) == 0 &&
                                      (m0 + q * 32 + 32 <= g.n_out) && ((((uintptr_t)g.out) & 15) == 0);
             bf16* stage = reinterpret_cast<bf16*>(smem_generic + staging_off) + (eg * 4 + q) * COLS_PER_GROUP * 16;
-#pragma unroll 1
+#pragma unroll (EPI == EPI_QKV ? 2 : 1)
             for (int c0 = eg * COLS_PER_GROUP; c0 < (eg + 1) * COLS_PER_GROUP; c0 += 16) {
                 float v[16];
                 tmem_load16(d_tmem + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
@@ -306,6 +345,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     // dim i = (row % hd) / 2, its odd neighbour dim i + hd/2.  Positions and cache offsets
                     // of the tile's tokens were put in shared memory while the products ran.
                     const int hd = g.hd, half = hd >> 1;
+                    if (qkv_fast) {
+                        const int row0 = m0 + q * 32;
+                        if (row0 < g.n_out) {                       // n_out is a multiple of 32 here: the warp's rows all exist
+                            const int head = row0 / hd, i0 = (row0 % hd) >> 1;
+                            const bool second = (lane & 1) != 0;
+                            const float b = bias_row;
+                            const bool rotate = head < g.q_heads + g.kv_heads && g.rope != nullptr;
+                            const bool is_q = head < g.q_heads;
+                            const bool is_k = !is_q && head < g.q_heads + g.kv_heads;
+                            const int kvh = is_k ? head - g.q_heads : head - g.q_heads - g.kv_heads;
+                            bf16* st = reinterpret_cast<bf16*>(smem_generic + staging_off) + (eg * 4 + q) * 1024 + ((c0 >> 4) & 1) * 512;   // [16 tokens][32], two in turn
+                            const float2* rs = reinterpret_cast<const float2*>(smem_generic + rope_off) +
+                                               (eg * 4 + q) * COLS_PER_GROUP * 16 + (c0 - eg * COLS_PER_GROUP) * 16 + (lane >> 1);
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj) {
+                                float2 cs = make_float2(1.0f, 0.0f);
+                                if (rotate) {
+                                    if (S::ROPE_BYTES > 0) cs = rs[jj * 16];
+                                    else if (n0 + c0 + jj < g.n_tok)
+                                        cs = __ldg(g.rope + (long long)min(tok_pos[c0 + jj], g.rope_positions - 1) * half + i0 + (lane >> 1));
+                                }
+                                const float mine = v[jj] + b;
+                                const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                                const float y = second ? (other * cs.y + mine * cs.x) : (mine * cs.x - other * cs.y);
+                                st[jj * 32 + (lane & 1) * 16 + (lane >> 1)] = __float2bfloat16_rn(y);     // dims i0.., then i0 + hd/2..
+                            }
+                            __syncwarp();
+                            bf16* dst_base = is_q ? (bf16*)g.out : (bf16*)(is_k ? g.cache.k_pool : g.cache.v_pool);
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {            // 16 tokens x two runs of 32 bytes = 64 pieces of 16 bytes
+                                const int id = lane + 32 * k;
+                                const int jj = id >> 2, run = (id >> 1) & 1, sub = id & 1;
+                                const int tt = c0 + jj;
+                                if (n0 + tt < g.n_tok) {
+                                    const long long at = is_q ? ((long long)(n0 + tt) * g.q_heads + head) * hd
+                                                              : tok_off[tt] + (long long)kvh * g.cache.page_size * hd;
+                                    *reinterpret_cast<uint4*>(dst_base + at + run * half + i0 + sub * 8) =
+                                        *reinterpret_cast<const uint4*>(st + jj * 32 + run * 16 + sub * 8);
+                                }
+                            }
+                            // no barrier here: the next 16 tokens go to the other staging tile, and the barrier after
+                            // their writes orders this tile's reads before its next writes
+                        }
+                        continue;
+                    }
                     const int head = row / hd, within = row % hd;
                     const int i = within >> 1;
                     const bool second = (within & 1) != 0;
@@ -347,6 +431,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 }
             }
+            if (stamps != nullptr && et == 0) stamps[7] = clock64();
             // the accumulator has been read: the tensor cores may fill it again
             tcgen05_fence_before();
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty_bar(buf)) : "memory");

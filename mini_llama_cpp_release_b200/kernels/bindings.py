@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -95,6 +95,7 @@ def core() -> ctypes.CDLL:
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
+            "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
@@ -122,7 +123,14 @@ def _check(rc: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA error {rc} at launch")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle (asked of torch directly: building a Stream object costs microseconds
+    that a step of two hundred launches notices)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -470,7 +478,9 @@ def check_gemm_status(device: torch.device) -> None:
             t.zero_()
             who = {1: "the matrix product's TMA loader", 2: "the matrix product's tensor-core issuer",
                    3: "the matrix product's epilogue", 11: "the attention kernel's TMA loader",
-                   12: "the attention kernel's tensor-core issuer", 13: "the attention kernel's softmax rows"}.get(code, str(code))
+                   12: "the attention kernel's tensor-core issuer", 13: "the attention kernel's softmax rows",
+                   21: "the prompt product's TMA loader", 22: "the prompt product's tensor-core issuer",
+                   23: "the prompt product's epilogue"}.get(code, str(code))
             raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier ({who}); its output is not valid")
 
 
@@ -489,6 +499,54 @@ def gemm_block_tokens(n_tok: int, row_tiles: int, n_sms: int) -> int:
         if n_tok <= bn:
             return bn
     return 256 if row_tiles * ((n_tok + 255) // 256) >= n_sms else 128
+
+
+def gemm_rows_takes(n_tok: int, n_out: int, k: int) -> bool:
+    """Whether the prompt form of the tcgen05 product (tokens as the M operand) takes these sizes."""
+    return n_tok > 64 and n_out % 16 == 0 and k % 8 == 0
+
+
+def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0,
+                      block_rows: Optional[int] = None, bias: Optional[torch.Tensor] = None,
+                      positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
+                      rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
+                      kv: Optional[KVView] = None, n_sms: int = 0) -> None:
+    """The tcgen05 product for prompts (csrc/gemm_tcgen05_rows.cu): bfloat16 x [n, K] times bfloat16 w [rows, K]
+    transposed, tiles of 128 tokens x `block_rows` (128 or 256) rows of w, the same epilogues as `gemm_tcgen05`;
+    EPI_ADD adds into `out` (float32 [n, rows]) with plain reads and writes."""
+    require_cuda(x, w, out, bias, positions, tok_seq, rope)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 matrix product takes bfloat16 operands")
+    if n_sms <= 0:
+        n_sms = _sm_count(x.device)
+    n_tok, K = x.shape
+    n_out = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    if K % 8 or n_out % 16:
+        raise KernelError(f"the prompt form of the tcgen05 product needs an inner size that is a multiple of 8 and "
+                          f"a multiple of 16 rows, got {K} and {n_out}")
+    if block_rows is None:
+        block_rows = 256 if ((n_tok + 127) // 128) * ((n_out + 255) // 256) >= n_sms and epilogue != EPI_QKV else 128
+    if epilogue == EPI_STORE:
+        assert out.numel() == n_tok * n_out
+    elif epilogue == EPI_ADD:
+        assert out.dtype == torch.float32 and out.numel() == n_tok * n_out
+    elif epilogue == EPI_SILU_MUL:
+        assert out.numel() == n_tok * (n_out // 2)
+    else:
+        assert out.numel() == n_tok * q_heads * head_dim and out.dtype == torch.bfloat16
+    if kv is not None:
+        assert kv.k_pool.dtype == out.dtype
+        cache = (kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset,
+                 kv.pages_per_seq, kv.page_size)
+    else:
+        cache = (None, None, None, 0, 0, 1)
+    status = gemm_status(x.device)
+    _check(core().mlc_gemm_tcgen05_rows(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
+                                        block_rows, epilogue, status.data_ptr(), n_sms, _ptr(bias), _ptr(positions),
+                                        _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
+                                        kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product (prompt form)")
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, n_splits: int = 1,

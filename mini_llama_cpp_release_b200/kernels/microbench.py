@@ -100,6 +100,32 @@ def bench_gemm(args) -> None:
         report(f"library product T={T} N={N} K={K}", lambda i: torch.mm(x, ws[i % C].t(), out_dtype=torch.float32, out=out),
                args, nbytes + T * N * 4, flops)
         return
+    if args.rows_form:
+        hd, KV = args.head_dim, args.kv_heads
+        if epi == 0:
+            out = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+            kw = {}
+        elif epi == 3:
+            out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+            kw = {}
+        elif epi == 1:
+            out = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
+            kw = {}
+        else:
+            H = N // hd - 2 * KV
+            n_pages = (T + 63) // 64 + 1
+            k_pool = torch.zeros(1, n_pages, KV, 64, hd, dtype=torch.bfloat16, device=DEV)
+            v_pool = torch.zeros_like(k_pool)
+            table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, n_pages)
+            from ..parts.rotary import neox_inv_freq
+            kw = dict(bias=torch.randn(N, device=DEV), positions=torch.arange(T, dtype=torch.int32, device=DEV),
+                      tok_seq=torch.zeros(T, dtype=torch.int32, device=DEV),
+                      rope=kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), max(T, 64)), q_heads=H, kv_heads=KV, head_dim=hd,
+                      kv=bindings.KVView(k_pool, v_pool, 0, table, 64, KV, hd))
+            out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
+        fn = lambda i: kernels.gemm_tcgen05_rows(x, ws[i % C], out, epi, args.block_tokens, **kw)
+        report(f"tcgen05 product, prompt form T={T} N={N} K={K} epilogue={args.epilogue}", fn, args, nbytes + out.numel() * out.element_size(), flops)
+        return
     if epi == 0:
         out = torch.empty(args.splits, T, N, dtype=torch.float32, device=DEV)
         fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 0, args.splits, args.block_tokens, **norm)
@@ -188,6 +214,7 @@ def main(argv=None) -> int:
     ap.add_argument("--block-tokens", type=int, default=None)
     ap.add_argument("--copies", type=int, default=24)
     ap.add_argument("--library", action="store_true")
+    ap.add_argument("--rows-form", action="store_true", help="the prompt form of the product (tokens as the M operand)")
     ap.add_argument("--once", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--seqs", type=int, default=8)

@@ -120,7 +120,12 @@ class GQAttention(Part):
                 self.q_only = Linear(self.qkv.weight[: self.H * self.hd], rt)   # a view of the fused rows
             proj = self.q_only
             bias = self.bias[: self.H * self.hd] if self.bias is not None else None
-        if self.fused:
+        if self.fused and kernels.gemm_rows_takes(n, proj.weight.shape[0], self.hidden) and self.hd % 16 == 0:
+            # prompts: tokens as the M operand, a thread of the epilogue holds a token's rotation pairs
+            kernels.gemm_tcgen05_rows(h, proj.weight, q, kernels.bindings.EPI_QKV, bias=bias, positions=step.positions,
+                                      tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
+                                      kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms)
+        elif self.fused:
             kernels.gemm_tcgen05(h, proj.weight, q, kernels.bindings.EPI_QKV, bias=bias, positions=step.positions,
                                  tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
                                  kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms,

@@ -326,6 +326,90 @@ def test_tcgen05_product_refuses_what_it_cannot_take():
         kernels.gemm_tcgen05(x.float(), w, torch.empty(1, 4, 8, device=DEV))
 
 
+# ------------------------------------------------------------------ the prompt form of the tcgen05 product
+@pytest.mark.parametrize("T,N,K,bn", [(128, 128, 64, 128), (65, 144, 72, None), (300, 784, 200, 128), (600, 272, 128, 256),
+                                      (2048, 1152, 896, None), (130, 40000, 72, 256), (257, 16, 8, 128)])
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+def test_prompt_product_plain_store(T, N, K, bn, out_dtype):
+    g = torch.Generator().manual_seed(T + N)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    out = torch.full((T, N), float("nan"), dtype=DT[out_dtype], device=DEV)
+    kernels.gemm_tcgen05_rows(x.to(DEV), w.to(DEV), out, 0, bn)
+    kernels.check_gemm_status(DEV)
+    close(out.float(), x.double() @ w.double().t(), 3e-6 if out_dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("T,I,K,bn", [(70, 344, 128, None), (200, 104, 72, 128), (300, 4864, 896, 256)])
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+def test_prompt_product_with_silu_mul_epilogue(T, I, K, bn, out_dtype):
+    g = torch.Generator().manual_seed(I)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    gate = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    up = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()          # g0, u0, g1, u1, ...
+    out = torch.full((T, I), float("nan"), dtype=DT[out_dtype], device=DEV)
+    kernels.gemm_tcgen05_rows(x.to(DEV), w.to(DEV), out, 1, bn)
+    kernels.check_gemm_status(DEV)
+    gg, uu = x.float() @ gate.float().t(), x.float() @ up.float().t()
+    close(out.float(), gg * (1 / (1 + torch.exp(-gg))) * uu, 2e-5 if out_dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("H,KV,hd,T,bn", [(6, 3, 32, 70, None), (14, 2, 64, 300, 128), (3, 1, 16, 129, 128), (2, 2, 80, 130, 128),
+                                          (2, 1, 256, 65, None), (5, 1, 48, 200, None)])
+def test_prompt_product_with_bias_rotation_and_cache_write(H, KV, hd, T, bn):
+    K = 72
+    g = torch.Generator().manual_seed(hd)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((H + 2 * KV) * hd, K, generator=g) * 0.3).to(torch.bfloat16)
+    bias = torch.randn((H + 2 * KV) * hd, generator=g)
+    half = hd // 2
+    within = torch.stack([torch.arange(half), torch.arange(half) + half], dim=1).reshape(-1)
+    order = (torch.arange(H + 2 * KV)[:, None] * hd + within[None, :]).reshape(-1)
+    lens = [T - T // 3 + 66, T // 3]
+    q_lens = [T - T // 3, T // 3]
+    positions = torch.cat([torch.arange(n - m, n) for n, m in zip(lens, q_lens)]).to(torch.int32)
+    tok_seq = torch.cat([torch.full((m,), b) for b, m in enumerate(q_lens)]).to(torch.int32)
+    kv = make_paged([torch.zeros(n, KV, hd) for n in lens], [torch.zeros(n, KV, hd) for n in lens], torch.bfloat16)
+    table = kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), 512)
+    q_out = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05_rows(x.to(DEV), w[order].contiguous().to(DEV), q_out, 2, bn, bias=bias[order].contiguous().to(DEV),
+                              positions=positions.to(DEV), tok_seq=tok_seq.to(DEV), rope=table, q_heads=H, kv_heads=KV,
+                              head_dim=hd, kv=kv)
+    kernels.check_gemm_status(DEV)
+    full = x.float() @ w.float().t() + bias
+    q_want = plain_impl.rope_neox(full[:, :H * hd].reshape(T, H, hd), positions, 1e6)
+    k_want = plain_impl.rope_neox(full[:, H * hd:(H + KV) * hd].reshape(T, KV, hd), positions, 1e6)
+    v_want = full[:, (H + KV) * hd:].reshape(T, KV, hd)
+    close(q_out.float().view(T, H, hd), q_want, 8e-3)
+    pages = kv.page_table.cpu()
+    k_got = torch.stack([kv.k_pool[1, int(pages[tok_seq[n], positions[n] // 64]), :, positions[n] % 64].float().cpu() for n in range(T)])
+    v_got = torch.stack([kv.v_pool[1, int(pages[tok_seq[n], positions[n] // 64]), :, positions[n] % 64].float().cpu() for n in range(T)])
+    close(k_got, k_want, 8e-3)
+    close(v_got, v_want, 8e-3)
+    assert torch.isnan(kv.k_pool[0].float()).all()
+
+
+@pytest.mark.parametrize("T,N,K,bn", [(128, 896, 4864, None), (70, 144, 896, 128), (300, 272, 1000, 256)])
+def test_prompt_product_adding_into_the_stream(T, N, K, bn):
+    g = torch.Generator().manual_seed(N + K)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+    stream0 = torch.randn(T, N, generator=g)
+    stream = stream0.clone().to(DEV)
+    kernels.gemm_tcgen05_rows(x.to(DEV), w.to(DEV), stream, 3, bn)
+    kernels.check_gemm_status(DEV)
+    # one float32 accumulator runs over all K terms here (no K splits): rounding grows like sqrt(K) * 2^-24
+    close(stream, stream0.double() + x.double() @ w.double().t(), 3 * math.sqrt(K) * 2.0 ** -24)
+
+
+def test_prompt_product_refuses_what_it_cannot_take():
+    x = torch.zeros(70, 24, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(kernels.KernelError, match="multiple of 16 rows"):
+        kernels.gemm_tcgen05_rows(x, torch.zeros(40, 24, dtype=torch.bfloat16, device=DEV), torch.empty(70, 40, device=DEV))
+    assert not kernels.gemm_rows_takes(70, 40, 24) and not kernels.gemm_rows_takes(8, 48, 24) and kernels.gemm_rows_takes(70, 48, 24)
+
+
 def test_norm_and_gather_add_up_split_partial_sums():
     x, parts, gain = torch.randn(5, 72), torch.randn(7, 5, 72), torch.ones(72)
     xd = x.clone().to(DEV)
