@@ -93,6 +93,81 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const float* __re
     }
 }
 
+// Many rows (prompts): one warp per row, the row held in registers between the sum of squares and the scaling, so
+// that every element is read once and the loads of a row are all in flight together; no block-wide barrier.
+// NV = 16-byte pieces per lane (d <= 128 * NV).
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_slices, long long slice_stride,
+                        const float* __restrict__ gain, float eps, int d, int n, T* __restrict__ out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const long long base = (long long)row * d;
+    const int d4 = d >> 2;
+    float4* x4 = reinterpret_cast<float4*>(x + base);
+    float4 v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane + 32 * k;
+        v[k] = (i < d4) ? x4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (delta != nullptr) {
+        for (int s = 0; s < n_slices; ++s) {
+            const float4* t4 = reinterpret_cast<const float4*>(delta + s * slice_stride + base);
+#pragma unroll
+            for (int k = 0; k < NV; ++k) {
+                const int i = lane + 32 * k;
+                if (i < d4) {
+                    const float4 t = __ldg(t4 + i);
+                    v[k].x += t.x; v[k].y += t.y; v[k].z += t.z; v[k].w += t.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int i = lane + 32 * k;
+            if (i < d4) x4[i] = v[k];
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane + 32 * k;
+        if (i < d4) {
+            const float4 g = __ldg(g4 + i);
+            const float a = v[k].x * scale * g.x, b = v[k].y * scale * g.y, c = v[k].z * scale * g.z, e = v[k].w * scale * g.w;
+            if (sizeof(T) == 4) {
+                reinterpret_cast<float4*>(out + base)[i] = make_float4(a, b, c, e);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+                reinterpret_cast<uint2*>(out + base)[i] = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+            }
+        }
+    }
+}
+
+template <typename T>
+static cudaError_t launch_rmsnorm_warp(int nv, float* x, const float* delta, int n_slices, long long stride, const float* gain,
+                                       float eps, int d, int n, T* out, cudaStream_t s) {
+    const dim3 grid((n + 7) / 8), block(256);
+    switch (nv) {
+        case 1: return launch_pdl(add_rmsnorm_warp_kernel<T, 1>, grid, block, 0, s, x, delta, n_slices, stride, gain, eps, d, n, out);
+        case 2: return launch_pdl(add_rmsnorm_warp_kernel<T, 2>, grid, block, 0, s, x, delta, n_slices, stride, gain, eps, d, n, out);
+        case 3: case 4: return launch_pdl(add_rmsnorm_warp_kernel<T, 4>, grid, block, 0, s, x, delta, n_slices, stride, gain, eps, d, n, out);
+        case 5: case 6: case 7: case 8:
+            return launch_pdl(add_rmsnorm_warp_kernel<T, 8>, grid, block, 0, s, x, delta, n_slices, stride, gain, eps, d, n, out);
+        default: return launch_pdl(add_rmsnorm_warp_kernel<T, 16>, grid, block, 0, s, x, delta, n_slices, stride, gain, eps, d, n, out);
+    }
+}
+
 // ------------------------------------------------------------------ rotation table
 // table[p][i] = (cos(p·f_i), sin(p·f_i)), the angle formed in float32 from an integer
 // position and a float32 frequency, as src/ops.cpp:132-134 does for each token.
@@ -286,7 +361,12 @@ extern "C" int mlc_add_rmsnorm(float* x, const float* delta, int n_slices, const
     cudaError_t e;
     const bool vec = (d & 3) == 0 && n > 64 &&
                      ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)gain) | ((uintptr_t)out)) & 15) == 0;
-    if (vec && out_dtype == MLC_DTYPE_F32)
+    const int nv = ((d >> 2) + 31) / 32;                 // 16-byte pieces per lane if a warp takes a row
+    if (vec && nv <= 16 && n >= 256 && out_dtype == MLC_DTYPE_F32)
+        e = launch_rmsnorm_warp<float>(nv, x, delta, n_slices, stride, gain, eps, d, n, (float*)out, s);
+    else if (vec && nv <= 16 && n >= 256 && out_dtype == MLC_DTYPE_BF16)
+        e = launch_rmsnorm_warp<bf16>(nv, x, delta, n_slices, stride, gain, eps, d, n, (bf16*)out, s);
+    else if (vec && out_dtype == MLC_DTYPE_F32)
         e = launch_pdl(add_rmsnorm_vec4_kernel<float>, dim3(n), dim3(row_threads(d >> 2)), 0, s, x, delta, n_slices, stride, gain, eps, d, (float*)out);
     else if (vec && out_dtype == MLC_DTYPE_BF16)
         e = launch_pdl(add_rmsnorm_vec4_kernel<bf16>, dim3(n), dim3(row_threads(d >> 2)), 0, s, x, delta, n_slices, stride, gain, eps, d, (bf16*)out);

@@ -45,6 +45,20 @@ def test_add_rmsnorm(d, dtype):
         close(out.float(), plain_impl.rmsnorm(s, gain, 1e-5), 2e-6 if dtype == "float32" else 5e-3)
 
 
+@pytest.mark.parametrize("n,d,slices", [(300, 896, 1), (257, 72, 3), (1000, 2048, 0), (256, 132, 1), (400, 3584, 2)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_add_rmsnorm_of_many_rows(n, d, slices, dtype):
+    """Prompts: a warp per row (rows of up to 2,048 elements), partial sums in several slices added first."""
+    torch.manual_seed(n + d)
+    x, delta, gain = torch.randn(n, d) * 3, torch.randn(max(slices, 1), n, d), 1 + 0.1 * torch.randn(d)
+    xd = x.clone().to(DEV)
+    out = torch.empty(n, d, dtype=DT[dtype], device=DEV)
+    kernels.add_rmsnorm(xd, delta.to(DEV) if slices else None, gain.to(DEV), 1e-6, out)
+    s = x + delta.sum(0) if slices else x
+    assert torch.allclose(xd.cpu(), s, atol=2e-6)
+    close(out.float(), plain_impl.rmsnorm(s, gain, 1e-6), 3e-6 if dtype == "float32" else 5e-3)
+
+
 def test_eps_sits_inside_the_square_root():
     x = torch.zeros(1, 64, device=DEV)
     x[0, 0] = 1e-3
