@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -60,14 +61,6 @@ class Context:
     def describe(self, batch: MiniBatch) -> StepInfo:
         """Reserve pages for the batch's tokens and put its description on the device."""
         cache = self.cache
-        tokens: List[int] = []
-        positions: List[int] = []
-        tok_seq: List[int] = []
-        cu = [0]
-        start_pos: List[int] = []
-        slots: List[int] = []
-        want_rows: List[int] = []
-        max_q = max_kv = 0
         for c in batch.chunks:
             if c.slot not in cache.length:
                 raise ValueError(f"forward_batch: slot {c.slot} is not held")
@@ -78,38 +71,28 @@ class Context:
                     f"{self.max_position}")                                          # src/forward.cpp:23-25
         for c in batch.chunks:
             cache.reserve(c.slot, len(c.tokens))
-        for b, c in enumerate(batch.chunks):
-            start = cache.length[c.slot]
-            n = len(c.tokens)
-            base = len(tokens)
-            tokens.extend(c.tokens)
-            positions.extend(range(start, start + n))
-            tok_seq.extend([b] * n)
-            cu.append(base + n)
-            start_pos.append(start)
-            slots.append(c.slot)
-            want_rows.extend(base + w for w in c.want)
-            max_q = max(max_q, n)
-            max_kv = max(max_kv, start + n)
+        B = len(batch.chunks)
+        slots = [c.slot for c in batch.chunks]
+        lens = [len(c.tokens) for c in batch.chunks]
+        start_pos = [cache.length[s] for s in slots]
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        n_tokens = cu[-1]
+        want_rows = [cu[b] + w for b, c in enumerate(batch.chunks) for w in c.want]
+        max_q = max(lens)
+        max_kv = max(s + n for s, n in zip(start_pos, lens))
         n_groups = len(cache.groups)
-        tables: List[List[int]] = []
-        widths: List[int] = []
-        for g in range(n_groups):
-            width = max(1, max(len(cache.page_lists[s][g]) for s in slots))
-            widths.append(width)
-            flat: List[int] = []
-            for s in slots:
-                pl = cache.page_lists[s][g]
-                flat.extend(pl)
-                flat.extend([-1] * (width - len(pl)))
-            tables.append(flat)
-        # one host buffer (pinned once and reused; an event says when the last copy out of it is done), one copy
-        segments = [tokens, positions, tok_seq, cu, start_pos, slots, want_rows, *tables]
+        widths = [max(1, max(len(cache.page_lists[s][g]) for s in slots)) for g in range(n_groups)]
+        # one host buffer (pinned once and reused; an event says when the last copy out of it is done), one copy.
+        # Segments: tokens, positions, sequence of each token, first token of each sequence, first position of each
+        # sequence, slots, wanted rows, then one page table per cache group; each 16-byte aligned.
+        sizes = [n_tokens, n_tokens, n_tokens, B + 1, B, B, len(want_rows)] + [B * w for w in widths]
         offsets = []
         total = 0
-        for seg_list in segments:
+        for size in sizes:
             offsets.append(total)
-            total += (len(seg_list) + 3) // 4 * 4                # keep every segment 16-byte aligned
+            total += (size + 3) // 4 * 4
         if getattr(self, "_pinned", None) is None or self._pinned.numel() < total:
             self._pinned = torch.empty(max(total, 4096) * 2, dtype=torch.int32).pin_memory()
             self._pinned_np = self._pinned.numpy()
@@ -117,8 +100,24 @@ class Context:
         if self._pinned_event is not None:
             self._pinned_event.synchronize()
         host_np = self._pinned_np
-        for off, seg_list in zip(offsets, segments):
-            host_np[off:off + len(seg_list)] = seg_list
+        # the per-token segments are filled a sequence at a time, as arrays: a prompt of thousands of tokens is not
+        # walked in Python
+        for b, c in enumerate(batch.chunks):
+            lo, n = cu[b], lens[b]
+            host_np[offsets[0] + lo: offsets[0] + lo + n] = c.tokens
+            host_np[offsets[1] + lo: offsets[1] + lo + n] = np.arange(start_pos[b], start_pos[b] + n, dtype=np.int32)
+            host_np[offsets[2] + lo: offsets[2] + lo + n] = b
+        host_np[offsets[3]: offsets[3] + B + 1] = cu
+        host_np[offsets[4]: offsets[4] + B] = start_pos
+        host_np[offsets[5]: offsets[5] + B] = slots
+        host_np[offsets[6]: offsets[6] + len(want_rows)] = want_rows
+        for g in range(n_groups):
+            w = widths[g]
+            table = host_np[offsets[7 + g]: offsets[7 + g] + B * w].reshape(B, w)
+            table[:] = -1
+            for b, s in enumerate(slots):
+                pl = cache.page_lists[s][g]
+                table[b, :len(pl)] = pl
         dev = torch.empty(total, dtype=torch.int32, device=self.model.runtime.device)
         dev.copy_(self._pinned[:total], non_blocking=True)
         self._pinned_event = torch.cuda.Event()
@@ -127,12 +126,11 @@ class Context:
         def seg(i: int, n: int) -> torch.Tensor:
             return dev[offsets[i]: offsets[i] + n]
 
-        B = len(slots)
         page_tables = [seg(7 + g, B * widths[g]).view(B, widths[g]) for g in range(n_groups)]
         slots_dev = seg(5, B)
         return StepInfo(
-            n_tokens=len(tokens), n_seqs=B, max_q_len=max_q, max_kv_len=max_kv,
-            tokens=seg(0, len(tokens)), positions=seg(1, len(tokens)), tok_seq=seg(2, len(tokens)),
+            n_tokens=n_tokens, n_seqs=B, max_q_len=max_q, max_kv_len=max_kv,
+            tokens=seg(0, n_tokens), positions=seg(1, n_tokens), tok_seq=seg(2, n_tokens),
             cu_seqlens=seg(3, B + 1), start_pos=seg(4, B), slots=slots_dev, want_rows=seg(6, len(want_rows)),
             page_tables=page_tables, slots_long=slots_dev.long(),
         )
