@@ -310,7 +310,7 @@ def main() -> int:
             "hidden": 896, "heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864, "vocab": 151936,
             "tied_head": True, "global_batch": args.batch, "prompt_len": PROMPT_LEN, "seq_len": CTX_LEN,
             "decode_steps": steps, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + cache per step)",
-            "peaks": pk["source"],
+            "peaks": pk["source"], "prefill_step": "the repeated step shape replays a captured CUDA graph",
         },
         "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches * steps, "library_gemm_launches": lib_launches * steps,

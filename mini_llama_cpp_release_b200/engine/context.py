@@ -58,8 +58,9 @@ class Context:
         return self.cache.length[slot]
 
     # ------------------------------------------------------------------ the step
-    def describe(self, batch: MiniBatch) -> StepInfo:
-        """Reserve pages for the batch's tokens and put its description on the device."""
+    def _describe_host(self, batch: MiniBatch) -> dict:
+        """Reserve pages for the batch's tokens and write the step's description into the pinned host buffer; returns
+        its layout (segment offsets and the sizes the host needs)."""
         cache = self.cache
         for c in batch.chunks:
             if c.slot not in cache.length:
@@ -118,36 +119,108 @@ class Context:
             for b, s in enumerate(slots):
                 pl = cache.page_lists[s][g]
                 table[b, :len(pl)] = pl
-        dev = torch.empty(total, dtype=torch.int32, device=self.model.runtime.device)
-        dev.copy_(self._pinned[:total], non_blocking=True)
+        return dict(total=total, offsets=offsets, n_tokens=n_tokens, n_seqs=B, max_q=max_q, max_kv=max_kv,
+                    widths=widths, n_want=len(want_rows))
+
+    def _upload(self, layout: dict, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The description `_describe_host` left in the pinned buffer, copied to the device (into `into` if given)."""
+        total = layout["total"]
+        if into is None:
+            into = torch.empty(total, dtype=torch.int32, device=self.model.runtime.device)
+        into.copy_(self._pinned[:total], non_blocking=True)
         self._pinned_event = torch.cuda.Event()
         self._pinned_event.record()
+        return into
+
+    def describe(self, batch: MiniBatch) -> StepInfo:
+        """Reserve pages for the batch's tokens and put its description on the device."""
+        layout = self._describe_host(batch)
+        return self._step_over(self._upload(layout), layout)
+
+    @staticmethod
+    def _step_key(layout: dict) -> tuple:
+        """Everything about a step that the host bakes into launches (grids, strides, the kernels chosen); whatever else
+        differs between two steps lies in the description on the device."""
+        return (layout["n_tokens"], layout["n_seqs"], layout["max_q"], layout["max_kv"], tuple(layout["widths"]),
+                layout["n_want"])
+
+    def _step_over(self, dev: torch.Tensor, layout: dict) -> StepInfo:
+        """The step's description as views of `dev`, the int32 buffer `describe` filled."""
+        offsets, B, n_tokens, widths = layout["offsets"], layout["n_seqs"], layout["n_tokens"], layout["widths"]
 
         def seg(i: int, n: int) -> torch.Tensor:
             return dev[offsets[i]: offsets[i] + n]
 
-        page_tables = [seg(7 + g, B * widths[g]).view(B, widths[g]) for g in range(n_groups)]
+        page_tables = [seg(7 + g, B * widths[g]).view(B, widths[g]) for g in range(len(widths))]
         slots_dev = seg(5, B)
         return StepInfo(
-            n_tokens=n_tokens, n_seqs=B, max_q_len=max_q, max_kv_len=max_kv,
+            n_tokens=n_tokens, n_seqs=B, max_q_len=layout["max_q"], max_kv_len=layout["max_kv"],
             tokens=seg(0, n_tokens), positions=seg(1, n_tokens), tok_seq=seg(2, n_tokens),
-            cu_seqlens=seg(3, B + 1), start_pos=seg(4, B), slots=slots_dev, want_rows=seg(6, len(want_rows)),
+            cu_seqlens=seg(3, B + 1), start_pos=seg(4, B), slots=slots_dev, want_rows=seg(6, layout["n_want"]),
             page_tables=page_tables, slots_long=slots_dev.long(),
         )
+
+    # A step of many tokens is some two hundred launches issued from Python; when its kernels are fast the host
+    # becomes the limit.  A shape of step that comes again (the same numbers of tokens and sequences, the same
+    # longest lengths: fixed-size prompts, a benchmark, chunks of a fixed size) is therefore captured into a CUDA
+    # graph the second time it is seen and replayed from then on; everything that may differ between two such
+    # steps (tokens, positions, lengths, pages) lies in the description buffer the graph reads.
+    STEP_GRAPHS = 4                     # captured shapes kept
+    STEP_GRAPH_MIN_TOKENS = 64          # smaller steps are cheap to issue
 
     def forward_batch(self, batch: MiniBatch) -> torch.Tensor:
         """Run the batch's tokens; returns float32 logits [number of wanted places, vocab], in
         the order of the batch's sequences and of each one's `want`."""
         batch.validate(self.model.config.vocab_size)
-        with torch.cuda.device(self.model.runtime.device):
-            step = self.describe(batch)
-            logits = self.model.forward(step, self.cache)
-            kernels.check_gemm_status(self.model.runtime.device)      # a tensor-core kernel that gave up a wait is an error
+        dev = self.model.runtime.device
+        with torch.cuda.device(dev):
+            n_new = sum(len(c.tokens) for c in batch.chunks)
+            if self.use_graphs and n_new >= self.STEP_GRAPH_MIN_TOKENS:
+                logits = self._forward_maybe_replayed(batch)
+            else:
+                step = self.describe(batch)
+                logits = self.model.forward(step, self.cache)
+            kernels.check_gemm_status(dev)      # a tensor-core kernel that gave up a wait is an error
         for c in batch.chunks:
             self.cache.commit(c.slot, len(c.tokens))
             self.token_history[c.slot].extend(c.tokens)                      # src/batch.cpp:49
         self.n_steps += 1
         return logits
+
+    def _forward_maybe_replayed(self, batch: MiniBatch) -> torch.Tensor:
+        graphs = self.__dict__.setdefault("_step_graphs", {})
+        seen = self.__dict__.setdefault("_step_shapes_seen", {})
+        dev = self.model.runtime.device
+        layout = self._describe_host(batch)
+        key = self._step_key(layout)
+        entry = graphs.get(key)
+        if entry is not None:
+            self._upload(layout, into=entry["dev"])
+            entry["graph"].replay()
+            graphs[key] = graphs.pop(key)                                     # most recently used last
+            return entry["logits"].clone()
+        seen[key] = seen.get(key, 0) + 1
+        if len(seen) > 64:
+            seen.pop(next(iter(seen)))
+        own = self._upload(layout)
+        if seen[key] < 2:
+            return self.model.forward(self._step_over(own, layout), self.cache)
+        # second time: run it once more eagerly on a side stream (what capture needs), then capture and replay
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(stream):
+            self.model.forward(self._step_over(own, layout), self.cache)
+        torch.cuda.current_stream(dev).wait_stream(stream)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            logits = self.model.forward(self._step_over(own, layout), self.cache)
+        torch.cuda.synchronize(dev)
+        while len(graphs) >= self.STEP_GRAPHS:
+            graphs.pop(next(iter(graphs)))
+        graphs[key] = dict(graph=graph, dev=own, logits=logits)
+        graph.replay()
+        return logits.clone()
 
     # ------------------------------------------------------------------ decoding through a captured graph
     def _runner(self, n_seqs: int, need_len: int, sampler) -> DecodeRunner:

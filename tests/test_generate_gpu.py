@@ -57,6 +57,36 @@ def test_first_tokens_of_a_sequence(dtype):
     ctx.release(s)
 
 
+@pytest.mark.parametrize("name", ["C", "W"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_shape_of_step_that_comes_again_is_replayed_with_the_new_contents(name, dtype):
+    """Steps of the same shape (the same numbers of tokens and sequences, the same longest lengths) are captured the
+    second time and replayed afterwards; tokens, the lengths of the shorter sequences and the slots differ each time."""
+    folder = model_folder(name)
+    pm = plain_model(folder)
+    ctx = helpers.engine(folder, dtype).context
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    graphs_before = len(ctx.__dict__.get("_step_graphs", {}))
+    for round_ in range(5):
+        a = random_tokens(90, vocab, 100 + round_)
+        b = random_tokens(40 + round_, vocab, 200 + round_)          # 130 + round_ tokens in all: make them 140 with c
+        c = random_tokens(140 - 90 - len(b), vocab, 300 + round_)
+        seqs = [a, b, c]
+        slots = [ctx.acquire() for _ in seqs]
+        if round_ % 2:
+            slots.reverse()                                             # other slots, other pages
+        got = ctx.forward_batch(MiniBatch.prefill(slots, seqs))
+        for i, toks in enumerate(seqs):
+            assert rel_err(got[i], pm.logits(toks)[-1]) <= TOL[dtype], (round_, i)
+        # and the cache the replayed step filled is the one decoding continues from
+        nxt = ctx.forward_batch(MiniBatch.single(slots[1], 7))
+        assert rel_err(nxt[0], pm.logits(b + [7])[-1]) <= TOL[dtype], round_
+        for s_ in slots:
+            ctx.release(s_)
+    assert len(ctx._step_graphs) == graphs_before + 1
+    ctx.cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_crosses_pages_and_split_boundaries(dtype):
     folder = model_folder("C")
