@@ -46,6 +46,7 @@ struct TcAttnArgs {
     int q_heads, kv_heads, group;
     int heads_per_block, tokens_per_block, head_chunks;
     int window;
+    int n_splits;               // blocks that share out a row tile's keys: one cluster, merged through distributed shared memory
     float scale_log2;
     int* status;
     long long* timing;          // optional [blocks][16] clock cycles spent in each phase by the first softmax warp (0-7)
@@ -62,7 +63,9 @@ constexpr int A_STAGES = 3;
 constexpr int A_Q_BYTES = A_KB * A_BM * 128;
 constexpr int A_TILE_BYTES = A_KB * A_BN * 128;        // one K or V page of one head
 constexpr int A_P_BYTES = A_BM * 128;
-constexpr int A_BAR_BYTES = 256 + 1024;                // barriers, then the row sums' exchange [2][128] floats
+constexpr int A_BAR_BYTES = 256 + 1024 + 1024;         // barriers, the row sums' exchange [2][128] floats, a split's (max, sum) [128][2]
+constexpr int A_PART_STRIDE = A_HD + 4;                // floats between rows of a split's partial output (padded against bank conflicts)
+static_assert(A_BM * A_PART_STRIDE * 4 <= 2 * 3 * (A_HD / 64) * 64 * 128, "a split's partial output reuses the K and V stages");
 constexpr int A_THREADS = 64 + 256;
 constexpr int A_SMEM_BYTES = A_Q_BYTES + 2 * A_STAGES * A_TILE_BYTES + 2 * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
 constexpr int A_TMEM_COLS = 256;                       // two score buffers of 64 columns, the output's A_HD
@@ -84,8 +87,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // ---- which rows: heavy blocks (late tokens see the most keys) first
     // blocks are handed out x first: every sequence's and head's last rows before anyone's earlier rows
     const int heads_y = a.kv_heads * a.head_chunks;
-    const int b = blockIdx.x / heads_y;
-    const int kvh = (blockIdx.x % heads_y) / a.head_chunks, chunk = blockIdx.x % a.head_chunks;
+    const int split = blockIdx.x % a.n_splits, xh = blockIdx.x / a.n_splits;      // the splits of a row tile are one cluster
+    const int b = xh / heads_y;
+    const int kvh = (xh % heads_y) / a.head_chunks, chunk = xh % a.head_chunks;
     const int tok0 = (gridDim.y - 1 - blockIdx.y) * a.tokens_per_block;
 
     extern __shared__ unsigned char smem_dyn[];
@@ -144,8 +148,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int start = a.start_pos[b];
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
-    const int tile_begin = lo_block / A_BN;
-    const int n_tiles = (n_tok > 0) ? p_last / A_BN + 1 - tile_begin : 0;
+    const bool active = n_tok > 0;                                   // the same for every block of a cluster
+    const int tiles_all = active ? p_last / A_BN + 1 - lo_block / A_BN : 0;
+    const int tiles_per_split = (tiles_all + a.n_splits - 1) / a.n_splits;
+    const int tile_begin = lo_block / A_BN + split * tiles_per_split;
+    const int n_tiles = max(0, min(tiles_per_split, tiles_all - split * tiles_per_split));
+    const bool clustered = a.n_splits > 1 && active;
+    auto cluster_sync = [&]() {
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    };
     const int* pages = a.page_table + (long long)b * a.pages_per_seq;
     const int seq_last = start + q_len - 1;                          // the sequence's last key
 
@@ -188,6 +199,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 page_v = page_k;
                 page_k = page_next;
             }
+        }
+        if (clustered) {                       // every thread of the cluster meets at both barriers of the merge
+            cluster_sync();
+            cluster_sync();
         }
     } else if (warp == 1) {
         // ---------------- tensor-core issuer
@@ -246,7 +261,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
 #undef MLC_PHASE
         }
-    } else if (n_tiles > 0) {
+        if (clustered) {
+            cluster_sync();
+            cluster_sync();
+        }
+    } else if (active) {
         // ---------------- two threads per row: warps 2-5 take keys 0-31 of every tile and the first half of the output's
         // columns, warps 6-9 keys 32-63 and the second half.  Both read all 64 scores for the maximum, so they agree on
         // the scale without exchanging anything; only the row sums meet at the end.
@@ -375,7 +394,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_arrive(p_full(i));
             MLC_PHASE(5)                                   // rescaling
         }
-        if (ok) ok = mbar_wait(o_full((n_tiles - 1) & 1), ((unsigned)(n_tiles - 1) >> 1) & 1u, a.status, 13);
+        if (ok && n_tiles > 0) ok = mbar_wait(o_full((n_tiles - 1) & 1), ((unsigned)(n_tiles - 1) >> 1) & 1u, a.status, 13);
         MLC_PHASE(6)                                       // waiting for the last product
         if (stamp && lane == 0) {
             long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
@@ -388,15 +407,85 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         l_part[half * 128 + r] = l;
         asm volatile("bar.sync 1, 256;" ::: "memory");                                 // the softmax warps only
         l += l_part[(half ^ 1) * 128 + r];
-        if (ok) {
-            tcgen05_fence_after();
-            const float inv = 1.0f / l;
-            bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD + half * O_COLS;
+        tcgen05_fence_after();
+        bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD + half * O_COLS;
+        float* part_o = reinterpret_cast<float*>(smem_generic + A_Q_BYTES);           // [128][A_PART_STRIDE], over the K and V stages
+        float* part_ml = reinterpret_cast<float*>(smem_generic + bar_off + 256 + 1024);   // [128][2]
+        if (clustered && split > 0) {
+            // this block's share of the keys: leave (max, sum, unnormalised output) in shared memory for the first block.
+            // The stages are free: every tile that was loaded has been multiplied.
+#pragma unroll
+            for (int c0 = 0; c0 < O_COLS; c0 += 32) {
+                float v[32];
+                if (n_tiles > 0) tmem_load32(o_taddr + (unsigned)c0, v);
+                else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = 0.0f;
+                }
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                    *reinterpret_cast<float4*>(part_o + r * A_PART_STRIDE + half * O_COLS + c0 + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+            }
+            if (half == 0) {
+                part_ml[2 * r] = m;
+                part_ml[2 * r + 1] = l;
+            }
+        }
+        if (clustered) cluster_sync();
+        if (!clustered || split == 0) {
+            // merge the other blocks' shares (the first block always has tiles), normalise, store
+            float scale_own = 1.0f, l_all = l;
+            unsigned peer_o[3], peer_ml[3];
+            float peer_f[3];
+            const int n_peers = clustered ? a.n_splits - 1 : 0;
+            if (n_peers > 0) {
+                float m_all = m, mk[3], lk[3];
+                const unsigned o_local = smem_u32(part_o), ml_local = smem_u32(part_ml);
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    mk[k] = -INFINITY;
+                    lk[k] = 0.0f;
+                    if (k >= n_peers) continue;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_o[k]) : "r"(o_local), "r"(k + 1));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_ml[k]) : "r"(ml_local), "r"(k + 1));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mk[k]) : "r"(peer_ml[k] + 8u * r));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lk[k]) : "r"(peer_ml[k] + 8u * r + 4u));
+                    m_all = fmaxf(m_all, mk[k]);
+                }
+                const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
+                scale_own = fast_exp2(m - m_ref);
+                l_all = l * scale_own;
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    peer_f[k] = fast_exp2(mk[k] - m_ref);                   // 0 for a block that saw nothing (or is not there)
+                    l_all += lk[k] * peer_f[k];
+                }
+            }
+            const float inv = 1.0f / l_all;
 #pragma unroll
             for (int c0 = 0; c0 < O_COLS; c0 += 32) {
                 float v[32];
                 tmem_load32(o_taddr + (unsigned)c0, v);          // every lane of the warp takes part in the load
-                if (row_ok) {
+                if (n_peers > 0) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] *= scale_own;
+#pragma unroll
+                    for (int k = 0; k < 3; ++k) {
+                        if (k >= n_peers) continue;
+                        const unsigned base_k = peer_o[k] + 4u * (unsigned)(r * A_PART_STRIDE + half * O_COLS + c0);
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4) {
+                            float4 p;
+                            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(p.x), "=f"(p.y), "=f"(p.z), "=f"(p.w) : "r"(base_k + 4u * c));
+                            v[c] = fmaf(p.x, peer_f[k], v[c]);
+                            v[c + 1] = fmaf(p.y, peer_f[k], v[c + 1]);
+                            v[c + 2] = fmaf(p.z, peer_f[k], v[c + 2]);
+                            v[c + 3] = fmaf(p.w, peer_f[k], v[c + 3]);
+                        }
+                    }
+                }
+                if (row_ok && ok) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         unsigned w[4];
@@ -410,6 +499,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
         }
+        if (clustered) cluster_sync();             // nobody leaves while its shared memory may still be read
         if (stamp && lane == 0) {
             long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
             dst[14] = t_role - t_entry;
@@ -438,17 +528,18 @@ using namespace mlc;
 // q, out: bfloat16 [n_tokens][q_heads*hd], 16-byte aligned; the cache entry starts `entry_offset` elements into the
 // pools and holds `pool_pages` pages of 64 tokens, [page][kv_head][64][hd].  hd is the head size the library was
 // built for (64 or 128; other sizes and pages of another length are refused with MLC_ERR_UNSUPPORTED).  status: one int on the device, 0 before the call; a bounded wait that
-// ran out leaves 11, 12 or 13 there.  timing: null, or [blocks][16] int64 that receive the clock cycles one softmax
+// ran out leaves 11, 12 or 13 there.  n_splits (1, 2 or 4): that many blocks, one cluster, share out each row tile's keys
+// and merge through distributed shared memory: for steps with too few row tiles to fill the GPU.  timing: null, or [blocks][16] int64 that receive the clock cycles one softmax
 // warp (0-6; 7 is the block's number of tiles) and the issuing thread (8-13) of each block spent in their phases.
 extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
                                      int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
-                                     int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
+                                     int n_splits, int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
                                      int pages_per_seq, int page_size, long long pool_pages, long long* timing, void* stream) {
 #if MLC_ATTENTION_TCGEN05
     if (hd != A_HD || page_size != A_BN) return MLC_ERR_UNSUPPORTED;
     if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return 0;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || status == nullptr || pool_pages <= 0) return MLC_ERR_BAD_SIZE;
-    if (!(scale > 0.0f) || window < 0) return MLC_ERR_BAD_SIZE;
+    if (!(scale > 0.0f) || window < 0 || n_splits < 1 || n_splits > 4) return MLC_ERR_BAD_SIZE;
     if ((((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) || (entry_offset & 7)) return MLC_ERR_BAD_SIZE;
     const int group = q_heads / kv_heads;
     TcAttnArgs a{};
@@ -464,6 +555,7 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
     a.tokens_per_block = A_BM / a.heads_per_block;
     a.head_chunks = (group + a.heads_per_block - 1) / a.heads_per_block;
     a.window = window;
+    a.n_splits = n_splits;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.status = status;
     a.timing = timing;
@@ -492,9 +584,30 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const dim3 grid(kv_heads * a.head_chunks * n_seqs, (max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, 1);
+    const dim3 grid(kv_heads * a.head_chunks * n_seqs * n_splits, (max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, 1);
     if (grid.y > 65535) return MLC_ERR_BAD_SIZE;
-    cudaError_t e = launch_pdl(attention_tcgen05_kernel, grid, dim3(A_THREADS), (size_t)A_SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(A_THREADS);
+    cfg.dynamicSmemBytes = (size_t)A_SMEM_BYTES;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (n_splits > 1) {                        // blockIdx.x = (sequence, head, split): the splits of a row tile are neighbours
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = (unsigned)n_splits;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_kernel, mq, mk, mv, a);
     return e == cudaSuccess ? 0 : (int)e;
 #else
     return MLC_ERR_UNSUPPORTED;

@@ -54,13 +54,14 @@ constexpr int R_A_BYTES = R_BM * R_BK * 2;
 template <int BN> struct RowsShape {
     static constexpr int B_BYTES = BN * R_BK * 2;
     static constexpr int STAGE_BYTES = R_A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN <= 128) ? 6 : 4;
+    static constexpr int STAGES_FIT = (227 * 1024 - 256 - 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_FIT < 6 ? STAGES_FIT : 6;
     static constexpr int THREADS = 64 + 256;
-    static constexpr int TMEM_COLS = 2 * BN;                          // two accumulators
+    static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;    // two accumulators of BN columns; allocations are powers of two
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024 /* alignment slack */;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of a block");
-    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "tensor memory of a block");
+    static_assert(BN % 32 == 0 && BN >= 128 && BN <= 256, "rows of W per tile");
 };
 
 __device__ __forceinline__ unsigned pack2(float a, float b) {
@@ -260,7 +261,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     if (n >= g.n_out) break;
                     float v[32];
                     tmem_load32(t_addr + (unsigned)c0, v);
-                    const bool second = n + 16 < g.n_out;             // n_out is a multiple of 16: the chunk has 16 or 32 columns
+                    // n_out and the group's share of the tile are multiples of 16: the chunk has 16 or 32 columns
+                    const bool second = n + 16 < g.n_out && c0 + 32 <= COLS_PER_GROUP;
                     if (!tok_ok) continue;
                     if (EPI == R_EPI_STORE) {
                         if (g.out_dtype == MLC_DTYPE_BF16) {
@@ -346,6 +348,9 @@ static int launch_rows(const CUtensorMap& mx, const CUtensorMap& mw, const RowsA
 template <int EPI>
 static int dispatch_rows(int bn, const CUtensorMap& mx, const CUtensorMap& mw, const RowsArgs& g, int n_sms, cudaStream_t s) {
     if (bn == 128) return launch_rows<128, EPI>(mx, mw, g, n_sms, s);
+    if (bn == 160) return launch_rows<160, EPI>(mx, mw, g, n_sms, s);
+    if (bn == 192) return launch_rows<192, EPI>(mx, mw, g, n_sms, s);
+    if (bn == 224) return launch_rows<224, EPI>(mx, mw, g, n_sms, s);
     if (bn == 256) return launch_rows<256, EPI>(mx, mw, g, n_sms, s);
     return MLC_ERR_BAD_SIZE;
 }
@@ -355,7 +360,7 @@ static int dispatch_rows(int bn, const CUtensorMap& mx, const CUtensorMap& mw, c
 using namespace mlc;
 
 // x: bfloat16 [n_tok][K]; w: bfloat16 [n_out][K]; K a multiple of 8, n_out a multiple of 16, everything 16-byte
-// aligned.  block_rows: 128 or 256 rows of W per tile.  epilogue 0: out [n_tok][n_out] float32 or bfloat16; 1: out
+// aligned.  block_rows: 128, 160, 192, 224 or 256 rows of W per tile.  epilogue 0: out [n_tok][n_out] float32 or bfloat16; 1: out
 // [n_tok][n_out/2]; 2: out = q [n_tok][q_heads*hd] bfloat16, k and v go to the bfloat16 cache (hd a multiple of 16; block_rows 128);
 // 3: adds into out, float32 [n_tok][n_out].  status: one int on the device, 0 before the call; a bounded wait that
 // ran out leaves 21 (loader), 22 (tensor cores) or 23 (epilogue) there.  n_sms: blocks to launch at most.

@@ -122,7 +122,7 @@ def attention_case(lens, q_lens, H, KV, hd, dtype, window=0, n_splits=1, seed=0,
     part_o = torch.empty(N * H * n_splits * hd, device=DEV) if n_splits > 1 and not in_cluster else None
     if impl == "tcgen05":
         kernels.attention_tcgen05(q.view(N, H * hd), out.view(N, H * hd), cu, start, len(lens), max(q_lens), H, kv,
-                                  1.0 / math.sqrt(hd), window)
+                                  1.0 / math.sqrt(hd), window, n_splits=n_splits)
         torch.cuda.synchronize()
         kernels.check_gemm_status(DEV)
     elif impl == "mma":
@@ -342,7 +342,8 @@ def test_tcgen05_product_refuses_what_it_cannot_take():
 
 # ------------------------------------------------------------------ the prompt form of the tcgen05 product
 @pytest.mark.parametrize("T,N,K,bn", [(128, 128, 64, 128), (65, 144, 72, None), (300, 784, 200, 128), (600, 272, 128, 256),
-                                      (2048, 1152, 896, None), (130, 40000, 72, 256), (257, 16, 8, 128)])
+                                      (2048, 1152, 896, None), (130, 40000, 72, 256), (257, 16, 8, 128), (300, 1000 * 16, 72, 224),
+                                      (129, 496, 136, 160), (200, 2000, 64, 192)])
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 def test_prompt_product_plain_store(T, N, K, bn, out_dtype):
     g = torch.Generator().manual_seed(T + N)
@@ -354,7 +355,8 @@ def test_prompt_product_plain_store(T, N, K, bn, out_dtype):
     close(out.float(), x.double() @ w.double().t(), 3e-6 if out_dtype == "float32" else 8e-3)
 
 
-@pytest.mark.parametrize("T,I,K,bn", [(70, 344, 128, None), (200, 104, 72, 128), (300, 4864, 896, 256)])
+@pytest.mark.parametrize("T,I,K,bn", [(70, 344, 128, None), (200, 104, 72, 128), (300, 4864, 896, 256), (2048, 4864, 72, 224),
+                                      (140, 1000, 64, 160)])
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 def test_prompt_product_with_silu_mul_epilogue(T, I, K, bn, out_dtype):
     g = torch.Generator().manual_seed(I)
@@ -404,7 +406,7 @@ def test_prompt_product_with_bias_rotation_and_cache_write(H, KV, hd, T, bn):
     assert torch.isnan(kv.k_pool[0].float()).all()
 
 
-@pytest.mark.parametrize("T,N,K,bn", [(128, 896, 4864, None), (70, 144, 896, 128), (300, 272, 1000, 256)])
+@pytest.mark.parametrize("T,N,K,bn", [(128, 896, 4864, None), (70, 144, 896, 128), (300, 272, 1000, 256), (300, 464, 200, 224)])
 def test_prompt_product_adding_into_the_stream(T, N, K, bn):
     g = torch.Generator().manual_seed(N + K)
     x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
@@ -568,6 +570,27 @@ def test_tcgen05_attention_window_edge_and_far_key(window):
         q[-1] = 0; q[-1, :, 5] = 16.0
         v[3] = 7.0
     got, want, _ = attention_case([900], [40], 14, 2, 64, "bfloat16", scale_up=one_far_key, impl="tcgen05")
+    close(got, want, 1e-2)
+    assert float((got[-1] - 7.0).abs().max()) < 0.2
+
+
+@pytest.mark.parametrize("n_splits", [2, 4])
+@pytest.mark.parametrize("H,KV,hd", [(14, 2, 64), (8, 2, 128), (3, 3, 64)])
+def test_tcgen05_attention_shares_out_the_keys_inside_a_cluster(H, KV, hd, n_splits):
+    kw = dict(impl="tcgen05", n_splits=n_splits)
+    got, want, _ = attention_case([7, 1, 130, 64], [7, 1, 130, 64], H, KV, hd, "bfloat16", **kw)      # splits without keys
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([700, 257], [700, 130], H, KV, hd, "bfloat16", seed=3, **kw)
+    close(got, want, 1e-2)
+    got, want, _ = attention_case([900, 300], [40, 300], H, KV, hd, "bfloat16", window=200, seed=4, **kw)
+    close(got, want, 1e-2)
+
+    def one_far_key(qs, ks, vs):
+        q, k, v = qs[0], ks[0], vs[0]
+        k[3] = 0; k[3, :, 5] = 16.0
+        q[-1] = 0; q[-1, :, 5] = 16.0
+        v[3] = 7.0
+    got, want, _ = attention_case([900], [40], H, KV, hd, "bfloat16", scale_up=one_far_key, **kw)
     close(got, want, 1e-2)
     assert float((got[-1] - 7.0).abs().max()) < 0.2
 
