@@ -7,9 +7,12 @@
 // decoded tokens and tiles a prompt of thousands.  K runs in steps of 64 elements (one
 // 128-byte swizzle span per row) through a ring of shared-memory stages:
 //     warp 0   one thread issues the TMA loads of the W tile and the activation tile;
-//     warp 1   allocates tensor memory, one thread issues tcgen05.mma and commits;
-//     warps 2-5 (2-9 for tiles of 64 tokens and more) read the accumulators with tcgen05.ld (each warp its 32
-//                lanes) and run the epilogue.
+//     warp 1   allocates tensor memory, one thread issues tcgen05.mma and commits; for tiles of up to 32 tokens a
+//              thread of each of warps 2-4 issues too: the four take K steps in turn into accumulators of their own (an issue
+//              costs its thread about sixty clocks however small the product, and one thread's rate would bound the
+//              K loop);
+//     the next four warps (eight for tiles of 64 tokens and more) read the accumulators with tcgen05.ld (each warp its
+//              32 lanes), add the issuers' accumulators and run the epilogue.
 // A K range can be split over blocks (blockIdx.z); partial sums then go to separate slices of
 // the output and the consumer adds them.
 //
@@ -64,21 +67,29 @@ template <int BN, int EPI> struct GemmShape {
     static constexpr int B_BYTES = BN * G_BK * 2;
     static constexpr int STAGE_BYTES = G_A_BYTES + B_BYTES;
     static constexpr int EPI_GROUPS = (BN >= 64) ? 2 : 1;            // epilogue warps: four per group, groups share out the tokens
-    static constexpr int THREADS = 64 + 128 * EPI_GROUPS;
+    // Threads that issue tcgen05.mma.  An issue costs the thread some sixty clocks and a wait on a stage's barrier twice
+    // that, whatever the size of the product: with few tokens (tiny products) one thread's issue rate, not the tensor
+    // cores, bounds the K loop.  Four threads then take K steps in turn, each into accumulators of its own; the epilogue
+    // adds them.
+    static constexpr int ISSUERS = (BN <= 32) ? 4 : 1;
+    static constexpr int THREADS = 32 + 32 * ISSUERS + 128 * EPI_GROUPS;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;                // tensor-memory columns of one accumulator
-    static constexpr int TMEM_COLS = 2 * ACC_COLS;                    // two accumulators: one is read out while the other fills
+    static constexpr int TMEM_COLS = 2 * ISSUERS * ACC_COLS;          // per issuer two accumulators: one is read out while the other fills
     static constexpr int META_BYTES = BN * 16;                        // per token: position, cache offset (QKV epilogue)
     // SILU_MUL: [8 or 4 warps][tokens][16 outputs] bfloat16; QKV: [8 or 4 warps][2 buffers][16 tokens][32 outputs] bfloat16
     static constexpr int STAGING_BYTES = (EPI == EPI_SILU_MUL) ? 128 * BN : (EPI == EPI_QKV ? EPI_GROUPS * 4 * 2048 : 0);
     // QKV: cos and sin of each warp's 16 rotation pairs for the tokens of its group, [warps][tokens][16] float2
     static constexpr int ROPE_BYTES = (EPI == EPI_QKV && BN <= 128) ? 4 * BN * 128 : 0;
-    static constexpr int BAR_BYTES = 256;
+    static constexpr int BAR_BYTES = 512;                           // up to 16 stages: full 0-15, empty 16-31, accumulators 32-35, slot 36
     static constexpr int FIXED_BYTES = STAGING_BYTES + ROPE_BYTES + BAR_BYTES + META_BYTES + 1024 /* alignment slack */;
     static constexpr int STAGES_FIT = (227 * 1024 - FIXED_BYTES) / STAGE_BYTES;
-    static constexpr int STAGES_WANTED = (BN <= 64) ? 8 : (BN <= 128 ? 6 : (EPI == EPI_SILU_MUL ? 3 : 4));
-    static constexpr int STAGES = STAGES_FIT < STAGES_WANTED ? STAGES_FIT : STAGES_WANTED;
+    // Few tokens: the whole K range of a 896-wide layer (14 steps) fits the ring, so that all of a tile's weights are
+    // requested before the wait for the kernel before (they depend on nothing) and arrive while it finishes.
+    static constexpr int STAGES_WANTED = (BN <= 32) ? 12 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : (EPI == EPI_SILU_MUL ? 3 : 4)));
+    // a multiple of ISSUERS: stage s then always belongs to issuer s % ISSUERS, who sees its barrier's phases in order
+    static constexpr int STAGES = (STAGES_FIT < STAGES_WANTED ? STAGES_FIT : STAGES_WANTED) / ISSUERS * ISSUERS;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIXED_BYTES;
-    static_assert(STAGES >= 2, "stage ring");
+    static_assert(STAGES >= 2 && STAGES <= 16, "stage ring");
 };
 
 template <typename T> __device__ __forceinline__ void store_out(void* base, long long idx, float v) {
@@ -116,11 +127,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     constexpr unsigned bar_off = rope_off + S::ROPE_BYTES;
     const unsigned bar_base = base + bar_off;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (8 + s); };
-    auto acc_full_bar = [&](int b) { return bar_base + 8u * (16 + b); };
-    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (18 + b); };
-    const unsigned tmem_slot = bar_base + 8u * 20;
-    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 20);
+    auto empty_bar = [&](int s) { return bar_base + 8u * (16 + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (32 + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (34 + b); };
+    const unsigned tmem_slot = bar_base + 8u * 36;
+    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 36);
     int* tok_pos = reinterpret_cast<int*>(smem_generic + bar_off + S::BAR_BYTES);                         // [BN]
     long long* tok_off = reinterpret_cast<long long*>(tok_pos + BN);                                      // [BN]
 
@@ -135,7 +146,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_full_bar(b), S::ISSUERS);
             mbar_init(acc_empty_bar(b), 128 * EG);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -183,20 +194,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: tile j accumulates in buffer j % 2 once the epilogue has emptied it
+    } else if (warp <= S::ISSUERS) {
+        // ---------------- MMA issuers: tile j accumulates in buffer j % 2 (of each issuer) once the epilogue has emptied
+        // it; issuer u takes the tile's K steps u, u + ISSUERS, ...
         if (lane == 0) {
             constexpr unsigned idesc = umma_idesc(BN);
+            const int u = warp - 1;
             int it = 0, j = 0;
             bool ok = true;
+            int total_it = 0;                  // K steps of all of this block's tiles: a stage is handed back only if needed again
+            for (int t = blockIdx.x; t < n_tiles_total; t += gridDim.x) total_it += tile_coord(g, t, BN).n_kb;
             for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
                 const TileCoord c = tile_coord(g, t, BN);
                 const int buf = j & 1;
                 ok = mbar_wait(acc_empty_bar(buf), (((unsigned)j >> 1) & 1u) ^ 1u, g.status, 2);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const unsigned d_tmem = tmem_base + (unsigned)(buf * S::ACC_COLS);
+                const unsigned d_tmem = tmem_base + (unsigned)((u * 2 + buf) * S::ACC_COLS);
+                // K steps are dealt out by their number in the block's whole sequence of steps, not by their place in the
+                // tile: a stage's barrier is then waited on by one thread only, in the order of its phases (a parity wait
+                // cannot tell a phase from the one two before it)
+                bool first = true;
                 for (int i = 0; i < c.n_kb; ++i, ++it) {
+                    if (it % S::ISSUERS != u) continue;
                     const int s = it % S::STAGES;
                     const unsigned phase = (it / S::STAGES) & 1;
                     ok = mbar_wait(full_bar(s), phase, g.status, 2);
@@ -208,21 +228,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < G_BK / 16; ++k) {
                         // 16 elements = 32 bytes further along K inside the swizzle span: +2 in address/16 units
-                        tcgen05_mma_f16(d_tmem, a_desc + 2ull * k, b_desc + 2ull * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        tcgen05_mma_f16(d_tmem, a_desc + 2ull * k, b_desc + 2ull * k, idesc, (!first || k > 0) ? 1u : 0u);
                     }
-                    tcgen05_commit(empty_bar(s));      // the stage is free once these products have read it
+                    first = false;
+                    if (it + S::STAGES < total_it) tcgen05_commit(empty_bar(s));      // the stage is free once these products have read it
                 }
                 if (!ok) break;
-                if (stamps != nullptr && j == 0) stamps[3] = global_ns();                 // first tile's last product issued
-                tcgen05_commit(acc_full_bar(buf));     // arrives when every product issued so far is done
+                if (stamps != nullptr && j == 0 && u == 0) stamps[3] = global_ns();       // first tile's last product issued
+                // arrives when every product this thread has issued is done (at once if it had no K step in this tile)
+                if (!first) tcgen05_commit(acc_full_bar(buf));
+                else mbar_arrive(acc_full_bar(buf));
             }
         }
     } else {
         // ---------------- epilogue: warp q of a group reads tensor-memory lanes 32q .. 32q+31; the groups share out
         // the tile's tokens
         const int q = warp & 3;
-        const int eg = (warp - 2) >> 2;
-        const int et = threadIdx.x - 64;                               // 0 .. 128*EG-1
+        const int eg = (warp - 1 - S::ISSUERS) >> 2;
+        const int et = threadIdx.x - 32 * (1 + S::ISSUERS);            // 0 .. 128*EG-1
         constexpr int COLS_PER_GROUP = BN / EG;
         grid_dependency_wait();                // positions, page lists and the output buffers may come from earlier kernels
         // QKV through shared memory: when a warp's 32 rows are 16 rotation pairs of one head (head sizes in steps of 32)
@@ -230,7 +253,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const bool qkv_fast = EPI == EPI_QKV && g.out_dtype == MLC_DTYPE_BF16 && (g.hd & 31) == 0 &&
                               ((((uintptr_t)g.out) | ((uintptr_t)g.cache.k_pool) | ((uintptr_t)g.cache.v_pool)) & 15) == 0 &&
                               (g.cache.entry_offset & 7) == 0;
-        int j = 0;
+        int j = 0, it_done = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
             const TileCoord c = tile_coord(g, t, BN);
@@ -279,6 +302,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tcgen05_fence_after();
             if (stamps != nullptr && et == 0 && j == 0) { stamps[4] = global_ns(); stamps[6] = -clock64(); }
             const unsigned d_tmem = tmem_base + (unsigned)(buf * S::ACC_COLS);
+            // issuers that had a K step in this tile: steps it0 .. it0 + n_kb - 1 of the block's sequence, dealt out in turn
+            const int it0 = it_done;
+            it_done += c.n_kb;
             const int row = m0 + q * 32 + lane;
             const float bias_row = (EPI == EPI_QKV && g.bias != nullptr && row < g.n_out) ? __ldg(g.bias + row) : 0.0f;
             // SiLU epilogue through shared memory: bfloat16 output, a full 16-output group inside the matrix, aligned rows
@@ -288,7 +314,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll (EPI == EPI_QKV ? 2 : 1)
             for (int c0 = eg * COLS_PER_GROUP; c0 < (eg + 1) * COLS_PER_GROUP; c0 += 16) {
                 float v[16];
-                tmem_load16(d_tmem + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+                if (S::ISSUERS == 1) tmem_load16(d_tmem + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+                if (S::ISSUERS > 1) {
+                    bool have = false;
+#pragma unroll
+                    for (int u = 0; u < S::ISSUERS; ++u) {
+                        const int first_step = it0 + ((u - it0 % S::ISSUERS) + S::ISSUERS) % S::ISSUERS;
+                        if (first_step < it0 + c.n_kb) {                // the same for the whole block
+                            float w[16];
+                            tmem_load16(d_tmem + (unsigned)(u * 2 * S::ACC_COLS) + ((unsigned)(q * 32) << 16) + (unsigned)c0, w);
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) v[e] = have ? v[e] + w[e] : w[e];
+                            have = true;
+                        }
+                    }
+                }
                 if (EPI == EPI_ADD) {
                     if (row < g.n_out) {
 #pragma unroll

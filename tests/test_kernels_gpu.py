@@ -270,6 +270,23 @@ def test_tcgen05_product_plain_store(T, N, K, bn, splits, out_dtype):
     close(out.float().sum(0), x.double() @ w.double().t(), 3e-6 if out_dtype == "float32" else 8e-3)
 
 
+@pytest.mark.parametrize("T,N,K", [(8, 40000, 448), (8, 151936, 896), (24, 30000, 200), (3, 25000, 1104)])
+def test_tcgen05_product_blocks_that_walk_many_tiles_with_several_issuing_threads(T, N, K):
+    """Few tokens: four threads issue the products, taking K steps in turn through the stage ring, over many tiles per
+    block and K step counts (7, 14, 4, 18) that do and do not divide by four; several runs, since what would go wrong is
+    a matter of timing."""
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.5).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    xd, wd = x.to(DEV), w.to(DEV)
+    for _ in range(5):
+        out = torch.full((1, T, N), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.gemm_tcgen05(xd, wd, out, 0, 1)
+        kernels.check_gemm_status(DEV)
+        close(out[0], want, 3e-6)
+
+
 @pytest.mark.parametrize("T,I,K", [(5, 344, 128), (64, 100, 72), (300, 4864, 896)])
 def test_tcgen05_product_with_silu_mul_epilogue(T, I, K):
     g = torch.Generator().manual_seed(I)
