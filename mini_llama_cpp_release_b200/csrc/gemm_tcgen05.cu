@@ -166,6 +166,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // ---------------- TMA producer: one stream of (tile, K block) pairs through the stage ring.  The weights do
         // not depend on the kernels before this one: the first ring of weight tiles is requested before the wait for
         // those kernels, the activations after it.
+        // The first ring of the first tile is requested by one lane per stage, so that the requests go out together
+        // (a single thread needs some hundred clocks per request, and the activations' requests sit on the critical path
+        // right after the wait).
+        const TileCoord c0 = tile_coord(g, blockIdx.x, BN);
+        const int early = (blockIdx.x < n_tiles_total) ? min(c0.n_kb, S::STAGES) : 0;
+        if (lane < early) {
+            mbar_expect_tx(full_bar(lane), S::STAGE_BYTES);
+            tma_load_2d(a_base + lane * G_A_BYTES, &map_w, (c0.kb_begin + lane) * G_BK, c0.m0, full_bar(lane));
+        }
+        grid_dependency_wait();
+        if (lane < early) tma_load_2d(b_base + lane * S::B_BYTES, &map_x, (c0.kb_begin + lane) * G_BK, c0.n0, full_bar(lane));
         if (lane == 0) {
             int it = 0;
             bool alive = true;
@@ -173,14 +184,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const TileCoord c = tile_coord(g, t, BN);
                 int i = 0;
                 if (it == 0) {
-                    const int early = min(c.n_kb, S::STAGES);
-                    for (; i < early; ++i) {
-                        mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
-                        tma_load_2d(a_base + i * G_A_BYTES, &map_w, (c.kb_begin + i) * G_BK, c.m0, full_bar(i));
-                    }
-                    grid_dependency_wait();
-                    for (int e = 0; e < early; ++e)
-                        tma_load_2d(b_base + e * S::B_BYTES, &map_x, (c.kb_begin + e) * G_BK, c.n0, full_bar(e));
+                    i = early;
                     it = early;
                 }
                 for (; i < c.n_kb; ++i, ++it) {
