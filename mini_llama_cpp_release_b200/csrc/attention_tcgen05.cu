@@ -8,13 +8,16 @@
 //     warp 0     one thread issues the TMA loads: the query rows once, then a ring of K and V pages;
 //     warp 1     allocates tensor memory; one thread issues tcgen05.mma: S_j = Q·K_jᵀ into one of two
 //                score buffers, and O += P_j·V_j (V is the MN-major operand, read as the cache holds it);
-//     warps 2-9  two threads per row (each 32 of a tile's keys): read the row's 64 scores from tensor memory, mask where the tile
-//                meets the diagonal, a window's edge or padding rows, keeps the running maximum and sum
-//                in float32, writes P_j = exp2(s·scale·log2e − m) as bfloat16 into shared memory for the
-//                tensor cores.  The output accumulates in tensor memory; when a row's maximum rises by more than
-//                2^8 the row's thread rescales its lane of the output there before O_j is added.
-// The tensor cores compute S_{j+1} and O_j while the rows work on tile j.  With a head size of 64 two
-// blocks share an SM, so one block's exponentials overlap the other's products.
+//     warps 2-9  two teams of four warps, one thread per row each; team 0 takes the even tiles, team 1 the odd ones.
+//                A thread reads its row's 64 scores from tensor memory (twice: for the maximum, then for the
+//                probabilities), masks where the tile meets the diagonal, a window's edge or padding rows, keeps the
+//                team's running maximum and sum in float32, and writes P_j = exp2(s·scale·log2e − m) as bfloat16 into
+//                shared memory for the tensor cores.  Each team's output accumulates in tensor memory; when a row's
+//                maximum rises by more than 2^8 the row's thread rescales its lane of the output there before O_j is
+//                added.  At the end the teams exchange each row's (maximum, sum) and every thread adds and stores half of
+//                the row's columns.
+// A block has two tiles in flight (one per team) and the scores of the two after them; with a head size of 64 two
+// blocks share an SM besides.
 //
 // Pages are handed out dirty.  Keys beyond a row's range give scores that are replaced, not multiplied; values
 // beyond the sequence's last key would meet probabilities of exactly zero, but 0 x NaN is NaN, so the rows of
@@ -46,11 +49,10 @@ struct TcAttnArgs {
     int q_heads, kv_heads, group;
     int heads_per_block, tokens_per_block, head_chunks;
     int window;
-    int n_splits;               // blocks that share out a row tile's keys: one cluster, merged through distributed shared memory
     float scale_log2;
     int* status;
-    long long* timing;          // optional [blocks][16] clock cycles spent in each phase by the first softmax warp (0-7)
-                                // and by the issuing thread (8-15), for tuning; or null
+    long long* timing;          // optional [blocks][16] clock cycles the first softmax warp spent in each phase (0-4), the
+                                // block's tiles (7), cycles from entry to the role's start (14) and end (15); or null
 };
 
 #if MLC_ATTENTION_TCGEN05
@@ -63,13 +65,11 @@ constexpr int A_STAGES = 3;
 constexpr int A_Q_BYTES = A_KB * A_BM * 128;
 constexpr int A_TILE_BYTES = A_KB * A_BN * 128;        // one K or V page of one head
 constexpr int A_P_BYTES = A_BM * 128;
-constexpr int A_BAR_BYTES = 256 + 1024 + 1024;         // barriers, the row sums' exchange [2][128] floats, a split's (max, sum) [128][2]
-constexpr int A_PART_STRIDE = A_HD + 4;                // floats between rows of a split's partial output (padded against bank conflicts)
-static_assert(A_BM * A_PART_STRIDE * 4 <= 2 * 3 * (A_HD / 64) * 64 * 128, "a split's partial output reuses the K and V stages");
+constexpr int A_BAR_BYTES = 256 + 2048;                // barriers, then the teams' (maximum, sum) of every row [2][128][2] floats
 constexpr int A_THREADS = 64 + 256;
 constexpr int A_SMEM_BYTES = A_Q_BYTES + 2 * A_STAGES * A_TILE_BYTES + 2 * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
-constexpr int A_TMEM_COLS = 256;                       // two score buffers of 64 columns, the output's A_HD
-static_assert(2 * A_BN + A_HD <= A_TMEM_COLS, "tensor memory of a block");
+constexpr int A_TMEM_COLS = (2 * A_BN + 2 * A_HD <= 256) ? 256 : 512;     // two score buffers of 64 columns, two outputs of A_HD
+static_assert(2 * A_BN + 2 * A_HD <= A_TMEM_COLS, "tensor memory of a block");
 constexpr int A_BLOCKS_PER_SM = (A_HD == 64) ? 2 : 1;
 static_assert(A_SMEM_BYTES * A_BLOCKS_PER_SM <= 226 * 1024, "shared memory of the blocks of one SM");
 
@@ -83,13 +83,11 @@ __global__ void __launch_bounds__(A_THREADS, A_BLOCKS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, TcAttnArgs a) {
     const int t_entry = (int)clock();
-    const unsigned long long g_entry = global_ns();
-    // ---- which rows: heavy blocks (late tokens see the most keys) first
-    // blocks are handed out x first: every sequence's and head's last rows before anyone's earlier rows
+    // ---- which rows: blocks are handed out x first, every sequence's and head's last rows (which see the most keys)
+    // before anyone's earlier rows
     const int heads_y = a.kv_heads * a.head_chunks;
-    const int split = blockIdx.x % a.n_splits, xh = blockIdx.x / a.n_splits;      // the splits of a row tile are one cluster
-    const int b = xh / heads_y;
-    const int kvh = (xh % heads_y) / a.head_chunks, chunk = xh % a.head_chunks;
+    const int b = blockIdx.x / heads_y;
+    const int kvh = (blockIdx.x % heads_y) / a.head_chunks, chunk = blockIdx.x % a.head_chunks;
     const int tok0 = (gridDim.y - 1 - blockIdx.y) * a.tokens_per_block;
 
     extern __shared__ unsigned char smem_dyn[];
@@ -106,13 +104,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     auto k_full = [&](int s) { return bar_base + 8u * s; };
     auto v_full = [&](int s) { return bar_base + 8u * (4 + s); };
     auto k_empty = [&](int s) { return bar_base + 8u * (8 + s); };
-    auto v_empty = [&](int s) { return bar_base + 8u * (26 + s); };
-    auto s_full = [&](int i) { return bar_base + 8u * (12 + i); };
-    auto p_full = [&](int i) { return bar_base + 8u * (16 + i); };
-    auto o_full = [&](int i) { return bar_base + 8u * (20 + i); };       // O_j complete: barrier j & 1
-    const unsigned q_full = bar_base + 8u * 24;
-    const unsigned tmem_slot = bar_base + 8u * 25;
-    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 25);
+    auto v_empty = [&](int s) { return bar_base + 8u * (12 + s); };
+    auto s_full = [&](int i) { return bar_base + 8u * (16 + i); };       // S_j complete: barrier j & 1 (the team's)
+    auto p_full = [&](int i) { return bar_base + 8u * (18 + i); };       // P_j written, O rescaled: by the team's 128 threads
+    auto o_full = [&](int i) { return bar_base + 8u * (20 + i); };       // O += P_j V_j complete
+    const unsigned q_full = bar_base + 8u * 22;
+    const unsigned tmem_slot = bar_base + 8u * 23;
+    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 23);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -124,11 +122,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full(i), 1);
-            mbar_init(p_full(i), 256);
+            mbar_init(p_full(i), 128);
+            mbar_init(o_full(i), 1);
         }
         mbar_init(q_full, 1);
-        mbar_init(o_full(0), 1);
-        mbar_init(o_full(1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -148,15 +145,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int start = a.start_pos[b];
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
-    const bool active = n_tok > 0;                                   // the same for every block of a cluster
-    const int tiles_all = active ? p_last / A_BN + 1 - lo_block / A_BN : 0;
-    const int tiles_per_split = (tiles_all + a.n_splits - 1) / a.n_splits;
-    const int tile_begin = lo_block / A_BN + split * tiles_per_split;
-    const int n_tiles = max(0, min(tiles_per_split, tiles_all - split * tiles_per_split));
-    const bool clustered = a.n_splits > 1 && active;
-    auto cluster_sync = [&]() {
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    };
+    const int tile_begin = lo_block / A_BN;
+    const int n_tiles = (n_tok > 0) ? p_last / A_BN + 1 - tile_begin : 0;
     const int* pages = a.page_table + (long long)b * a.pages_per_seq;
     const int seq_last = start + q_len - 1;                          // the sequence's last key
 
@@ -169,8 +159,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int kb = 0; kb < A_KB; ++kb)
                 tma_load_3d(q_base + kb * A_BM * 128, &map_q, kb * 64, kvh * a.group + chunk * a.heads_per_block,
                             seq_tok0 + tok0, q_full);
-            // K_j is wanted one tile before V_j (the scores run a tile ahead), and its stage is free as soon as S_j is done:
-            // the order is K_0, K_1, V_0, K_2, V_1, ...
             auto load_k = [&](int j, int page) -> bool {
                 const int s = j % A_STAGES;
                 if (!mbar_wait(k_empty(s), ((j / A_STAGES) & 1) ^ 1u, a.status, 11)) return false;
@@ -189,36 +177,30 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     tma_load_2d(v_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_v, kb * 64, row, v_full(s));
                 return true;
             };
-            int page_v = __ldg(pages + tile_begin);                                     // page of tile j
-            int page_k = (n_tiles > 1) ? __ldg(pages + tile_begin + 1) : 0;              // page of tile j + 1
-            bool alive = load_k(0, page_v);
+            // the scores run two tiles ahead of the products with V: K_0, K_1, then V_j and K_{j+2} in turn
+            int pg[3];
+            pg[0] = __ldg(pages + tile_begin);
+            pg[1] = (n_tiles > 1) ? __ldg(pages + tile_begin + 1) : 0;
+            bool alive = load_k(0, pg[0]);
+            if (alive && n_tiles > 1) alive = load_k(1, pg[1]);
             for (int j = 0; j < n_tiles && alive; ++j) {
-                const int page_next = (j + 2 < n_tiles) ? __ldg(pages + tile_begin + j + 2) : 0;
-                if (j + 1 < n_tiles) alive = load_k(j + 1, page_k);
-                if (alive) alive = load_v(j, page_v);
-                page_v = page_k;
-                page_k = page_next;
+                pg[2] = (j + 2 < n_tiles) ? __ldg(pages + tile_begin + j + 2) : 0;
+                alive = load_v(j, pg[0]);
+                if (alive && j + 2 < n_tiles) alive = load_k(j + 2, pg[2]);
+                pg[0] = pg[1];
+                pg[1] = pg[2];
             }
         }
-        if (clustered) {                       // every thread of the cluster meets at both barriers of the merge
-            cluster_sync();
-            cluster_sync();
-        }
     } else if (warp == 1) {
-        // ---------------- tensor-core issuer
+        // ---------------- tensor-core issuer: S_0, S_1, then for every tile O_{j&1} += P_j V_j and S_{j+2}
         if (lane == 0 && n_tiles > 0) {
             constexpr unsigned idesc_s = umma_idesc(A_BN);
             constexpr unsigned idesc_o = umma_idesc(A_HD, true);
-            const bool stamp = a.timing != nullptr;
-            int ph[6] = {0, 0, 0, 0, 0, 0}, t0 = 0, t1;
-#define MLC_PHASE(k) if (stamp) { t1 = (int)clock(); ph[k] += t1 - t0; t0 = t1; }
             bool ok = mbar_wait(q_full, 0, a.status, 12);
-            if (stamp) t0 = (int)clock();
             auto issue_scores = [&](int j) -> bool {
                 const int s = j % A_STAGES, i = j & 1;
                 if (!mbar_wait(k_full(s), (j / A_STAGES) & 1, a.status, 12)) return false;
-                MLC_PHASE(0)                                   // waiting for K
-                // the score buffer is free: the rows handed over P_{j-2} (seen in the last round) after reading S_{j-2}
+                // the team's score buffer is free: its rows handed over P_{j-2}, seen before O_{j-2} was issued, after reading S_{j-2}
                 tcgen05_fence_after();
                 const unsigned d = tmem_base + (unsigned)(i * A_BN);
 #pragma unroll
@@ -230,48 +212,33 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         tcgen05_mma_f16(d, qd + 2ull * k, kd + 2ull * k, idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(s_full(i));      // arrives when S_j and everything issued before it (O_{j-2} too) is complete
-                MLC_PHASE(2)                                   // issuing S
                 return true;
             };
             if (ok) ok = issue_scores(0);
+            if (ok && n_tiles > 1) ok = issue_scores(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) {
-                    ok = issue_scores(j + 1);
-                    if (!ok) break;
-                }
                 const int s = j % A_STAGES, i = j & 1;
-                ok = mbar_wait(v_full(s), (j / A_STAGES) & 1, a.status, 12);
-                MLC_PHASE(3)                                   // waiting for V
-                ok = ok && mbar_wait(p_full(i), ((unsigned)j >> 1) & 1u, a.status, 12);      // P_j written, the output rescaled
+                ok = mbar_wait(v_full(s), (j / A_STAGES) & 1, a.status, 12) &&
+                     mbar_wait(p_full(i), ((unsigned)j >> 1) & 1u, a.status, 12);      // P_j written, the team's output rescaled
                 if (!ok) break;
-                MLC_PHASE(4)                                   // waiting for P
                 tcgen05_fence_after();
-                const unsigned d = tmem_base + (unsigned)(2 * A_BN);
+                const unsigned d = tmem_base + (unsigned)(2 * A_BN + i * A_HD);
                 const unsigned long long pd = umma_desc_sw128(p_base + i * A_P_BYTES);
                 const unsigned long long vd = umma_desc_sw128_mn(v_base + s * A_TILE_BYTES, A_BN * 128);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)      // 16 keys a step: 32 bytes along a row of P, two 8-key groups of V
-                    tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j >= 2 || k > 0) ? 1u : 0u);
                 tcgen05_commit(o_full(i));
-                MLC_PHASE(5)                                   // issuing O
+                if (j + 2 < n_tiles) ok = issue_scores(j + 2);
             }
-            if (stamp) {
-                long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) + 8;
-                for (int k = 0; k < 6; ++k) dst[k] = ph[k];
-            }
-#undef MLC_PHASE
         }
-        if (clustered) {
-            cluster_sync();
-            cluster_sync();
-        }
-    } else if (active) {
-        // ---------------- two threads per row: warps 2-5 take keys 0-31 of every tile and the first half of the output's
-        // columns, warps 6-9 keys 32-63 and the second half.  Both read all 64 scores for the maximum, so they agree on
-        // the scale without exchanging anything; only the row sums meet at the end.
+    } else if (n_tiles > 0) {
+        // ---------------- two teams of four warps, one thread per row each.  Team 0 takes the even tiles, team 1 the odd
+        // ones, each with its own score buffer, P buffer, running maximum and sum and its own output accumulator in tensor
+        // memory; they meet once, at the end.  A block that is alone with a long row of tiles (the last rows of a long
+        // prompt) thus has two tiles in flight.
         const int q4 = warp & 3;
-        const int half = (warp - 2) >> 2;
-        const int st_id = threadIdx.x - 64;                 // 0 .. 255
+        const int team = (warp - 2) >> 2;
         const int r = q4 * 32 + lane;
         const int t = r / a.heads_per_block, hg = chunk * a.heads_per_block + r % a.heads_per_block;
         const bool row_ok = t < n_tok && hg < a.group && r < a.heads_per_block * a.tokens_per_block;
@@ -290,66 +257,86 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #define MLC_PHASE(k) if (stamp) { t1 = (int)clock(); ph[k] += t1 - t0; t0 = t1; }
         if (stamp) t0 = (int)clock();
         const int t_role = t0;
-        constexpr int O_COLS = A_HD / 2;                    // output columns of one thread
-        const unsigned o_taddr = tmem_base + lane_base + (unsigned)(2 * A_BN + half * O_COLS);
+        const unsigned s_taddr = tmem_base + lane_base + (unsigned)(team * A_BN);
+        const unsigned o_taddr = tmem_base + lane_base + (unsigned)(2 * A_BN + team * A_HD);
+        unsigned char* prow = smem_generic + p_off + team * A_P_BYTES + r * 128;
+        int my_tiles = 0;
 
-        for (int j = 0; j < n_tiles; ++j) {
-            const int i = j & 1;
-            ok = mbar_wait(s_full(i), ((unsigned)j >> 1) & 1u, a.status, 13);
+        for (int j = team; j < n_tiles; j += 2, ++my_tiles) {
+            ok = mbar_wait(s_full(team), ((unsigned)j >> 1) & 1u, a.status, 13);
             if (!ok) break;
             MLC_PHASE(0)                                   // waiting for the scores
             tcgen05_fence_after();
-            float s[32], u[32];                            // this thread's keys, and the other half's (for the maximum)
-            tmem_load32(tmem_base + lane_base + (unsigned)(i * A_BN + half * 32), s);
-            tmem_load32(tmem_base + lane_base + (unsigned)(i * A_BN + (half ^ 1) * 32), u);
-            tcgen05_fence_before();
-            if (threadIdx.x == 64) {
+            if (threadIdx.x == 64 + 128 * team) {
                 // S_j is complete, and with it everything the issuing thread had issued before: O_{j-2}.  Their K and V
                 // stages are free for the loader.
                 mbar_arrive(k_empty(j % A_STAGES));
                 if (j >= 2) mbar_arrive(v_empty((j - 2) % A_STAGES));
             }
             __syncwarp();
-            MLC_PHASE(1)                                   // reading them
-
             const int key0 = (tile_begin + j) * A_BN;
             // decided for the warp as a whole: lanes that went separate ways here would run everything below twice
-            if (!__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo)) {
-                const int ks = key0 + half * 32, ku = key0 + (half ^ 1) * 32;
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    s[c] = (ks + c >= lo && ks + c <= hi) ? s[c] : -INFINITY;
-                    u[c] = (ku + c >= lo && ku + c <= hi) ? u[c] : -INFINITY;
-                }
-            }
+            const bool masked = !__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo);
+
+            // first pass over the row's 64 scores: the maximum
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one of 64 links
 #pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-                mx4[0] = fmaxf(mx4[0], fmaxf(s[c], u[c]));
-                mx4[1] = fmaxf(mx4[1], fmaxf(s[c + 1], u[c + 1]));
-                mx4[2] = fmaxf(mx4[2], fmaxf(s[c + 2], u[c + 2]));
-                mx4[3] = fmaxf(mx4[3], fmaxf(s[c + 3], u[c + 3]));
+            for (int h = 0; h < 2; ++h) {
+                float s[32];
+                tmem_load32(s_taddr + (unsigned)(32 * h), s);
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int kpos = key0 + 32 * h + c;
+                        s[c] = (kpos >= lo && kpos <= hi) ? s[c] : -INFINITY;
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    mx4[0] = fmaxf(mx4[0], s[c]);
+                    mx4[1] = fmaxf(mx4[1], s[c + 1]);
+                    mx4[2] = fmaxf(mx4[2], s[c + 2]);
+                    mx4[3] = fmaxf(mx4[3], s[c + 3]);
+                }
             }
+            MLC_PHASE(1)                                   // reading them, maximum
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;   // the scale is positive
             const bool raise = mx > m + 8.0f;                         // false while nothing has been seen (-inf > -inf)
             const float m_new = raise ? mx : m;
             const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
             const float corr = raise ? fast_exp2(m - m_use) : 1.0f;   // 0 when nothing was seen before
             m = m_new;
+
+            // second pass: probabilities, their sum, P as bfloat16 into the team's swizzled shared-memory tile.  The P
+            // buffer is free: O_{j-2}, which read it, was complete when S_j was.
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            unsigned pk[16];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const float p0 = fast_exp2(fmaf(s[2 * c], a.scale_log2, -m_use));
-                const float p1 = fast_exp2(fmaf(s[2 * c + 1], a.scale_log2, -m_use));
-                ls4[(2 * c) & 3] += p0;
-                ls4[(2 * c + 1) & 3] += p1;
-                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                pk[c] = *reinterpret_cast<unsigned*>(&h);
+            for (int h = 0; h < 2; ++h) {
+                float s[32];
+                tmem_load32(s_taddr + (unsigned)(32 * h), s);
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int kpos = key0 + 32 * h + c;
+                        s[c] = (kpos >= lo && kpos <= hi) ? s[c] : -INFINITY;
+                    }
+                }
+                unsigned pk[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const float p0 = fast_exp2(fmaf(s[2 * c], a.scale_log2, -m_use));
+                    const float p1 = fast_exp2(fmaf(s[2 * c + 1], a.scale_log2, -m_use));
+                    ls4[(2 * c) & 3] += p0;
+                    ls4[(2 * c + 1) & 3] += p1;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    pk[c] = *reinterpret_cast<unsigned*>(&hh);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(prow + (((h * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             }
-            const float ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-            l = l * corr + ls;
-            MLC_PHASE(2)                                   // mask, maximum, exponentials
+            l = l * corr + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
+            MLC_PHASE(2)                                   // exponentials, writing P
 
             if (key0 + A_BN - 1 > seq_last) {
                 // the tile reaches past the sequence's last key: zero those rows of V (whole 128-byte rows, so the
@@ -358,30 +345,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 ok = mbar_wait(v_full(st), (j / A_STAGES) & 1, a.status, 13);
                 if (!ok) break;
                 const int first = max(seq_last + 1 - key0, 0), n_rows = A_BN - first;
-                for (int idx = st_id; idx < n_rows * 8 * A_KB; idx += 256) {
+                for (int idx = r; idx < n_rows * 8 * A_KB; idx += 128) {
                     const int kb = idx / (n_rows * 8), rem = idx % (n_rows * 8);
                     *reinterpret_cast<uint4*>(smem_generic + v_off + st * A_TILE_BYTES + kb * A_BN * 128 + (first + rem / 8) * 128 +
                                               (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
-            // the P buffer is free: O_{j-2}, which read it, was complete when S_j was
-            unsigned char* prow = smem_generic + p_off + i * A_P_BYTES + r * 128;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             fence_async_shared();
-            MLC_PHASE(4)                                   // writing P
-
-            if (j > 0 && __any_sync(0xffffffffu, raise)) {
-                // Rescale this warp's part of the output before P_j·V_j is added to it; O_{j-1} must be complete.  (A parity
-                // wait tells a barrier's phases k and k + 2 apart only if the barrier is known to be within one phase of k.
-                // O_j completes barrier j & 1; this thread has read S_j, which was issued after O_{j-2}, and O_{j+1} cannot
-                // be issued before this thread hands over P_{j+1}: so barrier (j-1) & 1 is at O_{j-1} or just before it.)
-                ok = mbar_wait(o_full((j - 1) & 1), ((unsigned)(j - 1) >> 1) & 1u, a.status, 13);
-                if (!ok) break;
-                tcgen05_fence_after();
+            if (j >= 2 && __any_sync(0xffffffffu, raise)) {
+                // Rescale this warp's rows of the team's output before P_j V_j is added to them.  The output is at rest:
+                // the team's last product, O_{j-2}, was complete when S_j was.
 #pragma unroll
-                for (int c0 = 0; c0 < O_COLS; c0 += 32) {
+                for (int c0 = 0; c0 < A_HD; c0 += 32) {
                     float v[32];
                     tmem_load32(o_taddr + (unsigned)c0, v);
 #pragma unroll
@@ -389,126 +364,64 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     tmem_store32(o_taddr + (unsigned)c0, v);
                 }
                 tmem_store_wait();
-                tcgen05_fence_before();
             }
-            mbar_arrive(p_full(i));
-            MLC_PHASE(5)                                   // rescaling
+            tcgen05_fence_before();
+            mbar_arrive(p_full(team));
+            MLC_PHASE(3)                                   // zeroing, rescaling, hand-over
         }
-        if (ok && n_tiles > 0) ok = mbar_wait(o_full((n_tiles - 1) & 1), ((unsigned)(n_tiles - 1) >> 1) & 1u, a.status, 13);
-        MLC_PHASE(6)                                       // waiting for the last product
+        // the team's last product: O_j completes barrier j & 1; the team has seen S of its last tile, issued after its
+        // last product but one, so the barrier is at the awaited phase or just before it
+        if (ok && my_tiles > 0) ok = mbar_wait(o_full(team), (unsigned)(my_tiles - 1) & 1u, a.status, 13);
+        MLC_PHASE(4)                                       // waiting for the last product
         if (stamp && lane == 0) {
-            long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+            long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * blockIdx.y);
             for (int k = 0; k < 7; ++k) dst[k] = ph[k];
             dst[7] = n_tiles;
         }
 #undef MLC_PHASE
-        // the two halves of a row add up their sums
-        float* l_part = reinterpret_cast<float*>(smem_generic + bar_off + 256);       // [2][128]
-        l_part[half * 128 + r] = l;
+        // ---- the teams meet: each row's two (maximum, sum) pairs cross through shared memory, then every thread takes
+        // half of the row's output columns and adds the two accumulators out of tensor memory
+        float* ml = reinterpret_cast<float*>(smem_generic + bar_off + 256);            // [2 teams][128 rows][2]
+        ml[(team * 128 + r) * 2] = m;
+        ml[(team * 128 + r) * 2 + 1] = l;
+        tcgen05_fence_before();
         asm volatile("bar.sync 1, 256;" ::: "memory");                                 // the softmax warps only
-        l += l_part[(half ^ 1) * 128 + r];
         tcgen05_fence_after();
-        bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD + half * O_COLS;
-        float* part_o = reinterpret_cast<float*>(smem_generic + A_Q_BYTES);           // [128][A_PART_STRIDE], over the K and V stages
-        float* part_ml = reinterpret_cast<float*>(smem_generic + bar_off + 256 + 1024);   // [128][2]
-        if (clustered && split > 0) {
-            // this block's share of the keys: leave (max, sum, unnormalised output) in shared memory for the first block.
-            // The stages are free: every tile that was loaded has been multiplied.
+        const float m0 = ml[r * 2], l0 = ml[r * 2 + 1], m1 = ml[(128 + r) * 2], l1 = ml[(128 + r) * 2 + 1];
+        const float m_all = fmaxf(m0, m1);
+        const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
+        const float f0 = fast_exp2(m0 - m_ref), f1 = (n_tiles > 1) ? fast_exp2(m1 - m_ref) : 0.0f;   // team 1 may have had no tile
+        const float inv = 1.0f / (l0 * f0 + l1 * f1);
+        constexpr int O_COLS = A_HD / 2;                    // output columns of one thread
+        bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD + team * O_COLS;
+        const unsigned o0 = tmem_base + lane_base + (unsigned)(2 * A_BN + team * O_COLS), o1 = o0 + (unsigned)A_HD;
 #pragma unroll
-            for (int c0 = 0; c0 < O_COLS; c0 += 32) {
-                float v[32];
-                if (n_tiles > 0) tmem_load32(o_taddr + (unsigned)c0, v);
-                else {
+        for (int c0 = 0; c0 < O_COLS; c0 += 32) {
+            float v[32], w[32];
+            tmem_load32(o0 + (unsigned)c0, v);              // every lane of the warp takes part in the loads
+            if (n_tiles > 1) tmem_load32(o1 + (unsigned)c0, w);
+            if (row_ok && ok) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = 0.0f;
-                }
+                for (int c = 0; c < 32; c += 8) {
+                    unsigned wd[4];
 #pragma unroll
-                for (int c = 0; c < 32; c += 4)
-                    *reinterpret_cast<float4*>(part_o + r * A_PART_STRIDE + half * O_COLS + c0 + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-            }
-            if (half == 0) {
-                part_ml[2 * r] = m;
-                part_ml[2 * r + 1] = l;
-            }
-        }
-        if (clustered) cluster_sync();
-        if (!clustered || split == 0) {
-            // merge the other blocks' shares (the first block always has tiles), normalise, store
-            float scale_own = 1.0f, l_all = l;
-            unsigned peer_o[3], peer_ml[3];
-            float peer_f[3];
-            const int n_peers = clustered ? a.n_splits - 1 : 0;
-            if (n_peers > 0) {
-                float m_all = m, mk[3], lk[3];
-                const unsigned o_local = smem_u32(part_o), ml_local = smem_u32(part_ml);
-#pragma unroll
-                for (int k = 0; k < 3; ++k) {
-                    mk[k] = -INFINITY;
-                    lk[k] = 0.0f;
-                    if (k >= n_peers) continue;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_o[k]) : "r"(o_local), "r"(k + 1));
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_ml[k]) : "r"(ml_local), "r"(k + 1));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mk[k]) : "r"(peer_ml[k] + 8u * r));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lk[k]) : "r"(peer_ml[k] + 8u * r + 4u));
-                    m_all = fmaxf(m_all, mk[k]);
-                }
-                const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
-                scale_own = fast_exp2(m - m_ref);
-                l_all = l * scale_own;
-#pragma unroll
-                for (int k = 0; k < 3; ++k) {
-                    peer_f[k] = fast_exp2(mk[k] - m_ref);                   // 0 for a block that saw nothing (or is not there)
-                    l_all += lk[k] * peer_f[k];
-                }
-            }
-            const float inv = 1.0f / l_all;
-#pragma unroll
-            for (int c0 = 0; c0 < O_COLS; c0 += 32) {
-                float v[32];
-                tmem_load32(o_taddr + (unsigned)c0, v);          // every lane of the warp takes part in the load
-                if (n_peers > 0) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] *= scale_own;
-#pragma unroll
-                    for (int k = 0; k < 3; ++k) {
-                        if (k >= n_peers) continue;
-                        const unsigned base_k = peer_o[k] + 4u * (unsigned)(r * A_PART_STRIDE + half * O_COLS + c0);
-#pragma unroll
-                        for (int c = 0; c < 32; c += 4) {
-                            float4 p;
-                            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                         : "=f"(p.x), "=f"(p.y), "=f"(p.z), "=f"(p.w) : "r"(base_k + 4u * c));
-                            v[c] = fmaf(p.x, peer_f[k], v[c]);
-                            v[c + 1] = fmaf(p.y, peer_f[k], v[c + 1]);
-                            v[c + 2] = fmaf(p.z, peer_f[k], v[c + 2]);
-                            v[c + 3] = fmaf(p.w, peer_f[k], v[c + 3]);
+                    for (int e = 0; e < 4; ++e) {
+                        float x0 = v[c + 2 * e] * f0, x1 = v[c + 2 * e + 1] * f0;
+                        if (n_tiles > 1) {
+                            x0 = fmaf(w[c + 2 * e], f1, x0);
+                            x1 = fmaf(w[c + 2 * e + 1], f1, x1);
                         }
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(x0 * inv, x1 * inv);
+                        wd[e] = *reinterpret_cast<unsigned*>(&hh);
                     }
-                }
-                if (row_ok && ok) {
-#pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        unsigned w[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(v[c + 2 * e] * inv, v[c + 2 * e + 1] * inv);
-                            w[e] = *reinterpret_cast<unsigned*>(&h);
-                        }
-                        *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
+                    *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
                 }
             }
         }
-        if (clustered) cluster_sync();             // nobody leaves while its shared memory may still be read
         if (stamp && lane == 0) {
-            long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-            dst[14] = t_role - t_entry;
-            dst[15] = (int)clock() - t_entry;
-            unsigned smid;
-            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            dst[6] = smid;
-            dst[12] = (long long)g_entry;
-            dst[13] = (long long)global_ns();
+            long long* dstt = a.timing + 16ll * (blockIdx.x + gridDim.x * blockIdx.y);
+            dstt[14] = t_role - t_entry;
+            dstt[15] = (int)clock() - t_entry;
         }
     }
 
@@ -528,18 +441,17 @@ using namespace mlc;
 // q, out: bfloat16 [n_tokens][q_heads*hd], 16-byte aligned; the cache entry starts `entry_offset` elements into the
 // pools and holds `pool_pages` pages of 64 tokens, [page][kv_head][64][hd].  hd is the head size the library was
 // built for (64 or 128; other sizes and pages of another length are refused with MLC_ERR_UNSUPPORTED).  status: one int on the device, 0 before the call; a bounded wait that
-// ran out leaves 11, 12 or 13 there.  n_splits (1, 2 or 4): that many blocks, one cluster, share out each row tile's keys
-// and merge through distributed shared memory: for steps with too few row tiles to fill the GPU.  timing: null, or [blocks][16] int64 that receive the clock cycles one softmax
+// ran out leaves 11, 12 or 13 there.  timing: null, or [blocks][16] int64 that receive the clock cycles one softmax
 // warp (0-6; 7 is the block's number of tiles) and the issuing thread (8-13) of each block spent in their phases.
 extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
                                      int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
-                                     int n_splits, int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
+                                     int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
                                      int pages_per_seq, int page_size, long long pool_pages, long long* timing, void* stream) {
 #if MLC_ATTENTION_TCGEN05
     if (hd != A_HD || page_size != A_BN) return MLC_ERR_UNSUPPORTED;
     if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return 0;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || status == nullptr || pool_pages <= 0) return MLC_ERR_BAD_SIZE;
-    if (!(scale > 0.0f) || window < 0 || n_splits < 1 || n_splits > 4) return MLC_ERR_BAD_SIZE;
+    if (!(scale > 0.0f) || window < 0) return MLC_ERR_BAD_SIZE;
     if ((((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) || (entry_offset & 7)) return MLC_ERR_BAD_SIZE;
     const int group = q_heads / kv_heads;
     TcAttnArgs a{};
@@ -555,7 +467,6 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
     a.tokens_per_block = A_BM / a.heads_per_block;
     a.head_chunks = (group + a.heads_per_block - 1) / a.heads_per_block;
     a.window = window;
-    a.n_splits = n_splits;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.status = status;
     a.timing = timing;
@@ -584,30 +495,9 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const dim3 grid(kv_heads * a.head_chunks * n_seqs * n_splits, (max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, 1);
+    const dim3 grid(kv_heads * a.head_chunks * n_seqs, (max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, 1);
     if (grid.y > 65535) return MLC_ERR_BAD_SIZE;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(A_THREADS);
-    cfg.dynamicSmemBytes = (size_t)A_SMEM_BYTES;
-    cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[2];
-    int n_attr = 0;
-    if (pdl_enabled()) {
-        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
-        ++n_attr;
-    }
-    if (n_splits > 1) {                        // blockIdx.x = (sequence, head, split): the splits of a row tile are neighbours
-        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-        attr[n_attr].val.clusterDim.x = (unsigned)n_splits;
-        attr[n_attr].val.clusterDim.y = 1;
-        attr[n_attr].val.clusterDim.z = 1;
-        ++n_attr;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = n_attr;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_kernel, mq, mk, mv, a);
+    cudaError_t e = launch_pdl(attention_tcgen05_kernel, grid, dim3(A_THREADS), (size_t)A_SMEM_BYTES, (cudaStream_t)stream, mq, mk, mv, a);
     return e == cudaSuccess ? 0 : (int)e;
 #else
     return MLC_ERR_UNSUPPORTED;

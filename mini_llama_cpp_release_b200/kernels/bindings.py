@@ -337,7 +337,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
         lib.mlc_attention_mma_head_dim.restype = c_int
         lib.mlc_attention_decode_clusters_resident.argtypes = [I]
         lib.mlc_attention_decode_clusters_resident.restype = c_int
-        lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, LL, I, I, LL, P, P]
+        lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P]
         lib.mlc_attention_tcgen05.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
@@ -415,11 +415,10 @@ def attention_tcgen05_blocks(max_q_len: int, n_seqs: int, q_heads: int, kv_heads
 
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
                       max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int,
-                      timing: Optional[torch.Tensor] = None, n_splits: int = 1) -> None:
+                      timing: Optional[torch.Tensor] = None) -> None:
     """Prompt attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry on the tcgen05 tensor cores
-    (head sizes 64 and 128, pages of 64 tokens).  `n_splits` (1, 2 or 4) blocks, one cluster, can share out a row
-    tile's keys and merge through distributed shared memory; measured on a 2,048-token prompt that gains 6 % with 2 and
-    loses with 4 (the clusters' placement costs more than the shorter chains save), so callers leave it at 1."""
+    (head sizes 64 and 128, pages of 64 tokens).  Keys are not shared out over blocks: meant for steps whose rows fill
+    the GPU; a block itself works on two key tiles at a time."""
     require_cuda(q, out, cu_seqlens, start_pos)
     if q.dtype != torch.bfloat16 or kv.k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("the tcgen05 attention takes bfloat16 queries, cache and output")
@@ -427,7 +426,7 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tens
     status = gemm_status(q.device)
     _check(lib.mlc_attention_tcgen05(q.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), start_pos.data_ptr(), n_seqs,
                                      q.shape[0], max_q_len, q_heads, kv.kv_heads, kv.head_dim, float(scale), int(window),
-                                     int(n_splits), status.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
+                                     status.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
                                      kv.entry_offset, kv.pages_per_seq, kv.page_size, kv.k_pool.shape[1], _ptr(timing), _stream()),
            "tcgen05 attention")
 

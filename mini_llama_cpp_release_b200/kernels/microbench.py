@@ -192,7 +192,7 @@ def bench_attention(args) -> None:
     def fn(i):
         kv = bindings.KVView(k_pool, v_pool, (i % C) * per, table, 64, KV, hd)
         if args.impl == "tcgen05":
-            kernels.attention_tcgen05(q, out, cu, start, B, q_len, H, kv, 1 / math.sqrt(hd), 0, n_splits=args.splits or 1)
+            kernels.attention_tcgen05(q, out, cu, start, B, q_len, H, kv, 1 / math.sqrt(hd), 0)
             return
         kernels.attention_mma(q, out, cu, start, B, q_len, H, kv, 1 / math.sqrt(hd), 0, row_tiles, n_splits, part_ml, part_o)
 
