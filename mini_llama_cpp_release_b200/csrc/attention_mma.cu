@@ -52,6 +52,7 @@ struct MmaArgs {
     int heads_per_block;
     int head_chunks;
     int n_splits;
+    int one_token_each;       // decode kernel: every sequence brings exactly one token, so sequence b's token is token b
     int cluster_merge;        // decode kernel: the blocks of one row tile form a cluster and merge their key splits through
                               // distributed shared memory instead of part_ml / part_o and a second kernel
 };
@@ -418,22 +419,43 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     grid_launch_dependents();
     grid_dependency_wait();                    // queries and the step's keys were written by the kernel before
     const int b = blockIdx.z;
-    // The sequence's page list is fetched at once, before its length is known: one trip to memory instead of
-    // two dependent ones (lengths, then pages).
-    for (int t = threadIdx.x; t < c.pages_per_seq && t < MAX_TILES_STAGED; t += DNW * 32)
-        tile_pages[t] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int y = blockIdx.y;
     const int split = y % a.n_splits;  y /= a.n_splits;
     const int chunk = y % a.head_chunks;  y /= a.head_chunks;
     const int kvh = y;
     const int tok0 = blockIdx.x * a.tokens_per_block;
-    const int seq_tok0 = a.cu_seqlens[b];
-    const int q_len = a.cu_seqlens[b + 1] - seq_tok0;
-    if (tok0 >= q_len) return;
-    const int start = a.start_pos[b];
-    const int n_tok = min(a.tokens_per_block, q_len - tok0);
     const int GH = a.heads_per_block;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // Everything that does not depend on anything else is asked of memory at once: the sequence's page list (before its
+    // length is known), its position, its first token, and, when every sequence brings exactly one token (then sequence
+    // b's token is token b), the query rows themselves.  Two trips to memory lie between the start and the first keys
+    // then (pages, keys) instead of four (first token, queries, pages, keys).
+    for (int t = tid; t < c.pages_per_seq && t < MAX_TILES_STAGED; t += DNW * 32)
+        tile_pages[t] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
+    const int start = a.start_pos[b];
+    int seq_tok0, q_len;
+    if (a.one_token_each) {
+        seq_tok0 = b;
+        q_len = 1;
+    } else {
+        seq_tok0 = a.cu_seqlens[b];
+        q_len = a.cu_seqlens[b + 1] - seq_tok0;
+    }
+    if (tok0 >= q_len) return;
+    const int n_tok = min(a.tokens_per_block, q_len - tok0);
+    constexpr int Q_PER_THREAD = (16 * CPR + DNW * 32 - 1) / (DNW * 32);
+    uint4 qv[Q_PER_THREAD];
+#pragma unroll
+    for (int u = 0; u < Q_PER_THREAD; ++u) {
+        const int idx = tid + u * DNW * 32;
+        const int r = idx / CPR, ch = idx % CPR;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        qv[u] = make_uint4(0, 0, 0, 0);
+        if (idx < 16 * CPR && t < n_tok && hg < a.group) {
+            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+            qv[u] = *reinterpret_cast<const uint4*>(a.q + row * HD + ch * 8);
+        }
+    }
 
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
@@ -441,38 +463,9 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     const int per_split = (tile_end - tile_begin + a.n_splits - 1) / a.n_splits;
     const int my_begin = tile_begin + split * per_split;
     const int my_end = min(tile_end, my_begin + per_split);
+    __syncthreads();                           // the page list is in shared memory
 
-    for (int idx = tid; idx < 16 * CPR; idx += DNW * 32) {
-        const int r = idx / CPR, ch = idx % CPR;
-        const int t = r / GH, hg = chunk * GH + r % GH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (t < n_tok && hg < a.group) {
-            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
-            v = *reinterpret_cast<const uint4*>(a.q + row * HD + ch * 8);
-        }
-        *reinterpret_cast<uint4*>(Qs + r * STRIDE + ch * 8) = v;
-    }
-    __syncthreads();
-
-    int row_hi[2], row_lo[2];
-    bool row_ok[2];
-    int all_hi = 0x7fffffff, all_lo = 0;          // keys in [all_lo, all_hi] are visible to every existing row
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        const int r = (lane >> 2) + 8 * e;
-        const int t = r / GH, hg = chunk * GH + r % GH;
-        row_ok[e] = (t < n_tok) && (hg < a.group);
-        row_hi[e] = row_ok[e] ? start + tok0 + t : -1;
-        row_lo[e] = (a.window > 0) ? max(0, row_hi[e] - a.window + 1) : 0;
-    }
-    all_hi = start + tok0;                                                           // the first token's position
-    all_lo = (a.window > 0) ? max(0, p_last - a.window + 1) : 0;                     // the last token's window start
-
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float o[NT_O][4];
-#pragma unroll
-    for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-
+    // ---- the warp's first sub-tiles of keys and values are requested before the queries are staged
     constexpr int SUB = TILE / DKT;                     // sub-tiles per page
     const int st_begin = my_begin * SUB, st_end = my_end * SUB;
     const bf16* kp = (const bf16*)c.k_pool;
@@ -495,6 +488,39 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         }
     };
 
+    int st = st_begin + warp;
+#pragma unroll
+    for (int p = 0; p < D_NSTAGE - 1; ++p) {
+        if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
+        cp_async_commit();
+    }
+
+#pragma unroll
+    for (int u = 0; u < Q_PER_THREAD; ++u) {
+        const int idx = tid + u * DNW * 32;
+        if (idx < 16 * CPR) *reinterpret_cast<uint4*>(Qs + (idx / CPR) * STRIDE + (idx % CPR) * 8) = qv[u];
+    }
+    __syncthreads();
+
+    int row_hi[2], row_lo[2];
+    bool row_ok[2];
+    int all_hi = 0x7fffffff, all_lo = 0;          // keys in [all_lo, all_hi] are visible to every existing row
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int r = (lane >> 2) + 8 * e;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        row_ok[e] = (t < n_tok) && (hg < a.group);
+        row_hi[e] = row_ok[e] ? start + tok0 + t : -1;
+        row_lo[e] = (a.window > 0) ? max(0, row_hi[e] - a.window + 1) : 0;
+    }
+    all_hi = start + tok0;                                                           // the first token's position
+    all_lo = (a.window > 0) ? max(0, p_last - a.window + 1) : 0;                     // the last token's window start
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[NT_O][4];
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
     unsigned qf[Q_IN_REGS ? KS_QK : 1][4];
     if (Q_IN_REGS) {
 #pragma unroll
@@ -502,12 +528,6 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
             ldmatrix_x4(qf[Q_IN_REGS ? kk : 0], Qs + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
     }
 
-    int st = st_begin + warp;
-#pragma unroll
-    for (int p = 0; p < D_NSTAGE - 1; ++p) {
-        if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
-        cp_async_commit();
-    }
     for (int it = 0; st < st_end; st += DNW, ++it) {
         const int stage = it % D_NSTAGE;
         if (st + DNW * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + DNW * (D_NSTAGE - 1));
@@ -836,6 +856,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     a.head_chunks = (a.group + a.heads_per_block - 1) / a.heads_per_block;
     a.n_splits = n_splits;
     a.cluster_merge = cluster_merge ? 1 : 0;
+    a.one_token_each = (max_q_len == 1 && n_tokens == n_seqs) ? 1 : 0;
     const long long gy = (long long)kv_heads * a.head_chunks * n_splits;
     if (gy > 65535) return MLC_ERR_BAD_SIZE;
     PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, kv_heads, hd};
