@@ -5,19 +5,22 @@
 // A block owns 128 rows of one key/value head: the group's query heads of 128 / group successive
 // tokens (one row per token and head, so keys are read once for the whole group), and walks the
 // keys the rows may see in tiles of 64, which is one page of the cache.  Roles:
-//     warp 0     one thread issues the TMA loads: the query rows once, then a ring of K and V pages;
-//     warp 1     allocates tensor memory; one thread issues tcgen05.mma: S_j = Q·K_jᵀ into one of two
-//                score buffers, and O += P_j·V_j (V is the MN-major operand, read as the cache holds it);
-//     warps 2-9  two teams of four warps, one thread per row each; team 0 takes the even tiles, team 1 the odd ones.
-//                A thread reads its row's 64 scores from tensor memory (twice: for the maximum, then for the
-//                probabilities), masks where the tile meets the diagonal, a window's edge or padding rows, keeps the
-//                team's running maximum and sum in float32, and writes P_j = exp2(s·scale·log2e − m) as bfloat16 into
+//     warp 0     one thread issues the TMA loads: the query rows once, then a ring of K pages and a ring of V pages;
+//     warp 1     allocates tensor memory; one thread issues the scores S_j = Q·K_jᵀ, four tiles ahead of the rows that
+//                read them, into one of four score buffers (two per team);
+//     warp 2     one thread issues O += P_j·V_j (V is the MN-major operand, read as the cache holds it);
+//     warps 3-10 two teams of four warps, one thread per row each; team 0 takes the even tiles, team 1 the odd ones.
+//                A thread reads its row's 64 scores from tensor memory, masks where the tile meets the diagonal, a
+//                window's edge or padding rows, keeps the team's running maximum and sum in float32, and writes P_j = exp2(s·scale·log2e − m) as bfloat16 into
 //                shared memory for the tensor cores.  Each team's output accumulates in tensor memory; when a row's
 //                maximum rises by more than 2^8 the row's thread rescales its lane of the output there before O_j is
 //                added.  At the end the teams exchange each row's (maximum, sum) and every thread adds and stores half of
 //                the row's columns.
-// A block has two tiles in flight (one per team) and the scores of the two after them; with a head size of 64 two
-// blocks share an SM besides.
+// A block has two tiles in flight (one per team) and the scores of the four after them: a team finds its next
+// scores complete when it has handed over its probabilities, and neither issuing thread waits for the other's
+// products (an issue costs its thread some 60 clocks and a barrier wait twice that, whatever the product's size).
+// Every barrier has one waiting thread, or a team's threads in step: a parity wait cannot tell a phase from the
+// one two before it.
 //
 // Pages are handed out dirty.  Keys beyond a row's range give scores that are replaced, not multiplied; values
 // beyond the sequence's last key would meet probabilities of exactly zero, but 0 x NaN is NaN, so the rows of
@@ -61,16 +64,20 @@ constexpr int A_HD = MLC_HEAD_DIM;
 constexpr int A_BM = 128;                              // rows of a block
 constexpr int A_BN = 64;                               // keys of a tile: one page
 constexpr int A_KB = A_HD / 64;                        // 64-element spans of the head size
-constexpr int A_STAGES = 3;
+constexpr int A_K_STAGES = (A_HD == 64) ? 6 : 4;       // K pages in flight: the scores run A_AHEAD tiles ahead
+constexpr int A_V_STAGES = 3;
+constexpr int A_AHEAD = 4;                             // score buffers and P buffers (two per team): tiles the scores are ahead
 constexpr int A_Q_BYTES = A_KB * A_BM * 128;
 constexpr int A_TILE_BYTES = A_KB * A_BN * 128;        // one K or V page of one head
 constexpr int A_P_BYTES = A_BM * 128;
-constexpr int A_BAR_BYTES = 256 + 2048;                // barriers, then the teams' (maximum, sum) of every row [2][128][2] floats
-constexpr int A_THREADS = 64 + 256;
-constexpr int A_SMEM_BYTES = A_Q_BYTES + 2 * A_STAGES * A_TILE_BYTES + 2 * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
-constexpr int A_TMEM_COLS = (2 * A_BN + 2 * A_HD <= 256) ? 256 : 512;     // two score buffers of 64 columns, two outputs of A_HD
-static_assert(2 * A_BN + 2 * A_HD <= A_TMEM_COLS, "tensor memory of a block");
-constexpr int A_BLOCKS_PER_SM = (A_HD == 64) ? 2 : 1;
+constexpr int A_BAR_BYTES = 512 + 2048;                // barriers, then the teams' (maximum, sum) of every row [2][128][2] floats
+constexpr int A_THREADS = 96 + 256;
+constexpr int A_SMEM_BYTES = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES + A_AHEAD * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
+static_assert(A_SMEM_BYTES <= 227 * 1024, "shared memory of a block");
+constexpr int A_TMEM_COLS = 512;                       // four score buffers of 64 columns, then two outputs of A_HD
+constexpr int A_O_COL = A_AHEAD * A_BN;                // first column of the outputs
+static_assert(A_O_COL + 2 * A_HD <= A_TMEM_COLS, "tensor memory of a block");
+constexpr int A_BLOCKS_PER_SM = 1;
 static_assert(A_SMEM_BYTES * A_BLOCKS_PER_SM <= 226 * 1024, "shared memory of the blocks of one SM");
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -95,37 +102,46 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char* smem_generic = smem_dyn + (base - smem_u32(smem_dyn));
     const unsigned q_base = base;
     const unsigned k_base = q_base + A_Q_BYTES;
-    const unsigned v_base = k_base + A_STAGES * A_TILE_BYTES;
-    const unsigned p_base = v_base + A_STAGES * A_TILE_BYTES;
-    constexpr unsigned v_off = A_Q_BYTES + A_STAGES * A_TILE_BYTES;
-    constexpr unsigned p_off = A_Q_BYTES + 2 * A_STAGES * A_TILE_BYTES;
-    const unsigned bar_base = p_base + 2 * A_P_BYTES;
-    constexpr unsigned bar_off = p_off + 2 * A_P_BYTES;
+    const unsigned v_base = k_base + A_K_STAGES * A_TILE_BYTES;
+    const unsigned p_base = v_base + A_V_STAGES * A_TILE_BYTES;
+    constexpr unsigned v_off = A_Q_BYTES + A_K_STAGES * A_TILE_BYTES;
+    constexpr unsigned p_off = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES;
+    const unsigned bar_base = p_base + A_AHEAD * A_P_BYTES;
+    constexpr unsigned bar_off = p_off + A_AHEAD * A_P_BYTES;
+    // a tile's buffer: i = 2 * team + (j >> 1 & 1), for its scores and for its probabilities
+    constexpr int B_KE = A_K_STAGES, B_VF = 2 * A_K_STAGES, B_VE = B_VF + A_V_STAGES, B_SF = B_VE + A_V_STAGES;
+    static_assert(B_SF + 4 * A_AHEAD + 3 <= 64, "the barriers' area");
     auto k_full = [&](int s) { return bar_base + 8u * s; };
-    auto v_full = [&](int s) { return bar_base + 8u * (4 + s); };
-    auto k_empty = [&](int s) { return bar_base + 8u * (8 + s); };
-    auto v_empty = [&](int s) { return bar_base + 8u * (12 + s); };
-    auto s_full = [&](int i) { return bar_base + 8u * (16 + i); };       // S_j complete: barrier j & 1 (the team's)
-    auto p_full = [&](int i) { return bar_base + 8u * (18 + i); };       // P_j written, O rescaled: by the team's 128 threads
-    auto o_full = [&](int i) { return bar_base + 8u * (20 + i); };       // O += P_j V_j complete
-    const unsigned q_full = bar_base + 8u * 22;
-    const unsigned tmem_slot = bar_base + 8u * 23;
-    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 23);
+    auto k_empty = [&](int s) { return bar_base + 8u * (B_KE + s); };
+    auto v_full = [&](int s) { return bar_base + 8u * (B_VF + s); };
+    auto v_empty = [&](int s) { return bar_base + 8u * (B_VE + s); };
+    auto s_full = [&](int i) { return bar_base + 8u * (B_SF + i); };                   // S_j complete
+    auto s_free = [&](int i) { return bar_base + 8u * (B_SF + A_AHEAD + i); };         // S_j read for the last time, by the team's 128 threads
+    auto p_full = [&](int i) { return bar_base + 8u * (B_SF + 2 * A_AHEAD + i); };     // P_j written, O rescaled: by the team's 128 threads
+    auto o_full = [&](int i) { return bar_base + 8u * (B_SF + 3 * A_AHEAD + i); };     // the team's O += P_j V_j complete
+    const unsigned q_full = bar_base + 8u * (B_SF + 4 * A_AHEAD);
+    const unsigned v_last = bar_base + 8u * (B_SF + 4 * A_AHEAD + 1);                  // the block's last V tile has landed
+    const unsigned tmem_slot = bar_base + 8u * (B_SF + 4 * A_AHEAD + 2);
+    volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * (B_SF + 4 * A_AHEAD + 2));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < A_STAGES; ++s) {
+        for (int s = 0; s < A_K_STAGES; ++s) {
             mbar_init(k_full(s), 1);
-            mbar_init(v_full(s), 1);
             mbar_init(k_empty(s), 1);
+        }
+        for (int s = 0; s < A_V_STAGES; ++s) {
+            mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < A_AHEAD; ++i) {
             mbar_init(s_full(i), 1);
+            mbar_init(s_free(i), 128);
             mbar_init(p_full(i), 128);
             mbar_init(o_full(i), 1);
         }
         mbar_init(q_full, 1);
+        mbar_init(v_last, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -160,8 +176,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tma_load_3d(q_base + kb * A_BM * 128, &map_q, kb * 64, kvh * a.group + chunk * a.heads_per_block,
                             seq_tok0 + tok0, q_full);
             auto load_k = [&](int j, int page) -> bool {
-                const int s = j % A_STAGES;
-                if (!mbar_wait(k_empty(s), ((j / A_STAGES) & 1) ^ 1u, a.status, 11)) return false;
+                const int s = j % A_K_STAGES;
+                if (!mbar_wait(k_empty(s), ((j / A_K_STAGES) & 1) ^ 1u, a.status, 11)) return false;
                 const int row = (page * a.kv_heads + kvh) * A_BN;       // a missing page (-1) reads as zeros
                 mbar_expect_tx(k_full(s), A_TILE_BYTES);
                 for (int kb = 0; kb < A_KB; ++kb)
@@ -169,38 +185,41 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 return true;
             };
             auto load_v = [&](int j, int page) -> bool {
-                const int s = j % A_STAGES;
-                if (!mbar_wait(v_empty(s), ((j / A_STAGES) & 1) ^ 1u, a.status, 11)) return false;
+                const int s = j % A_V_STAGES;
+                if (!mbar_wait(v_empty(s), ((j / A_V_STAGES) & 1) ^ 1u, a.status, 11)) return false;
                 const int row = (page * a.kv_heads + kvh) * A_BN;
                 mbar_expect_tx(v_full(s), A_TILE_BYTES);
                 for (int kb = 0; kb < A_KB; ++kb)
                     tma_load_2d(v_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_v, kb * 64, row, v_full(s));
                 return true;
             };
-            // the scores run two tiles ahead of the products with V: K_0, K_1, then V_j and K_{j+2} in turn
-            int pg[3];
-            pg[0] = __ldg(pages + tile_begin);
-            pg[1] = (n_tiles > 1) ? __ldg(pages + tile_begin + 1) : 0;
-            bool alive = load_k(0, pg[0]);
-            if (alive && n_tiles > 1) alive = load_k(1, pg[1]);
+            // the scores run A_AHEAD tiles ahead of the products with V: K_0 .. K_3, then V_j and K_{j+4} in turn
+            int pg[A_AHEAD + 1];                  // pages of tiles j .. j + A_AHEAD
+#pragma unroll
+            for (int i = 0; i < A_AHEAD; ++i) pg[i] = (i < n_tiles) ? __ldg(pages + tile_begin + i) : 0;
+            bool alive = true;
+#pragma unroll
+            for (int i = 0; i < A_AHEAD; ++i)
+                if (alive && i < n_tiles) alive = load_k(i, pg[i]);
             for (int j = 0; j < n_tiles && alive; ++j) {
-                pg[2] = (j + 2 < n_tiles) ? __ldg(pages + tile_begin + j + 2) : 0;
+                pg[A_AHEAD] = (j + A_AHEAD < n_tiles) ? __ldg(pages + tile_begin + j + A_AHEAD) : 0;
                 alive = load_v(j, pg[0]);
-                if (alive && j + 2 < n_tiles) alive = load_k(j + 2, pg[2]);
-                pg[0] = pg[1];
-                pg[1] = pg[2];
+                if (alive && j + A_AHEAD < n_tiles) alive = load_k(j + A_AHEAD, pg[A_AHEAD]);
+#pragma unroll
+                for (int i = 0; i < A_AHEAD; ++i) pg[i] = pg[i + 1];
             }
         }
     } else if (warp == 1) {
-        // ---------------- tensor-core issuer: S_0, S_1, then for every tile O_{j&1} += P_j V_j and S_{j+2}
+        // ---------------- scores: S_j into buffer 2 * (j & 1) + (j >> 1 & 1) as soon as K_j has landed and the team has
+        // read S_{j-4} out of that buffer; the commits hand S_j to the team and the K stage back to the loader
         if (lane == 0 && n_tiles > 0) {
             constexpr unsigned idesc_s = umma_idesc(A_BN);
-            constexpr unsigned idesc_o = umma_idesc(A_HD, true);
             bool ok = mbar_wait(q_full, 0, a.status, 12);
-            auto issue_scores = [&](int j) -> bool {
-                const int s = j % A_STAGES, i = j & 1;
-                if (!mbar_wait(k_full(s), (j / A_STAGES) & 1, a.status, 12)) return false;
-                // the team's score buffer is free: its rows handed over P_{j-2}, seen before O_{j-2} was issued, after reading S_{j-2}
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % A_K_STAGES, i = 2 * (j & 1) + ((j >> 1) & 1);
+                ok = mbar_wait(k_full(s), (j / A_K_STAGES) & 1, a.status, 12);
+                if (ok && j >= A_AHEAD) ok = mbar_wait(s_free(i), (((unsigned)j >> 2) - 1u) & 1u, a.status, 12);
+                if (!ok) break;
                 tcgen05_fence_after();
                 const unsigned d = tmem_base + (unsigned)(i * A_BN);
 #pragma unroll
@@ -211,34 +230,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     for (int k = 0; k < 4; ++k)
                         tcgen05_mma_f16(d, qd + 2ull * k, kd + 2ull * k, idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
                 }
-                tcgen05_commit(s_full(i));      // arrives when S_j and everything issued before it (O_{j-2} too) is complete
-                return true;
-            };
-            if (ok) ok = issue_scores(0);
-            if (ok && n_tiles > 1) ok = issue_scores(1);
+                tcgen05_commit(s_full(i));
+                tcgen05_commit(k_empty(s));
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------- outputs: the team's O += P_j V_j once V_j has landed and the team has written P_j (and rescaled
+        // its output where needed); the commits tell the team that this buffer of P and its O are at rest again, and hand
+        // the V stage back to the loader
+        if (lane == 0 && n_tiles > 0) {
+            constexpr unsigned idesc_o = umma_idesc(A_HD, true);
+            bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % A_STAGES, i = j & 1;
-                ok = mbar_wait(v_full(s), (j / A_STAGES) & 1, a.status, 12) &&
-                     mbar_wait(p_full(i), ((unsigned)j >> 1) & 1u, a.status, 12);      // P_j written, the team's output rescaled
+                const int s = j % A_V_STAGES, i = 2 * (j & 1) + ((j >> 1) & 1);
+                ok = mbar_wait(v_full(s), (j / A_V_STAGES) & 1, a.status, 12);
+                if (!ok) break;
+                // the rows zero what lies beyond the sequence's end in the last V tile: told here that it has landed, since
+                // this thread alone follows the V stages' barriers phase by phase
+                if (j == n_tiles - 1 && (tile_begin + j) * A_BN + A_BN - 1 > seq_last) mbar_arrive(v_last);
+                ok = mbar_wait(p_full(i), ((unsigned)j >> 2) & 1u, a.status, 12);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const unsigned d = tmem_base + (unsigned)(2 * A_BN + i * A_HD);
+                const unsigned d = tmem_base + (unsigned)(A_O_COL + (j & 1) * A_HD);
                 const unsigned long long pd = umma_desc_sw128(p_base + i * A_P_BYTES);
                 const unsigned long long vd = umma_desc_sw128_mn(v_base + s * A_TILE_BYTES, A_BN * 128);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)      // 16 keys a step: 32 bytes along a row of P, two 8-key groups of V
                     tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j >= 2 || k > 0) ? 1u : 0u);
                 tcgen05_commit(o_full(i));
-                if (j + 2 < n_tiles) ok = issue_scores(j + 2);
+                tcgen05_commit(v_empty(s));
             }
         }
     } else if (n_tiles > 0) {
         // ---------------- two teams of four warps, one thread per row each.  Team 0 takes the even tiles, team 1 the odd
-        // ones, each with its own score buffer, P buffer, running maximum and sum and its own output accumulator in tensor
-        // memory; they meet once, at the end.  A block that is alone with a long row of tiles (the last rows of a long
-        // prompt) thus has two tiles in flight.
-        const int q4 = warp & 3;
-        const int team = (warp - 2) >> 2;
+        // ones, each with its own two score buffers, P buffer, running maximum and sum and its own output accumulator in
+        // tensor memory; they meet once, at the end.
+        const int q4 = warp & 3;                  // the quarter of tensor memory's lanes this warp may read
+        const int team = (warp - 3) >> 2;
         const int r = q4 * 32 + lane;
         const int t = r / a.heads_per_block, hg = chunk * a.heads_per_block + r % a.heads_per_block;
         const bool row_ok = t < n_tok && hg < a.group && r < a.heads_per_block * a.tokens_per_block;
@@ -252,52 +280,46 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // is the output in tensor memory rescaled, so that after the first tiles the rescaling almost never runs.
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
-        const bool stamp = a.timing != nullptr && warp == 2;      // the whole warp keeps time, so that it stays converged
+        const bool stamp = a.timing != nullptr && warp == 3;      // the whole warp keeps time, so that it stays converged
         int ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t0 = 0, t1;        // 32-bit clocks: differences survive the wrap
 #define MLC_PHASE(k) if (stamp) { t1 = (int)clock(); ph[k] += t1 - t0; t0 = t1; }
         if (stamp) t0 = (int)clock();
         const int t_role = t0;
-        const unsigned s_taddr = tmem_base + lane_base + (unsigned)(team * A_BN);
-        const unsigned o_taddr = tmem_base + lane_base + (unsigned)(2 * A_BN + team * A_HD);
-        unsigned char* prow = smem_generic + p_off + team * A_P_BYTES + r * 128;
+        const unsigned o_taddr = tmem_base + lane_base + (unsigned)(A_O_COL + team * A_HD);
         int my_tiles = 0;
 
         for (int j = team; j < n_tiles; j += 2, ++my_tiles) {
-            ok = mbar_wait(s_full(team), ((unsigned)j >> 1) & 1u, a.status, 13);
+            const int sbuf = 2 * team + ((j >> 1) & 1);
+            ok = mbar_wait(s_full(sbuf), ((unsigned)j >> 2) & 1u, a.status, 13);
             if (!ok) break;
             MLC_PHASE(0)                                   // waiting for the scores
             tcgen05_fence_after();
-            if (threadIdx.x == 64 + 128 * team) {
-                // S_j is complete, and with it everything the issuing thread had issued before: O_{j-2}.  Their K and V
-                // stages are free for the loader.
-                mbar_arrive(k_empty(j % A_STAGES));
-                if (j >= 2) mbar_arrive(v_empty((j - 2) % A_STAGES));
-            }
-            __syncwarp();
+            const unsigned s_taddr = tmem_base + lane_base + (unsigned)(sbuf * A_BN);
+            unsigned char* prow = smem_generic + p_off + sbuf * A_P_BYTES + r * 128;
             const int key0 = (tile_begin + j) * A_BN;
             // decided for the warp as a whole: lanes that went separate ways here would run everything below twice
             const bool masked = !__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo);
 
-            // first pass over the row's 64 scores: the maximum
+            // the row's 64 scores, read once and kept in registers; the scores four tiles on may then take the buffer
+            float sc[A_BN];
+            static_assert(A_BN == 64, "one load of 64 columns");
+            tmem_load64(s_taddr, sc);
+            tcgen05_fence_before();
+            mbar_arrive(s_free(sbuf));
+            if (masked) {
+#pragma unroll
+                for (int c = 0; c < A_BN; ++c) {
+                    const int kpos = key0 + c;
+                    sc[c] = (kpos >= lo && kpos <= hi) ? sc[c] : -INFINITY;
+                }
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one of 64 links
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float s[32];
-                tmem_load32(s_taddr + (unsigned)(32 * h), s);
-                if (masked) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int kpos = key0 + 32 * h + c;
-                        s[c] = (kpos >= lo && kpos <= hi) ? s[c] : -INFINITY;
-                    }
-                }
-#pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    mx4[0] = fmaxf(mx4[0], s[c]);
-                    mx4[1] = fmaxf(mx4[1], s[c + 1]);
-                    mx4[2] = fmaxf(mx4[2], s[c + 2]);
-                    mx4[3] = fmaxf(mx4[3], s[c + 3]);
-                }
+            for (int c = 0; c < A_BN; c += 4) {
+                mx4[0] = fmaxf(mx4[0], sc[c]);
+                mx4[1] = fmaxf(mx4[1], sc[c + 1]);
+                mx4[2] = fmaxf(mx4[2], sc[c + 2]);
+                mx4[3] = fmaxf(mx4[3], sc[c + 3]);
             }
             MLC_PHASE(1)                                   // reading them, maximum
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;   // the scale is positive
@@ -307,42 +329,35 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float corr = raise ? fast_exp2(m - m_use) : 1.0f;   // 0 when nothing was seen before
             m = m_new;
 
-            // second pass: probabilities, their sum, P as bfloat16 into the team's swizzled shared-memory tile.  The P
-            // buffer is free: O_{j-2}, which read it, was complete when S_j was.
+            // probabilities, their sum, P as bfloat16 into one of the team's two swizzled shared-memory tiles, once the
+            // product that read that tile last (the team's last but one) is complete
+            if (j >= A_AHEAD) {
+                ok = mbar_wait(o_full(sbuf), (((unsigned)j >> 2) - 1u) & 1u, a.status, 13);
+                if (!ok) break;
+            }
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float s[32];
-                tmem_load32(s_taddr + (unsigned)(32 * h), s);
-                if (masked) {
+            for (int c8 = 0; c8 < A_BN / 8; ++c8) {
+                unsigned pk[4];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int kpos = key0 + 32 * h + c;
-                        s[c] = (kpos >= lo && kpos <= hi) ? s[c] : -INFINITY;
-                    }
-                }
-                unsigned pk[16];
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const float p0 = fast_exp2(fmaf(s[2 * c], a.scale_log2, -m_use));
-                    const float p1 = fast_exp2(fmaf(s[2 * c + 1], a.scale_log2, -m_use));
+                for (int c = 0; c < 4; ++c) {
+                    const float p0 = fast_exp2(fmaf(sc[8 * c8 + 2 * c], a.scale_log2, -m_use));
+                    const float p1 = fast_exp2(fmaf(sc[8 * c8 + 2 * c + 1], a.scale_log2, -m_use));
                     ls4[(2 * c) & 3] += p0;
                     ls4[(2 * c + 1) & 3] += p1;
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                     pk[c] = *reinterpret_cast<unsigned*>(&hh);
                 }
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<uint4*>(prow + (((h * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
             l = l * corr + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
             MLC_PHASE(2)                                   // exponentials, writing P
 
-            if (key0 + A_BN - 1 > seq_last) {
-                // the tile reaches past the sequence's last key: zero those rows of V (whole 128-byte rows, so the
-                // swizzle does not matter) once TMA has delivered the tile
-                const int st = j % A_STAGES;
-                ok = mbar_wait(v_full(st), (j / A_STAGES) & 1, a.status, 13);
+            if (j == n_tiles - 1 && key0 + A_BN - 1 > seq_last) {
+                // the block's last tile reaches past the sequence's last key: zero those rows of V (whole 128-byte rows,
+                // so the swizzle does not matter) once TMA has delivered the tile
+                const int st = j % A_V_STAGES;
+                ok = mbar_wait(v_last, 0, a.status, 13);
                 if (!ok) break;
                 const int first = max(seq_last + 1 - key0, 0), n_rows = A_BN - first;
                 for (int idx = r; idx < n_rows * 8 * A_KB; idx += 128) {
@@ -353,8 +368,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             fence_async_shared();
             if (j >= 2 && __any_sync(0xffffffffu, raise)) {
-                // Rescale this warp's rows of the team's output before P_j V_j is added to them.  The output is at rest:
-                // the team's last product, O_{j-2}, was complete when S_j was.
+                // Rescale this warp's rows of the team's output before P_j V_j is added to them, once the output is at
+                // rest: when the team's last product is complete.
+                ok = mbar_wait(o_full(sbuf ^ 1), ((unsigned)(j - 2) >> 2) & 1u, a.status, 13);
+                if (!ok) break;
+                tcgen05_fence_after();
 #pragma unroll
                 for (int c0 = 0; c0 < A_HD; c0 += 32) {
                     float v[32];
@@ -366,12 +384,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tmem_store_wait();
             }
             tcgen05_fence_before();
-            mbar_arrive(p_full(team));
+            mbar_arrive(p_full(sbuf));
             MLC_PHASE(3)                                   // zeroing, rescaling, hand-over
         }
-        // the team's last product: O_j completes barrier j & 1; the team has seen S of its last tile, issued after its
-        // last product but one, so the barrier is at the awaited phase or just before it
-        if (ok && my_tiles > 0) ok = mbar_wait(o_full(team), (unsigned)(my_tiles - 1) & 1u, a.status, 13);
+        // the team's last two products (one per buffer)
+        for (int back = 0; back < 2 && back < my_tiles && ok; ++back) {
+            const int jl = team + 2 * (my_tiles - 1 - back);
+            ok = mbar_wait(o_full(2 * team + ((jl >> 1) & 1)), ((unsigned)jl >> 2) & 1u, a.status, 13);
+        }
         MLC_PHASE(4)                                       // waiting for the last product
         if (stamp && lane == 0) {
             long long* dst = a.timing + 16ll * (blockIdx.x + gridDim.x * blockIdx.y);
@@ -381,7 +401,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #undef MLC_PHASE
         // ---- the teams meet: each row's two (maximum, sum) pairs cross through shared memory, then every thread takes
         // half of the row's output columns and adds the two accumulators out of tensor memory
-        float* ml = reinterpret_cast<float*>(smem_generic + bar_off + 256);            // [2 teams][128 rows][2]
+        float* ml = reinterpret_cast<float*>(smem_generic + bar_off + 512);            // [2 teams][128 rows][2]
         ml[(team * 128 + r) * 2] = m;
         ml[(team * 128 + r) * 2 + 1] = l;
         tcgen05_fence_before();
@@ -394,7 +414,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const float inv = 1.0f / (l0 * f0 + l1 * f1);
         constexpr int O_COLS = A_HD / 2;                    // output columns of one thread
         bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD + team * O_COLS;
-        const unsigned o0 = tmem_base + lane_base + (unsigned)(2 * A_BN + team * O_COLS), o1 = o0 + (unsigned)A_HD;
+        const unsigned o0 = tmem_base + lane_base + (unsigned)(A_O_COL + team * O_COLS), o1 = o0 + (unsigned)A_HD;
 #pragma unroll
         for (int c0 = 0; c0 < O_COLS; c0 += 32) {
             float v[32], w[32];

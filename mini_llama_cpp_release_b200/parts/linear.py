@@ -11,7 +11,8 @@ Which kernel runs is decided by the operand types and sizes, never by the model:
     where the K range is split over blocks and the partial sums are left to the consumer.
   * plain bfloat16 products of more rows (prompts): the library's tensor-core product with
     float32 accumulation, as the reference calls cuBLAS for its linears
-    (src/cuda_matmul.cpp:216-233).
+    (src/cuda_matmul.cpp:216-233); where the product is a branch's last, it adds into the
+    float32 residual stream in the same call.
 """
 from __future__ import annotations
 
@@ -52,12 +53,19 @@ class Linear:
         return self.weight.numel() * self.weight.element_size()
 
     def can_add_into_stream(self, n_rows: int) -> bool:
-        """Whether `add_into` has a kernel for this many rows (the tcgen05 product with atomic adds)."""
-        return self.tensor_core_ok and n_rows <= SMALL_BATCH
+        """Whether `add_into` has a kernel for these operands: the tcgen05 product with atomic adds for few rows, the
+        library's product with the stream as the matrix it adds to for more."""
+        return self.tensor_core_ok
 
     def add_into(self, x: torch.Tensor, stream: torch.Tensor) -> None:
-        """stream (float32 [n, out]) += x · Wᵀ, the K range shared out over as many blocks as is useful."""
+        """stream (float32 [n, out]) += x · Wᵀ.  Few rows: the K range shared out over as many blocks as is useful.
+        More rows: the library's product reads and writes the stream in its epilogue, so the norm that follows has one
+        tensor to read, not two."""
         m = x.shape[0]
+        if m > SMALL_BATCH:
+            torch.addmm(stream, x, self.weight.t(), out_dtype=torch.float32, out=stream)
+            kernels.count_library_launches(1)
+            return
         splits = split_count(self.out_features, self.in_features, m, self.runtime.n_sms, max_splits=ADD_MAX_SPLITS)
         kernels.gemm_tcgen05(x, self.weight, stream, kernels.bindings.EPI_ADD, splits, n_sms=self.runtime.n_sms)
 
