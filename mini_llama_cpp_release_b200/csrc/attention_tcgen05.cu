@@ -6,21 +6,22 @@
 // tokens (one row per token and head, so keys are read once for the whole group), and walks the
 // keys the rows may see in tiles of 64, which is one page of the cache.  Roles:
 //     warp 0     one thread issues the TMA loads: the query rows once, then a ring of K pages and a ring of V pages;
-//     warp 1     allocates tensor memory; one thread issues the scores S_j = Q·K_jᵀ, four tiles ahead of the rows that
-//                read them, into one of four score buffers (two per team);
+//     warp 1     allocates tensor memory; one thread issues the scores S_j = Q·K_jᵀ, some tiles ahead of the rows that
+//                read them, into a ring of score buffers (buffer j mod 5 with a head size of 64, j mod 4 with 128);
 //     warp 2     one thread issues O += P_j·V_j (V is the MN-major operand, read as the cache holds it);
-//     warps 3-10 two teams of four warps, one thread per row each; team 0 takes the even tiles, team 1 the odd ones.
+//     warps 3-   teams of four warps, one thread per row each: three teams with a head size of 64, two with 128 (tensor
+//                memory holds a team's output beside the score buffers); team t takes the tiles t, t + teams, ...
 //                A thread reads its row's 64 scores from tensor memory, masks where the tile meets the diagonal, a
 //                window's edge or padding rows, keeps the team's running maximum and sum in float32, and writes P_j = exp2(s·scale·log2e − m) as bfloat16 into
 //                shared memory for the tensor cores.  Each team's output accumulates in tensor memory; when a row's
 //                maximum rises by more than 2^8 the row's thread rescales its lane of the output there before O_j is
-//                added.  At the end the teams exchange each row's (maximum, sum) and every thread adds and stores half of
-//                the row's columns.
-// A block has two tiles in flight (one per team) and the scores of the four after them: a team finds its next
+//                added.  At the end the teams exchange each row's (maximum, sum) and every thread adds and stores a share
+//                of the row's columns.
+// A block has one tile in flight per team and the scores of those after them: a team finds its next
 // scores complete when it has handed over its probabilities, and neither issuing thread waits for the other's
 // products (an issue costs its thread some 60 clocks and a barrier wait twice that, whatever the product's size).
-// Every barrier has one waiting thread, or a team's threads in step: a parity wait cannot tell a phase from the
-// one two before it.
+// Every barrier has one waiting thread, or a team's threads in step, and a waiter knows the phase before the one
+// it waits for to be complete: a parity wait cannot tell a phase from the one two before or after it.
 //
 // Pages are handed out dirty.  Keys beyond a row's range give scores that are replaced, not multiplied; values
 // beyond the sequence's last key would meet probabilities of exactly zero, but 0 x NaN is NaN, so the rows of
@@ -64,19 +65,21 @@ constexpr int A_HD = MLC_HEAD_DIM;
 constexpr int A_BM = 128;                              // rows of a block
 constexpr int A_BN = 64;                               // keys of a tile: one page
 constexpr int A_KB = A_HD / 64;                        // 64-element spans of the head size
-constexpr int A_K_STAGES = (A_HD == 64) ? 6 : 4;       // K pages in flight: the scores run A_AHEAD tiles ahead
+constexpr int A_TEAMS = (A_HD == 64) ? 3 : 2;          // tiles in the rows' hands at a time
+constexpr int A_AHEAD = (A_HD == 64) ? 5 : 4;          // score buffers and P buffers (rings): tiles the scores are ahead
+constexpr int A_K_STAGES = (A_HD == 64) ? 6 : 4;       // K pages in flight
 constexpr int A_V_STAGES = 3;
-constexpr int A_AHEAD = 4;                             // score buffers and P buffers (two per team): tiles the scores are ahead
 constexpr int A_Q_BYTES = A_KB * A_BM * 128;
 constexpr int A_TILE_BYTES = A_KB * A_BN * 128;        // one K or V page of one head
 constexpr int A_P_BYTES = A_BM * 128;
-constexpr int A_BAR_BYTES = 512 + 2048;                // barriers, then the teams' (maximum, sum) of every row [2][128][2] floats
-constexpr int A_THREADS = 96 + 256;
+constexpr int A_BAR_BYTES = 512 + A_TEAMS * 1024;      // barriers, then the teams' (maximum, sum) of every row [teams][128][2] floats
+constexpr int A_THREADS = 96 + 128 * A_TEAMS;
 constexpr int A_SMEM_BYTES = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES + A_AHEAD * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
 static_assert(A_SMEM_BYTES <= 227 * 1024, "shared memory of a block");
-constexpr int A_TMEM_COLS = 512;                       // four score buffers of 64 columns, then two outputs of A_HD
+constexpr int A_TMEM_COLS = 512;                       // the score buffers of 64 columns, then every team's output of A_HD
 constexpr int A_O_COL = A_AHEAD * A_BN;                // first column of the outputs
-static_assert(A_O_COL + 2 * A_HD <= A_TMEM_COLS, "tensor memory of a block");
+static_assert(A_O_COL + A_TEAMS * A_HD <= A_TMEM_COLS, "tensor memory of a block");
+static_assert(A_HD % (16 * A_TEAMS) == 0 || A_TEAMS == 3, "how the teams share out the output's columns at the end");
 constexpr int A_BLOCKS_PER_SM = 1;
 static_assert(A_SMEM_BYTES * A_BLOCKS_PER_SM <= 226 * 1024, "shared memory of the blocks of one SM");
 
@@ -108,7 +111,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     constexpr unsigned p_off = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES;
     const unsigned bar_base = p_base + A_AHEAD * A_P_BYTES;
     constexpr unsigned bar_off = p_off + A_AHEAD * A_P_BYTES;
-    // a tile's buffer: i = 2 * team + (j >> 1 & 1), for its scores and for its probabilities
+    // tile j's buffer, for its scores and for its probabilities: j mod A_AHEAD
     constexpr int B_KE = A_K_STAGES, B_VF = 2 * A_K_STAGES, B_VE = B_VF + A_V_STAGES, B_SF = B_VE + A_V_STAGES;
     static_assert(B_SF + 4 * A_AHEAD + 3 <= 64, "the barriers' area");
     auto k_full = [&](int s) { return bar_base + 8u * s; };
@@ -175,50 +178,54 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int kb = 0; kb < A_KB; ++kb)
                 tma_load_3d(q_base + kb * A_BM * 128, &map_q, kb * 64, kvh * a.group + chunk * a.heads_per_block,
                             seq_tok0 + tok0, q_full);
-            auto load_k = [&](int j, int page) -> bool {
-                const int s = j % A_K_STAGES;
-                if (!mbar_wait(k_empty(s), ((j / A_K_STAGES) & 1) ^ 1u, a.status, 11)) return false;
-                const int row = (page * a.kv_heads + kvh) * A_BN;       // a missing page (-1) reads as zeros
-                mbar_expect_tx(k_full(s), A_TILE_BYTES);
-                for (int kb = 0; kb < A_KB; ++kb)
-                    tma_load_2d(k_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_k, kb * 64, row, k_full(s));
-                return true;
-            };
-            auto load_v = [&](int j, int page) -> bool {
-                const int s = j % A_V_STAGES;
-                if (!mbar_wait(v_empty(s), ((j / A_V_STAGES) & 1) ^ 1u, a.status, 11)) return false;
-                const int row = (page * a.kv_heads + kvh) * A_BN;
-                mbar_expect_tx(v_full(s), A_TILE_BYTES);
-                for (int kb = 0; kb < A_KB; ++kb)
-                    tma_load_2d(v_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_v, kb * 64, row, v_full(s));
-                return true;
-            };
-            // the scores run A_AHEAD tiles ahead of the products with V: K_0 .. K_3, then V_j and K_{j+4} in turn
-            int pg[A_AHEAD + 1];                  // pages of tiles j .. j + A_AHEAD
-#pragma unroll
-            for (int i = 0; i < A_AHEAD; ++i) pg[i] = (i < n_tiles) ? __ldg(pages + tile_begin + i) : 0;
-            bool alive = true;
-#pragma unroll
-            for (int i = 0; i < A_AHEAD; ++i)
-                if (alive && i < n_tiles) alive = load_k(i, pg[i]);
-            for (int j = 0; j < n_tiles && alive; ++j) {
-                pg[A_AHEAD] = (j + A_AHEAD < n_tiles) ? __ldg(pages + tile_begin + j + A_AHEAD) : 0;
-                alive = load_v(j, pg[0]);
-                if (alive && j + A_AHEAD < n_tiles) alive = load_k(j + A_AHEAD, pg[A_AHEAD]);
-#pragma unroll
-                for (int i = 0; i < A_AHEAD; ++i) pg[i] = pg[i + 1];
+            // Two streams of pages, K and V, each held up only by its own ring: K_j wants the scores that read its stage
+            // complete, V_j the product that read its stage.  The thread looks at both in turn and never waits on one
+            // while the other could go (K runs ahead of V by the score buffers and its ring).
+            int jk = 0, jv = 0;
+            int page_k = __ldg(pages + tile_begin), page_v = page_k;
+            unsigned long long deadline = 0;
+            for (unsigned spin = 0; jk < n_tiles || jv < n_tiles; ++spin) {
+                bool moved = false;
+                if (jk < n_tiles && mbar_test(k_empty(jk % A_K_STAGES), ((jk / A_K_STAGES) & 1) ^ 1u)) {
+                    const int s = jk % A_K_STAGES;
+                    const int row = (page_k * a.kv_heads + kvh) * A_BN;       // a missing page (-1) reads as zeros
+                    mbar_expect_tx(k_full(s), A_TILE_BYTES);
+                    for (int kb = 0; kb < A_KB; ++kb)
+                        tma_load_2d(k_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_k, kb * 64, row, k_full(s));
+                    if (++jk < n_tiles) page_k = __ldg(pages + tile_begin + jk);
+                    moved = true;
+                }
+                if (jv < n_tiles && jv < jk && mbar_test(v_empty(jv % A_V_STAGES), ((jv / A_V_STAGES) & 1) ^ 1u)) {
+                    const int s = jv % A_V_STAGES;
+                    const int row = (page_v * a.kv_heads + kvh) * A_BN;
+                    mbar_expect_tx(v_full(s), A_TILE_BYTES);
+                    for (int kb = 0; kb < A_KB; ++kb)
+                        tma_load_2d(v_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_v, kb * 64, row, v_full(s));
+                    if (++jv < n_tiles) page_v = __ldg(pages + tile_begin + jv);
+                    moved = true;
+                }
+                if (moved) {
+                    deadline = 0;
+                } else if ((spin & 255u) == 255u) {
+                    const unsigned long long now = global_ns();
+                    if (deadline == 0) deadline = now + TC_WAIT_NS;
+                    else if (now > deadline) {
+                        atomicCAS(a.status, 0, 11);
+                        break;
+                    }
+                }
             }
         }
     } else if (warp == 1) {
-        // ---------------- scores: S_j into buffer 2 * (j & 1) + (j >> 1 & 1) as soon as K_j has landed and the team has
-        // read S_{j-4} out of that buffer; the commits hand S_j to the team and the K stage back to the loader
+        // ---------------- scores: S_j into buffer j mod A_AHEAD as soon as K_j has landed and the rows have read what the
+        // buffer held before; the commits hand S_j to its team and the K stage back to the loader
         if (lane == 0 && n_tiles > 0) {
             constexpr unsigned idesc_s = umma_idesc(A_BN);
-            bool ok = mbar_wait(q_full, 0, a.status, 12);
+            bool ok = mbar_wait_polling(q_full, 0, a.status, 12);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % A_K_STAGES, i = 2 * (j & 1) + ((j >> 1) & 1);
-                ok = mbar_wait(k_full(s), (j / A_K_STAGES) & 1, a.status, 12);
-                if (ok && j >= A_AHEAD) ok = mbar_wait(s_free(i), (((unsigned)j >> 2) - 1u) & 1u, a.status, 12);
+                const int s = j % A_K_STAGES, i = j % A_AHEAD;
+                ok = mbar_wait_polling(k_full(s), (j / A_K_STAGES) & 1, a.status, 12);
+                if (ok && j >= A_AHEAD) ok = mbar_wait_polling(s_free(i), (unsigned)(j / A_AHEAD - 1) & 1u, a.status, 12);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const unsigned d = tmem_base + (unsigned)(i * A_BN);
@@ -242,29 +249,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             constexpr unsigned idesc_o = umma_idesc(A_HD, true);
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % A_V_STAGES, i = 2 * (j & 1) + ((j >> 1) & 1);
-                ok = mbar_wait(v_full(s), (j / A_V_STAGES) & 1, a.status, 12);
+                const int s = j % A_V_STAGES, i = j % A_AHEAD;
+                ok = mbar_wait_polling(v_full(s), (j / A_V_STAGES) & 1, a.status, 12);
                 if (!ok) break;
                 // the rows zero what lies beyond the sequence's end in the last V tile: told here that it has landed, since
                 // this thread alone follows the V stages' barriers phase by phase
                 if (j == n_tiles - 1 && (tile_begin + j) * A_BN + A_BN - 1 > seq_last) mbar_arrive(v_last);
-                ok = mbar_wait(p_full(i), ((unsigned)j >> 2) & 1u, a.status, 12);
+                ok = mbar_wait_polling(p_full(i), (unsigned)(j / A_AHEAD) & 1u, a.status, 12);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const unsigned d = tmem_base + (unsigned)(A_O_COL + (j & 1) * A_HD);
+                const unsigned d = tmem_base + (unsigned)(A_O_COL + (j % A_TEAMS) * A_HD);
                 const unsigned long long pd = umma_desc_sw128(p_base + i * A_P_BYTES);
                 const unsigned long long vd = umma_desc_sw128_mn(v_base + s * A_TILE_BYTES, A_BN * 128);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)      // 16 keys a step: 32 bytes along a row of P, two 8-key groups of V
-                    tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j >= 2 || k > 0) ? 1u : 0u);
+                    tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j >= A_TEAMS || k > 0) ? 1u : 0u);
                 tcgen05_commit(o_full(i));
                 tcgen05_commit(v_empty(s));
             }
         }
     } else if (n_tiles > 0) {
-        // ---------------- two teams of four warps, one thread per row each.  Team 0 takes the even tiles, team 1 the odd
-        // ones, each with its own two score buffers, P buffer, running maximum and sum and its own output accumulator in
-        // tensor memory; they meet once, at the end.
+        // ---------------- teams of four warps, one thread per row each.  Team t takes the tiles t, t + A_TEAMS, ..., with
+        // its own running maximum and sum and its own output accumulator in tensor memory; the teams meet once, at the end.
         const int q4 = warp & 3;                  // the quarter of tensor memory's lanes this warp may read
         const int team = (warp - 3) >> 2;
         const int r = q4 * 32 + lane;
@@ -288,9 +294,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const unsigned o_taddr = tmem_base + lane_base + (unsigned)(A_O_COL + team * A_HD);
         int my_tiles = 0;
 
-        for (int j = team; j < n_tiles; j += 2, ++my_tiles) {
-            const int sbuf = 2 * team + ((j >> 1) & 1);
-            ok = mbar_wait(s_full(sbuf), ((unsigned)j >> 2) & 1u, a.status, 13);
+        for (int j = team; j < n_tiles; j += A_TEAMS, ++my_tiles) {
+            const int sbuf = j % A_AHEAD;
+            ok = mbar_wait(s_full(sbuf), (unsigned)(j / A_AHEAD) & 1u, a.status, 13);
             if (!ok) break;
             MLC_PHASE(0)                                   // waiting for the scores
             tcgen05_fence_after();
@@ -300,7 +306,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // decided for the warp as a whole: lanes that went separate ways here would run everything below twice
             const bool masked = !__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo);
 
-            // the row's 64 scores, read once and kept in registers; the scores four tiles on may then take the buffer
+            // the row's 64 scores, read once and kept in registers; the scores A_AHEAD tiles on may then take the buffer
             float sc[A_BN];
             static_assert(A_BN == 64, "one load of 64 columns");
             tmem_load64(s_taddr, sc);
@@ -329,10 +335,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float corr = raise ? fast_exp2(m - m_use) : 1.0f;   // 0 when nothing was seen before
             m = m_new;
 
-            // probabilities, their sum, P as bfloat16 into one of the team's two swizzled shared-memory tiles, once the
-            // product that read that tile last (the team's last but one) is complete
+            // probabilities, their sum, P as bfloat16 into the tile's swizzled shared-memory buffer, once the product that
+            // read that buffer last is complete
             if (j >= A_AHEAD) {
-                ok = mbar_wait(o_full(sbuf), (((unsigned)j >> 2) - 1u) & 1u, a.status, 13);
+                ok = mbar_wait(o_full(sbuf), (unsigned)(j / A_AHEAD - 1) & 1u, a.status, 13);
                 if (!ok) break;
             }
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -367,10 +373,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
             fence_async_shared();
-            if (j >= 2 && __any_sync(0xffffffffu, raise)) {
+            if (j >= A_TEAMS && __any_sync(0xffffffffu, raise)) {
                 // Rescale this warp's rows of the team's output before P_j V_j is added to them, once the output is at
                 // rest: when the team's last product is complete.
-                ok = mbar_wait(o_full(sbuf ^ 1), ((unsigned)(j - 2) >> 2) & 1u, a.status, 13);
+                ok = mbar_wait(o_full((j - A_TEAMS) % A_AHEAD), (unsigned)((j - A_TEAMS) / A_AHEAD) & 1u, a.status, 13);
                 if (!ok) break;
                 tcgen05_fence_after();
 #pragma unroll
@@ -387,10 +393,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_arrive(p_full(sbuf));
             MLC_PHASE(3)                                   // zeroing, rescaling, hand-over
         }
-        // the team's last two products (one per buffer)
-        for (int back = 0; back < 2 && back < my_tiles && ok; ++back) {
-            const int jl = team + 2 * (my_tiles - 1 - back);
-            ok = mbar_wait(o_full(2 * team + ((jl >> 1) & 1)), ((unsigned)jl >> 2) & 1u, a.status, 13);
+        // the team's last product: the tensor cores complete products in the order of their issue, so the team's earlier
+        // ones are complete with it
+        if (ok && my_tiles > 0) {
+            const int jl = team + A_TEAMS * (my_tiles - 1);
+            ok = mbar_wait(o_full(jl % A_AHEAD), (unsigned)(jl / A_AHEAD) & 1u, a.status, 13);
         }
         MLC_PHASE(4)                                       // waiting for the last product
         if (stamp && lane == 0) {
@@ -399,43 +406,53 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             dst[7] = n_tiles;
         }
 #undef MLC_PHASE
-        // ---- the teams meet: each row's two (maximum, sum) pairs cross through shared memory, then every thread takes
-        // half of the row's output columns and adds the two accumulators out of tensor memory
-        float* ml = reinterpret_cast<float*>(smem_generic + bar_off + 512);            // [2 teams][128 rows][2]
+        // ---- the teams meet: each row's (maximum, sum) pairs cross through shared memory, then every thread takes a share
+        // of the row's output columns (in runs of 16) and adds the teams' accumulators out of tensor memory
+        float* ml = reinterpret_cast<float*>(smem_generic + bar_off + 512);            // [teams][128 rows][2]
         ml[(team * 128 + r) * 2] = m;
         ml[(team * 128 + r) * 2 + 1] = l;
         tcgen05_fence_before();
-        asm volatile("bar.sync 1, 256;" ::: "memory");                                 // the softmax warps only
+        asm volatile("bar.sync 1, %0;" ::"n"(128 * A_TEAMS) : "memory");               // the softmax warps only
         tcgen05_fence_after();
-        const float m0 = ml[r * 2], l0 = ml[r * 2 + 1], m1 = ml[(128 + r) * 2], l1 = ml[(128 + r) * 2 + 1];
-        const float m_all = fmaxf(m0, m1);
+        float f[A_TEAMS], m_all = -INFINITY, l_all = 0.0f;
+#pragma unroll
+        for (int u = 0; u < A_TEAMS; ++u) m_all = fmaxf(m_all, ml[(u * 128 + r) * 2]);       // -inf where a team had no tile
         const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
-        const float f0 = fast_exp2(m0 - m_ref), f1 = (n_tiles > 1) ? fast_exp2(m1 - m_ref) : 0.0f;   // team 1 may have had no tile
-        const float inv = 1.0f / (l0 * f0 + l1 * f1);
-        constexpr int O_COLS = A_HD / 2;                    // output columns of one thread
-        bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD + team * O_COLS;
-        const unsigned o0 = tmem_base + lane_base + (unsigned)(A_O_COL + team * O_COLS), o1 = o0 + (unsigned)A_HD;
 #pragma unroll
-        for (int c0 = 0; c0 < O_COLS; c0 += 32) {
-            float v[32], w[32];
-            tmem_load32(o0 + (unsigned)c0, v);              // every lane of the warp takes part in the loads
-            if (n_tiles > 1) tmem_load32(o1 + (unsigned)c0, w);
-            if (row_ok && ok) {
+        for (int u = 0; u < A_TEAMS; ++u) {
+            f[u] = (n_tiles > u) ? fast_exp2(ml[(u * 128 + r) * 2] - m_ref) : 0.0f;
+            l_all += (n_tiles > u) ? ml[(u * 128 + r) * 2 + 1] * f[u] : 0.0f;
+        }
+        const float inv = 1.0f / l_all;
+        // runs of 16 columns: two teams take half of them each; three teams (64 columns) take 2, 1 and 1
+        constexpr int RUNS = A_HD / 16;
+        const int run0 = (A_TEAMS == 3) ? (team == 0 ? 0 : team + 1) : team * (RUNS / A_TEAMS);
+        const int n_runs = (A_TEAMS == 3) ? (team == 0 ? 2 : 1) : RUNS / A_TEAMS;
+        static_assert(A_TEAMS != 3 || RUNS == 4, "three teams share out four runs of columns");
+        bf16* dst = (bf16*)a.out + ((long long)(seq_tok0 + tok0 + t) * a.q_heads + kvh * a.group + hg) * A_HD;
+        const unsigned o_first = tmem_base + lane_base + (unsigned)A_O_COL;
+        for (int run = run0; run < run0 + n_runs; ++run) {
+            float acc[16];
 #pragma unroll
-                for (int c = 0; c < 32; c += 8) {
-                    unsigned wd[4];
+            for (int c = 0; c < 16; ++c) acc[c] = 0.0f;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float x0 = v[c + 2 * e] * f0, x1 = v[c + 2 * e + 1] * f0;
-                        if (n_tiles > 1) {
-                            x0 = fmaf(w[c + 2 * e], f1, x0);
-                            x1 = fmaf(w[c + 2 * e + 1], f1, x1);
-                        }
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(x0 * inv, x1 * inv);
-                        wd[e] = *reinterpret_cast<unsigned*>(&hh);
-                    }
-                    *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+            for (int u = 0; u < A_TEAMS; ++u) {
+                if (n_tiles > u) {                         // the same for the whole block: every lane takes part in the load
+                    float v[16];
+                    tmem_load16(o_first + (unsigned)(u * A_HD + 16 * run), v);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) acc[c] = fmaf(v[c], f[u], acc[c]);
                 }
+            }
+            if (row_ok && ok) {
+                unsigned wd[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
+                    wd[e] = *reinterpret_cast<unsigned*>(&hh);
+                }
+                *reinterpret_cast<uint4*>(dst + 16 * run) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                *reinterpret_cast<uint4*>(dst + 16 * run + 8) = make_uint4(wd[4], wd[5], wd[6], wd[7]);
             }
         }
         if (stamp && lane == 0) {

@@ -44,6 +44,32 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* st
         }
     }
 }
+// One look at a barrier: whether the phase with the given parity is complete.
+__device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// The same for a thread whose wake-up is on everyone's critical path (one that issues tensor-core work): test_wait
+// polls and never suspends the thread.
+__device__ __forceinline__ bool mbar_wait_polling(unsigned bar, unsigned parity, int* status, int code) {
+    unsigned long long deadline = 0;
+    for (unsigned spin = 0;; ++spin) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spin & 1023u) == 1023u) {
+            const unsigned long long now = global_ns();
+            if (deadline == 0) deadline = now + TC_WAIT_NS;
+            else if (now > deadline) {
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");

@@ -564,6 +564,21 @@ def test_tcgen05_attention_prompts_chunks_and_single_tokens(H, KV, hd):
     close(got, want, 1e-2)
 
 
+@pytest.mark.parametrize("H,KV,hd", [(14, 2, 64), (4, 1, 128)])
+def test_tcgen05_attention_long_rows_go_round_every_ring_many_times(H, KV, hd):
+    """Rows of 33 and 40 key tiles: the rings of K and V stages and of score and probability buffers (3 to 6 deep) are
+    gone round many times, whole and with a remainder.  One far key that only the last rows may prefer shows a tile that
+    was skipped or taken twice."""
+    def one_far_key(qs, ks, vs):
+        q, k, v = qs[0], ks[0], vs[0]
+        k[70] = 0; k[70, :, 3] = 16.0
+        q[-5:] = 0; q[-5:, :, 3] = 16.0
+        v[70] = 5.0
+    got, want, _ = attention_case([2100, 2560], [2100, 300], H, KV, hd, "bfloat16", scale_up=one_far_key, seed=5, impl="tcgen05")
+    close(got, want, 1e-2)
+    assert float((got[2099] - 5.0).abs().max()) < 0.2
+
+
 @pytest.mark.parametrize("window", [1, 24, 64, 65, 130])
 def test_tcgen05_attention_window_edge_and_far_key(window):
     def prefer_outside(qs, ks, vs):
