@@ -12,8 +12,10 @@
 //     warps 3-   teams of four warps, one thread per row each: three teams with a head size of 64, two with 128 (tensor
 //                memory holds a team's output beside the score buffers); team t takes the tiles t, t + teams, ...
 //                A thread reads its row's 64 scores from tensor memory, masks where the tile meets the diagonal, a
-//                window's edge or padding rows, keeps the team's running maximum and sum in float32, and writes P_j = exp2(s·scale·log2e − m) as bfloat16 into
-//                shared memory for the tensor cores.  Each team's output accumulates in tensor memory; when a row's
+//                window's edge or padding rows, keeps the team's running maximum and sum in float32, and writes
+//                P_j = exp2(s·scale·log2e − m) as bfloat16 back into tensor memory, over the scores it has read: the
+//                product with V takes P from there, so P never crosses shared memory (whose bandwidth the operands of
+//                the products and the arriving pages fill).  Each team's output accumulates in tensor memory; when a row's
 //                maximum rises by more than 2^8 the row's thread rescales its lane of the output there before O_j is
 //                added.  At the end the teams exchange each row's (maximum, sum) and every thread adds and stores a share
 //                of the row's columns.
@@ -67,14 +69,13 @@ constexpr int A_BN = 64;                               // keys of a tile: one pa
 constexpr int A_KB = A_HD / 64;                        // 64-element spans of the head size
 constexpr int A_TEAMS = (A_HD == 64) ? 3 : 2;          // tiles in the rows' hands at a time
 constexpr int A_AHEAD = (A_HD == 64) ? 5 : 4;          // score buffers and P buffers (rings): tiles the scores are ahead
-constexpr int A_K_STAGES = (A_HD == 64) ? 6 : 4;       // K pages in flight
-constexpr int A_V_STAGES = 3;
+constexpr int A_K_STAGES = 6;                          // K pages in flight
+constexpr int A_V_STAGES = 4;
 constexpr int A_Q_BYTES = A_KB * A_BM * 128;
 constexpr int A_TILE_BYTES = A_KB * A_BN * 128;        // one K or V page of one head
-constexpr int A_P_BYTES = A_BM * 128;
 constexpr int A_BAR_BYTES = 512 + A_TEAMS * 1024;      // barriers, then the teams' (maximum, sum) of every row [teams][128][2] floats
 constexpr int A_THREADS = 96 + 128 * A_TEAMS;
-constexpr int A_SMEM_BYTES = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES + A_AHEAD * A_P_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
+constexpr int A_SMEM_BYTES = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES + A_BAR_BYTES + 1024 /* alignment slack */;
 static_assert(A_SMEM_BYTES <= 227 * 1024, "shared memory of a block");
 constexpr int A_TMEM_COLS = 512;                       // the score buffers of 64 columns, then every team's output of A_HD
 constexpr int A_O_COL = A_AHEAD * A_BN;                // first column of the outputs
@@ -106,12 +107,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const unsigned q_base = base;
     const unsigned k_base = q_base + A_Q_BYTES;
     const unsigned v_base = k_base + A_K_STAGES * A_TILE_BYTES;
-    const unsigned p_base = v_base + A_V_STAGES * A_TILE_BYTES;
     constexpr unsigned v_off = A_Q_BYTES + A_K_STAGES * A_TILE_BYTES;
-    constexpr unsigned p_off = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES;
-    const unsigned bar_base = p_base + A_AHEAD * A_P_BYTES;
-    constexpr unsigned bar_off = p_off + A_AHEAD * A_P_BYTES;
-    // tile j's buffer, for its scores and for its probabilities: j mod A_AHEAD
+    const unsigned bar_base = v_base + A_V_STAGES * A_TILE_BYTES;
+    constexpr unsigned bar_off = A_Q_BYTES + (A_K_STAGES + A_V_STAGES) * A_TILE_BYTES;
+    // tile j's buffer in tensor memory, for its scores and then for its probabilities: j mod A_AHEAD
     constexpr int B_KE = A_K_STAGES, B_VF = 2 * A_K_STAGES, B_VE = B_VF + A_V_STAGES, B_SF = B_VE + A_V_STAGES;
     static_assert(B_SF + 4 * A_AHEAD + 3 <= 64, "the barriers' area");
     auto k_full = [&](int s) { return bar_base + 8u * s; };
@@ -119,7 +118,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     auto v_full = [&](int s) { return bar_base + 8u * (B_VF + s); };
     auto v_empty = [&](int s) { return bar_base + 8u * (B_VE + s); };
     auto s_full = [&](int i) { return bar_base + 8u * (B_SF + i); };                   // S_j complete
-    auto s_free = [&](int i) { return bar_base + 8u * (B_SF + A_AHEAD + i); };         // S_j read for the last time, by the team's 128 threads
     auto p_full = [&](int i) { return bar_base + 8u * (B_SF + 2 * A_AHEAD + i); };     // P_j written, O rescaled: by the team's 128 threads
     auto o_full = [&](int i) { return bar_base + 8u * (B_SF + 3 * A_AHEAD + i); };     // the team's O += P_j V_j complete
     const unsigned q_full = bar_base + 8u * (B_SF + 4 * A_AHEAD);
@@ -139,7 +137,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         for (int i = 0; i < A_AHEAD; ++i) {
             mbar_init(s_full(i), 1);
-            mbar_init(s_free(i), 128);
             mbar_init(p_full(i), 128);
             mbar_init(o_full(i), 1);
         }
@@ -217,15 +214,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else if (warp == 1) {
-        // ---------------- scores: S_j into buffer j mod A_AHEAD as soon as K_j has landed and the rows have read what the
-        // buffer held before; the commits hand S_j to its team and the K stage back to the loader
+        // ---------------- scores: S_j into buffer j mod A_AHEAD as soon as K_j has landed and the product that read the
+        // buffer's last probabilities is complete; the commits hand S_j to its team and the K stage back to the loader
         if (lane == 0 && n_tiles > 0) {
             constexpr unsigned idesc_s = umma_idesc(A_BN);
             bool ok = mbar_wait_polling(q_full, 0, a.status, 12);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % A_K_STAGES, i = j % A_AHEAD;
                 ok = mbar_wait_polling(k_full(s), (j / A_K_STAGES) & 1, a.status, 12);
-                if (ok && j >= A_AHEAD) ok = mbar_wait_polling(s_free(i), (unsigned)(j / A_AHEAD - 1) & 1u, a.status, 12);
+                if (ok && j >= A_AHEAD) ok = mbar_wait_polling(o_full(i), (unsigned)(j / A_AHEAD - 1) & 1u, a.status, 12);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const unsigned d = tmem_base + (unsigned)(i * A_BN);
@@ -243,8 +240,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
     } else if (warp == 2) {
         // ---------------- outputs: the team's O += P_j V_j once V_j has landed and the team has written P_j (and rescaled
-        // its output where needed); the commits tell the team that this buffer of P and its O are at rest again, and hand
-        // the V stage back to the loader
+        // its output where needed); the commits tell that the tile's buffer is free for other scores and the team's O at
+        // rest again, and hand the V stage back to the loader
         if (lane == 0 && n_tiles > 0) {
             constexpr unsigned idesc_o = umma_idesc(A_HD, true);
             bool ok = true;
@@ -259,11 +256,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (!ok) break;
                 tcgen05_fence_after();
                 const unsigned d = tmem_base + (unsigned)(A_O_COL + (j % A_TEAMS) * A_HD);
-                const unsigned long long pd = umma_desc_sw128(p_base + i * A_P_BYTES);
+                const unsigned p_tmem = tmem_base + (unsigned)(i * A_BN);       // P_j: 32 columns of bfloat16 pairs
                 const unsigned long long vd = umma_desc_sw128_mn(v_base + s * A_TILE_BYTES, A_BN * 128);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)      // 16 keys a step: 32 bytes along a row of P, two 8-key groups of V
-                    tcgen05_mma_f16(d, pd + 2ull * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j >= A_TEAMS || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k)      // 16 keys a step: 8 columns of P, two 8-key groups of V
+                    tcgen05_mma_f16_ts(d, p_tmem + 8u * k, vd + (unsigned long long)((2048u >> 4) * k), idesc_o, (j >= A_TEAMS || k > 0) ? 1u : 0u);
                 tcgen05_commit(o_full(i));
                 tcgen05_commit(v_empty(s));
             }
@@ -301,17 +298,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             MLC_PHASE(0)                                   // waiting for the scores
             tcgen05_fence_after();
             const unsigned s_taddr = tmem_base + lane_base + (unsigned)(sbuf * A_BN);
-            unsigned char* prow = smem_generic + p_off + sbuf * A_P_BYTES + r * 128;
             const int key0 = (tile_begin + j) * A_BN;
             // decided for the warp as a whole: lanes that went separate ways here would run everything below twice
             const bool masked = !__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo);
 
-            // the row's 64 scores, read once and kept in registers; the scores A_AHEAD tiles on may then take the buffer
+            // the row's 64 scores, read once and kept in registers
             float sc[A_BN];
             static_assert(A_BN == 64, "one load of 64 columns");
             tmem_load64(s_taddr, sc);
-            tcgen05_fence_before();
-            mbar_arrive(s_free(sbuf));
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < A_BN; ++c) {
@@ -335,27 +329,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float corr = raise ? fast_exp2(m - m_use) : 1.0f;   // 0 when nothing was seen before
             m = m_new;
 
-            // probabilities, their sum, P as bfloat16 into the tile's swizzled shared-memory buffer, once the product that
-            // read that buffer last is complete
-            if (j >= A_AHEAD) {
-                ok = mbar_wait(o_full(sbuf), (unsigned)(j / A_AHEAD - 1) & 1u, a.status, 13);
-                if (!ok) break;
-            }
+            // probabilities, their sum, P as pairs of bfloat16 over the first half of the scores' columns
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            unsigned pk[A_BN / 2];
 #pragma unroll
-            for (int c8 = 0; c8 < A_BN / 8; ++c8) {
-                unsigned pk[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float p0 = fast_exp2(fmaf(sc[8 * c8 + 2 * c], a.scale_log2, -m_use));
-                    const float p1 = fast_exp2(fmaf(sc[8 * c8 + 2 * c + 1], a.scale_log2, -m_use));
-                    ls4[(2 * c) & 3] += p0;
-                    ls4[(2 * c + 1) & 3] += p1;
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    pk[c] = *reinterpret_cast<unsigned*>(&hh);
-                }
-                *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            for (int c = 0; c < A_BN / 2; ++c) {
+                const float p0 = fast_exp2(fmaf(sc[2 * c], a.scale_log2, -m_use));
+                const float p1 = fast_exp2(fmaf(sc[2 * c + 1], a.scale_log2, -m_use));
+                ls4[(2 * c) & 3] += p0;
+                ls4[(2 * c + 1) & 3] += p1;
+                __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);        // key 2c in the low half
+                pk[c] = *reinterpret_cast<unsigned*>(&hh);
             }
+            tmem_store32_words(s_taddr, pk);
             l = l * corr + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
             MLC_PHASE(2)                                   // exponentials, writing P
 
@@ -371,8 +357,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     *reinterpret_cast<uint4*>(smem_generic + v_off + st * A_TILE_BYTES + kb * A_BN * 128 + (first + rem / 8) * 128 +
                                               (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
                 }
+                fence_async_shared();
             }
-            fence_async_shared();
             if (j >= A_TEAMS && __any_sync(0xffffffffu, raise)) {
                 // Rescale this warp's rows of the team's output before P_j V_j is added to them, once the output is at
                 // rest: when the team's last product is complete.
@@ -387,8 +373,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     for (int c = 0; c < 32; ++c) v[c] *= corr;
                     tmem_store32(o_taddr + (unsigned)c0, v);
                 }
-                tmem_store_wait();
             }
+            tmem_store_wait();                             // P_j (and a rescaled output) is in tensor memory
             tcgen05_fence_before();
             mbar_arrive(p_full(sbuf));
             MLC_PHASE(3)                                   // zeroing, rescaling, hand-over
