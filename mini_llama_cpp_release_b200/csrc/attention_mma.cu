@@ -55,7 +55,14 @@ struct MmaArgs {
     int one_token_each;       // decode kernel: every sequence brings exactly one token, so sequence b's token is token b
     int cluster_merge;        // decode kernel: the blocks of one row tile form a cluster and merge their key splits through
                               // distributed shared memory instead of part_ml / part_o and a second kernel
+    unsigned long long* stamps;   // decode kernel: null, or [blocks][12] nanosecond stamps of each block's phases
 };
+
+__device__ __forceinline__ unsigned long long stamp_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -408,16 +415,31 @@ constexpr int DKT = (HD <= 64) ? 32 : 16;                        // keys per sub
 constexpr int D_STAGE = DKT * STRIDE;                            // elements per stage and operand
 constexpr int D_NT_S = DKT / 8, D_KS_PV = DKT / 16;
 constexpr int D_NSTAGE = 3;                                      // stages per warp: two sub-tiles in flight while one is used
+constexpr int D_TILES_STAGED = 512;                              // page numbers kept in shared memory (32,768 keys); later tiles look theirs up
+constexpr int D_MAX_CLUSTER = 16;                                // the largest cluster there is
+// Cluster merge: what the other blocks of a cluster send this one.  Its share of the 16 x HD outputs (at most a
+// D_MAX_CLUSTER-th of them, rounded up, in four-float pieces) from every block, and every block's (maximum, sum) per row.
+constexpr int D_VPR = HD / 4;                                    // four-float pieces per row
+constexpr int D_RECV_O_BYTES = (16 * D_VPR + D_MAX_CLUSTER) * 16;
+constexpr int D_RECV_BYTES = D_RECV_O_BYTES + D_MAX_CLUSTER * 16 * 8;
+constexpr size_t D_SMEM_BYTES = (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16) + D_RECV_BYTES;
+static_assert(D_SMEM_BYTES + D_TILES_STAGED * 4 <= 227 * 1024, "shared memory of a block");
 
 __global__ void __launch_bounds__(DNW * 32)
 attention_decode_kernel(MmaArgs a, PagedKV c) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][STRIDE]
     bf16* KVs = Qs + 16 * STRIDE;                                 // [DNW warps][D_NSTAGE][K | V][DKT][STRIDE]
-    __shared__ int tile_pages[MAX_TILES_STAGED];
+    __shared__ int tile_pages[D_TILES_STAGED];
+    // where the cluster's other blocks write; nothing else of this block lives here, so they may write at any time
+    unsigned char* recv = smem_raw + (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
 
+    unsigned long long* stamps = (a.stamps != nullptr && threadIdx.x == 0)
+        ? a.stamps + 12ull * (blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z)) : nullptr;
+    if (stamps) stamps[0] = stamp_ns();                                   // entry
     grid_launch_dependents();
     grid_dependency_wait();                    // queries and the step's keys were written by the kernel before
+    if (stamps) stamps[1] = stamp_ns();                                   // the kernels before are done
     const int b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int y = blockIdx.y;
@@ -430,7 +452,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     // length is known), its position, its first token, and, when every sequence brings exactly one token (then sequence
     // b's token is token b), the query rows themselves.  Two trips to memory lie between the start and the first keys
     // then (pages, keys) instead of four (first token, queries, pages, keys).
-    for (int t = tid; t < c.pages_per_seq && t < MAX_TILES_STAGED; t += DNW * 32)
+    for (int t = tid; t < c.pages_per_seq && t < D_TILES_STAGED; t += DNW * 32)
         tile_pages[t] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
     const int start = a.start_pos[b];
     int seq_tok0, q_len;
@@ -464,6 +486,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     const int my_begin = tile_begin + split * per_split;
     const int my_end = min(tile_end, my_begin + per_split);
     __syncthreads();                           // the page list is in shared memory
+    if (stamps) stamps[2] = stamp_ns();                                   // page list, position and queries have arrived
 
     // ---- the warp's first sub-tiles of keys and values are requested before the queries are staged
     constexpr int SUB = TILE / DKT;                     // sub-tiles per page
@@ -473,7 +496,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     bf16* my_stages = KVs + warp * D_NSTAGE * 2 * D_STAGE;
     auto load_sub = [&](int stage, int st) {
         const int tile = st / SUB;
-        const int page = (tile < MAX_TILES_STAGED) ? tile_pages[tile] : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
+        const int page = (tile < D_TILES_STAGED) ? tile_pages[tile] : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
         const long long base = c.entry_offset + (((long long)max(page, 0) * c.kv_heads + kvh) * TILE + (st % SUB) * DKT) * HD;
         bf16* kd = my_stages + stage * 2 * D_STAGE;
         bf16* vd = kd + D_STAGE;
@@ -494,6 +517,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
         cp_async_commit();
     }
+    if (stamps) stamps[8] = stamp_ns();                                   // warp 0 has asked for its first keys
 
 #pragma unroll
     for (int u = 0; u < Q_PER_THREAD; ++u) {
@@ -528,6 +552,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
             ldmatrix_x4(qf[Q_IN_REGS ? kk : 0], Qs + (lane & 15) * STRIDE + kk * 16 + (lane >> 4) * 8);
     }
 
+    if (stamps) stamps[3] = stamp_ns();                                   // queries staged, first keys requested
     for (int it = 0; st < st_end; st += DNW, ++it) {
         const int stage = it % D_NSTAGE;
         if (st + DNW * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + DNW * (D_NSTAGE - 1));
@@ -639,97 +664,122 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     }
 
     // ---- merge the four warps' partial results
+    if (stamps) stamps[4] = stamp_ns();                                   // warp 0 is through its keys
     __syncthreads();
-    float* Oc = reinterpret_cast<float*>(KVs);                      // [DNW warps][16][HD]
-    float* MLc = Oc + DNW * 16 * HD;                                // [DNW warps][16][2]
-    static_assert(DNW * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (DNW * 16 * HD + DNW * 16 * 2 + 16 * HD + 32) * sizeof(float), "merge buffer");
+    if (stamps) stamps[5] = stamp_ns();                                   // every warp is
+    constexpr int OS = HD + 8;                                      // row stride of the warps' outputs: a warp's eight rows
+                                                                    // land on different banks (rows of HD floats would all
+                                                                    // start on the same one)
+    float* Oc = reinterpret_cast<float*>(KVs);                      // [DNW warps][16][OS]
+    float* MLc = Oc + DNW * 16 * OS;                                // [DNW warps][16][2]
+    static_assert(DNW * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (DNW * 16 * OS + DNW * 16 * 2 + 32 + DNW * 16) * sizeof(float), "merge buffer");
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         const int r16 = (lane >> 2) + 8 * rr;
-        float* dst = Oc + (warp * 16 + r16) * HD + 2 * (lane & 3);
+        float* dst = Oc + (warp * 16 + r16) * OS + 2 * (lane & 3);
 #pragma unroll
-        for (int j = 0; j < NT_O; ++j) {
-            dst[8 * j] = o[j][2 * rr];
-            dst[8 * j + 1] = o[j][2 * rr + 1];
-        }
+        for (int j = 0; j < NT_O; ++j) *reinterpret_cast<float2*>(dst + 8 * j) = make_float2(o[j][2 * rr], o[j][2 * rr + 1]);
         if ((lane & 3) == 0) {
             MLc[(warp * 16 + r16) * 2] = m[rr];
             MLc[(warp * 16 + r16) * 2 + 1] = l[rr];
         }
     }
     __syncthreads();
+    if (stamps) stamps[10] = stamp_ns();                                  // the warps' results are in shared memory
     constexpr float LN2 = 0.6931471805599453f;
-    float* Pc = MLc + DNW * 16 * 2;                                 // [16][HD] this block's merged output (cluster merge)
-    float* PMLc = Pc + 16 * HD;                                     // [16][2] and its maximum and sum
-    for (int idx = tid; idx < 16 * HD; idx += DNW * 32) {
-        const int r = idx / HD, d = idx % HD;
-        const int t = r / GH, hg = chunk * GH + r % GH;
-        if (!(t < n_tok && hg < a.group) && !a.cluster_merge) continue;
+    float* PMLc = MLc + DNW * 16 * 2;                               // [16][2] the block's maximum and sum per row
+    float* Fc = PMLc + 32;                                          // [DNW][16] what a warp's sum and output are scaled by
+    // a thread per (warp, row): the row's maximum over the warps and that warp's factor against it
+    if (tid < DNW * 16) {
+        const int w = tid / 16, r = tid % 16;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DNW; ++w) M = fmaxf(M, MLc[(w * 16 + r) * 2]);
-        float L = 0.0f, acc = 0.0f;
+        for (int u = 0; u < DNW; ++u) M = fmaxf(M, MLc[(u * 16 + r) * 2]);
+        const float mw = MLc[(w * 16 + r) * 2];
+        Fc[w * 16 + r] = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+        if (w == 0) PMLc[2 * r] = M;
+    }
+    __syncthreads();
+    // Cluster merge: the n_splits blocks of this row tile are one cluster (rank = split).  Block k owns the pieces
+    // k * per .. (k + 1) * per - 1 of the 16 x HD outputs; every block sends each owner its partial result for the
+    // owner's pieces and its (maximum, sum) of every row, straight into the owner's shared memory.  Stores to another
+    // block's shared memory need no answer, so their way through the cluster overlaps the barrier that follows.
+    const int S = a.n_splits;
+    const int per = (16 * D_VPR + S - 1) / S;
+    const unsigned recv_local = (unsigned)__cvta_generic_to_shared(recv);
+    // a thread per four neighbouring outputs of a row
+    for (int v = tid; v < 16 * D_VPR; v += DNW * 32) {
+        const int r = v / D_VPR, d = (v % D_VPR) * 4;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        if (!(t < n_tok && hg < a.group) && !a.cluster_merge) continue;
+        float L = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (int w = 0; w < DNW; ++w) {
-            const float mw = MLc[(w * 16 + r) * 2];
-            if (mw != -INFINITY) {
-                const float f = exp2f(mw - M);
-                L += MLc[(w * 16 + r) * 2 + 1] * f;
-                acc += Oc[(w * 16 + r) * HD + d] * f;
-            }
+            const float f = Fc[w * 16 + r];
+            const float4 x = *reinterpret_cast<const float4*>(Oc + (w * 16 + r) * OS + d);
+            L = fmaf(MLc[(w * 16 + r) * 2 + 1], f, L);
+            acc.x = fmaf(x.x, f, acc.x); acc.y = fmaf(x.y, f, acc.y); acc.z = fmaf(x.z, f, acc.z); acc.w = fmaf(x.w, f, acc.w);
         }
         const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
         if (a.cluster_merge) {
-            Pc[idx] = acc;
+            const int owner = v / per;
+            unsigned dst;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(recv_local + 16u * (unsigned)(split * per + (v - owner * per))), "r"(owner));
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
             if (d == 0) {
-                PMLc[2 * r] = M;
-                PMLc[2 * r + 1] = L;
+                const float M = PMLc[2 * r];
+                for (int k = 0; k < S; ++k) {
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(recv_local + (unsigned)D_RECV_O_BYTES + 8u * (unsigned)(split * 16 + r)), "r"(k));
+                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(dst), "f"(M), "f"(L) : "memory");
+                }
             }
         } else if (a.n_splits == 1) {
-            a.out[row * HD + d] = __float2bfloat16_rn(acc / L);
+            const float inv = 1.0f / L;
+            *reinterpret_cast<uint2*>(a.out + row * HD + d) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         } else {
             const long long pr = row * a.n_splits + split;
-            a.part_o[pr * HD + d] = acc;
+            a.part_o[pr * HD + d] = acc.x; a.part_o[pr * HD + d + 1] = acc.y;
+            a.part_o[pr * HD + d + 2] = acc.z; a.part_o[pr * HD + d + 3] = acc.w;
             if (d == 0) {
-                a.part_ml[pr * 2] = M * LN2;
+                a.part_ml[pr * 2] = PMLc[2 * r] * LN2;
                 a.part_ml[pr * 2 + 1] = L;
             }
         }
     }
+    if (stamps) stamps[9] = stamp_ns();                                   // the block's warps are merged
     if (a.cluster_merge) {
-        // The n_splits blocks of this row tile are one cluster (rank = split).  Each takes a share of the 16 x HD outputs
-        // and reads every block's partial result for them out of that block's shared memory.
+        // release: this block's stores into the others' shared memory; acquire: theirs into this block's
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        const int S = a.n_splits;
-        const int per = (16 * HD + S - 1) / S;
-        const unsigned pc_local = (unsigned)__cvta_generic_to_shared(Pc), pml_local = (unsigned)__cvta_generic_to_shared(PMLc);
-        for (int idx = split * per + tid; idx < min(16 * HD, (split + 1) * per); idx += DNW * 32) {
-            const int r = idx / HD, d = idx % HD;
+        if (stamps) stamps[6] = stamp_ns();                               // every block of the cluster has sent its results
+        const float4* ro = reinterpret_cast<const float4*>(recv);                      // [S][per]
+        const float2* rml = reinterpret_cast<const float2*>(recv + D_RECV_O_BYTES);    // [S][16]
+        for (int i = tid; i < per; i += DNW * 32) {
+            const int v = split * per + i;
+            if (v >= 16 * D_VPR) break;
+            const int r = v / D_VPR, d = (v % D_VPR) * 4;
             const int t = r / GH, hg = chunk * GH + r % GH;
             if (!(t < n_tok && hg < a.group)) continue;
-            float M = -INFINITY, L = 0.0f, acc = 0.0f;
-            for (int k = 0; k < S; ++k) {                 // running merge: one pass over the blocks
-                unsigned pc_r, pml_r;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(pc_r) : "r"(pc_local), "r"(k));
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(pml_r) : "r"(pml_local), "r"(k));
-                float mk, lk, ok;
-                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mk) : "r"(pml_r + 8u * r));
-                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lk) : "r"(pml_r + 8u * r + 4u));
-                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ok) : "r"(pc_r + 4u * idx));
-                if (mk != -INFINITY) {
-                    const float Mn = fmaxf(M, mk);
-                    const float f_old = exp2f(M - Mn), f_new = exp2f(mk - Mn);      // exp2f(-inf) = 0 for the first
-                    L = L * f_old + lk * f_new;
-                    acc = acc * f_old + ok * f_new;
-                    M = Mn;
+            float M = -INFINITY, L = 0.0f;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int k = 0; k < S; ++k) M = fmaxf(M, rml[k * 16 + r].x);
+            for (int k = 0; k < S; ++k) {
+                const float2 ml = rml[k * 16 + r];
+                if (ml.x != -INFINITY) {
+                    const float f = exp2f(ml.x - M);
+                    const float4 x = ro[k * per + i];
+                    L = fmaf(ml.y, f, L);
+                    acc.x = fmaf(x.x, f, acc.x); acc.y = fmaf(x.y, f, acc.y); acc.z = fmaf(x.z, f, acc.z); acc.w = fmaf(x.w, f, acc.w);
                 }
             }
             const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
-            a.out[row * HD + d] = __float2bfloat16_rn(acc / L);
+            const float inv = 1.0f / L;
+            *reinterpret_cast<uint2*>(a.out + row * HD + d) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         }
-        // nobody leaves while its shared memory may still be read
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        // Nobody reads another block's shared memory after the barrier, and nobody writes it: a block may leave when it
+        // has stored its share.
     }
+    if (stamps) stamps[7] = stamp_ns();                                   // done
 }
 
 // How many clusters of `size` blocks of the decode kernel the GPU can hold at once (0: that size cannot be launched).
@@ -739,7 +789,7 @@ static int decode_clusters_resident(int size) {
     static bool known[17] = {false};
     if (size < 1 || size > 16) return 0;
     if (!known[size]) {
-        const size_t smem = (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
+        const size_t smem = D_SMEM_BYTES;
         int n = 0;
         bool can = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         if (can && size > 8)
@@ -766,7 +816,7 @@ static int decode_clusters_resident(int size) {
 }
 
 static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_t s) {
-    const size_t smem = (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
+    const size_t smem = D_SMEM_BYTES;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -820,6 +870,14 @@ extern "C" int mlc_attention_mma_head_dim() { return HD; }
 // cannot be launched.  Key splits merged inside a cluster (n_splits > 1 without part_ml / part_o) need at least 1.
 extern "C" int mlc_attention_decode_clusters_resident(int size) { return decode_clusters_resident(size); }
 
+// Measurement hook: later launches of the decode kernel leave nanosecond stamps of their phases in p ([blocks][12] on
+// the device; null switches it off again).
+static unsigned long long* g_decode_stamps = nullptr;
+extern "C" int mlc_attention_decode_stamps(unsigned long long* p) {
+    g_decode_stamps = p;
+    return 0;
+}
+
 // q, out: bfloat16 [n_tokens][q_heads][HD]; the cache pools hold bfloat16 in pages of 64 tokens.
 // row_tiles: 1, 2 or 4 (16, 32 or 64 rows per block); with row_tiles 1, warp_private != 0 picks the
 // kernel whose warps each stream their own sub-tiles (the decode form).  n_splits > 1 writes partial results to
@@ -857,6 +915,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     a.n_splits = n_splits;
     a.cluster_merge = cluster_merge ? 1 : 0;
     a.one_token_each = (max_q_len == 1 && n_tokens == n_seqs) ? 1 : 0;
+    a.stamps = g_decode_stamps;
     const long long gy = (long long)kv_heads * a.head_chunks * n_splits;
     if (gy > 65535) return MLC_ERR_BAD_SIZE;
     PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, kv_heads, hd};
