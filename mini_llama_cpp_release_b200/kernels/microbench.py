@@ -11,7 +11,8 @@ of `--copies` launches captured back to back in one CUDA graph, each on its own 
 weights or cache so that the data comes from HBM as it does in a model with that many layers.
 The second figure is what a decode step pays.  `--library` times the library's matrix product
 on the same operands for comparison.  With `--once` the kernel runs a single time (the mode to
-put under a profiler).
+put under a profiler).  `attention --q-len 1 --cluster --phases` prints where the single-token attention kernel's
+time goes: nanosecond stamps that thread 0 of every block takes between the kernel's phases, inside the chain.
 """
 from __future__ import annotations
 
@@ -196,10 +197,60 @@ def bench_attention(args) -> None:
             return
         kernels.attention_mma(q, out, cu, start, B, q_len, H, kv, 1 / math.sqrt(hd), 0, row_tiles, n_splits, part_ml, part_o)
 
+    if args.phases:
+        decode_phases(args, fn, B * KV * max(1, (H // KV + 15) // 16) * n_splits, n_splits)
+        return
     nbytes = 2.0 * B * L * KV * hd * 2
     flops = 4.0 * B * H * hd * (q_len * L - q_len * (q_len - 1) / 2)
     report(f"attention impl={args.impl} seqs={B} q_len={q_len} context={L} H={H} KV={KV} hd={hd} row_tiles={row_tiles} splits={n_splits}",
            fn, args, nbytes, flops)
+
+
+PHASES = ["entered", "kernels before done", "page list, position, queries arrived", "first keys asked for", "queries staged",
+          "warp 0 through its keys", "all warps through", "warps' results in shared memory", "warps merged (and sent)",
+          "cluster's results arrived", "done"]
+PHASE_SLOT = [0, 1, 2, 8, 3, 4, 5, 10, 9, 6, 7]          # where the kernel leaves each of them
+
+
+def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
+    """The single-token kernel between small kernels, as it sits between the products of a decode step."""
+    import ctypes
+    if args.q_len != 1 or args.impl != "mma":
+        raise SystemExit("--phases is for the single-token kernel (--q-len 1, --impl mma)")
+    lib = kernels.attention_library(args.head_dim)
+    lib.mlc_attention_decode_stamps.argtypes = [ctypes.c_void_p]
+    C = args.copies
+    x = torch.zeros(args.seqs, 896, device=DEV)
+    gain = torch.ones(896, device=DEV)
+    h = torch.empty(args.seqs, 896, dtype=torch.bfloat16, device=DEV)
+    stamps = torch.zeros(C, blocks, 12, dtype=torch.int64, device=DEV)
+
+    def chain(record: bool) -> None:
+        for i in range(C):
+            kernels.add_rmsnorm(x, None, gain, 1e-6, h)
+            lib.mlc_attention_decode_stamps(stamps[i].data_ptr() if record else None)
+            fn(i)
+        lib.mlc_attention_decode_stamps(None)
+
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        chain(False)
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            chain(True)
+        for _ in range(3):
+            g.replay()
+        s.synchronize()
+    t = stamps.cpu().double()[min(2, C - 1):]
+    t0 = t[:, :, 1].min(dim=1, keepdim=True).values               # the kernels before are done
+    out = {"blocks": blocks, "splits": n_splits, "unit": "us after the kernels before were done: mean over blocks, latest block"}
+    for name, slot in zip(PHASES, PHASE_SLOT):
+        if slot == 6 and n_splits == 1:
+            continue
+        rel = (t[:, :, slot] - t0) / 1e3
+        out[name] = [round(rel.mean().item(), 2), round(rel.max(dim=1).values.mean().item(), 2)]
+    print(json.dumps(out, indent=1))
 
 
 def main(argv=None) -> int:
@@ -225,6 +276,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--cluster", action="store_true", help="single tokens: merge key splits inside a thread-block cluster")
     ap.add_argument("--impl", default="mma", choices=["mma", "tcgen05"], help="attention kernel")
+    ap.add_argument("--phases", action="store_true", help="single-token attention: time stamps of the kernel's phases")
     args = ap.parse_args(argv)
     kernels.set_pdl(not args.no_pdl)
     if args.kernel == "gemm":
