@@ -95,7 +95,6 @@ def bench_gemm(args) -> None:
     nbytes = N * K * 2 + T * K * 2
     flops = 2.0 * T * N * K
     epi = {"store": 0, "silu": 1, "qkv": 2, "add": 3}[args.epilogue]
-    norm = {}
     if args.library:
         out = torch.empty(T, N, dtype=torch.float32, device=DEV)
         report(f"library product T={T} N={N} K={K}", lambda i: torch.mm(x, ws[i % C].t(), out_dtype=torch.float32, out=out),
@@ -129,7 +128,7 @@ def bench_gemm(args) -> None:
         return
     if epi == 0:
         out = torch.empty(args.splits, T, N, dtype=torch.float32, device=DEV)
-        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 0, args.splits, args.block_tokens, **norm)
+        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 0, args.splits, args.block_tokens)
         nbytes += args.splits * T * N * 4
     elif epi == 3:
         out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
@@ -137,7 +136,7 @@ def bench_gemm(args) -> None:
         nbytes += T * N * 4
     elif epi == 1:
         out = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
-        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 1, 1, args.block_tokens, **norm)
+        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 1, 1, args.block_tokens)
         nbytes += T * N
     else:
         hd, KV = args.head_dim, args.kv_heads
@@ -154,7 +153,7 @@ def bench_gemm(args) -> None:
         bias = torch.randn(N, device=DEV)
         out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
         fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 2, 1, args.block_tokens, bias=bias, positions=positions,
-                                            tok_seq=tok_seq, rope=rope, q_heads=H, kv_heads=KV, head_dim=hd, kv=kv, **norm)
+                                            tok_seq=tok_seq, rope=rope, q_heads=H, kv_heads=KV, head_dim=hd, kv=kv)
         nbytes += T * N * 2
     report(f"tcgen05 product T={T} N={N} K={K} epilogue={args.epilogue} splits={args.splits}", fn, args, nbytes, flops)
 
