@@ -438,8 +438,6 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         ? a.stamps + 12ull * (blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z)) : nullptr;
     if (stamps) stamps[0] = stamp_ns();                                   // entry
     grid_launch_dependents();
-    grid_dependency_wait();                    // queries and the step's keys were written by the kernel before
-    if (stamps) stamps[1] = stamp_ns();                                   // the kernels before are done
     const int b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int y = blockIdx.y;
@@ -448,10 +446,11 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     const int kvh = y;
     const int tok0 = blockIdx.x * a.tokens_per_block;
     const int GH = a.heads_per_block;
-    // Everything that does not depend on anything else is asked of memory at once: the sequence's page list (before its
-    // length is known), its position, its first token, and, when every sequence brings exactly one token (then sequence
-    // b's token is token b), the query rows themselves.  Two trips to memory lie between the start and the first keys
-    // then (pages, keys) instead of four (first token, queries, pages, keys).
+    // What the kernel before this one writes is the step's queries and the step's own keys and values, at positions
+    // from start_pos on.  The description of the step (page lists, positions, token ranges) was complete before the
+    // step's first kernel, and the keys before start_pos were written by earlier steps.  So the page list, the position
+    // and the first sub-tiles of older keys are asked for now, while the kernel before may still be running; only the
+    // queries, and a sub-tile that holds a key of this step, wait for it.
     for (int t = tid; t < c.pages_per_seq && t < D_TILES_STAGED; t += DNW * 32)
         tile_pages[t] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
     const int start = a.start_pos[b];
@@ -465,20 +464,6 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     }
     if (tok0 >= q_len) return;
     const int n_tok = min(a.tokens_per_block, q_len - tok0);
-    constexpr int Q_PER_THREAD = (16 * CPR + DNW * 32 - 1) / (DNW * 32);
-    uint4 qv[Q_PER_THREAD];
-#pragma unroll
-    for (int u = 0; u < Q_PER_THREAD; ++u) {
-        const int idx = tid + u * DNW * 32;
-        const int r = idx / CPR, ch = idx % CPR;
-        const int t = r / GH, hg = chunk * GH + r % GH;
-        qv[u] = make_uint4(0, 0, 0, 0);
-        if (idx < 16 * CPR && t < n_tok && hg < a.group) {
-            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
-            qv[u] = *reinterpret_cast<const uint4*>(a.q + row * HD + ch * 8);
-        }
-    }
-
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
     const int tile_begin = lo_block / TILE, tile_end = p_last / TILE + 1;          // in 64-key pages
@@ -486,9 +471,8 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     const int my_begin = tile_begin + split * per_split;
     const int my_end = min(tile_end, my_begin + per_split);
     __syncthreads();                           // the page list is in shared memory
-    if (stamps) stamps[2] = stamp_ns();                                   // page list, position and queries have arrived
+    if (stamps) stamps[2] = stamp_ns();                                   // page list and position have arrived
 
-    // ---- the warp's first sub-tiles of keys and values are requested before the queries are staged
     constexpr int SUB = TILE / DKT;                     // sub-tiles per page
     const int st_begin = my_begin * SUB, st_end = my_end * SUB;
     const bf16* kp = (const bf16*)c.k_pool;
@@ -511,13 +495,43 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         }
     };
 
+    // ---- the warp's first sub-tiles, one copy group each and in order: those whose keys all lie before the step's
+    // first position now, the others (the sequence's last sub-tile, as a rule) once the kernel before is done
     int st = st_begin + warp;
+    int early = 0;
 #pragma unroll
     for (int p = 0; p < D_NSTAGE - 1; ++p) {
-        if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
-        cp_async_commit();
+        const int sp = st + DNW * p;
+        if (early == p && (sp >= st_end || sp * DKT + DKT - 1 < start)) {
+            if (sp < st_end) load_sub(p, sp);
+            cp_async_commit();
+            early = p + 1;
+        }
     }
-    if (stamps) stamps[8] = stamp_ns();                                   // warp 0 has asked for its first keys
+    if (stamps) stamps[8] = stamp_ns();                                   // warp 0 has asked for its first older keys
+
+    grid_dependency_wait();                    // queries and the step's keys were written by the kernel before
+    if (stamps) stamps[1] = stamp_ns();                                   // the kernels before are done
+    constexpr int Q_PER_THREAD = (16 * CPR + DNW * 32 - 1) / (DNW * 32);
+    uint4 qv[Q_PER_THREAD];
+#pragma unroll
+    for (int u = 0; u < Q_PER_THREAD; ++u) {
+        const int idx = tid + u * DNW * 32;
+        const int r = idx / CPR, ch = idx % CPR;
+        const int t = r / GH, hg = chunk * GH + r % GH;
+        qv[u] = make_uint4(0, 0, 0, 0);
+        if (idx < 16 * CPR && t < n_tok && hg < a.group) {
+            const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+            qv[u] = *reinterpret_cast<const uint4*>(a.q + row * HD + ch * 8);
+        }
+    }
+#pragma unroll
+    for (int p = 0; p < D_NSTAGE - 1; ++p) {
+        if (p >= early) {
+            if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
+            cp_async_commit();
+        }
+    }
 
 #pragma unroll
     for (int u = 0; u < Q_PER_THREAD; ++u) {

@@ -205,10 +205,10 @@ def bench_attention(args) -> None:
            fn, args, nbytes, flops)
 
 
-PHASES = ["entered", "kernels before done", "page list, position, queries arrived", "first keys asked for", "queries staged",
+PHASES = ["entered", "page list and position arrived", "first older keys asked for", "kernels before done", "queries staged",
           "warp 0 through its keys", "all warps through", "warps' results in shared memory", "warps merged (and sent)",
           "cluster's results arrived", "done"]
-PHASE_SLOT = [0, 1, 2, 8, 3, 4, 5, 10, 9, 6, 7]          # where the kernel leaves each of them
+PHASE_SLOT = [0, 2, 8, 1, 3, 4, 5, 10, 9, 6, 7]          # where the kernel leaves each of them
 
 
 def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
