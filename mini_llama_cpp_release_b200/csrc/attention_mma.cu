@@ -414,7 +414,7 @@ constexpr int DNW = (HD <= 128) ? 8 : 4;                         // warps per bl
 constexpr int DKT = (HD <= 64) ? 32 : 16;                        // keys per sub-tile
 constexpr int D_STAGE = DKT * STRIDE;                            // elements per stage and operand
 constexpr int D_NT_S = DKT / 8, D_KS_PV = DKT / 16;
-constexpr int D_NSTAGE = 3;                                      // stages per warp: two sub-tiles in flight while one is used
+constexpr int D_NSTAGE = 3;                                      // stages per warp: all filled before the loop, then two sub-tiles in flight while one is used
 constexpr int D_TILES_STAGED = 512;                              // page numbers kept in shared memory (32,768 keys); later tiles look theirs up
 constexpr int D_MAX_CLUSTER = 16;                                // the largest cluster there is
 // Cluster merge: what the other blocks of a cluster send this one.  Its share of the 16 x HD outputs (at most a
@@ -495,12 +495,13 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         }
     };
 
-    // ---- the warp's first sub-tiles, one copy group each and in order: those whose keys all lie before the step's
-    // first position now, the others (the sequence's last sub-tile, as a rule) once the kernel before is done
+    // ---- the warp's first sub-tiles, one for every stage, one copy group each and in order: those whose keys all lie
+    // before the step's first position now, the others (the sequence's last sub-tile, as a rule) once the kernel before
+    // is done.  With a few sub-tiles a warp (eight sequences: under three) its whole share is on its way before the wait.
     int st = st_begin + warp;
     int early = 0;
 #pragma unroll
-    for (int p = 0; p < D_NSTAGE - 1; ++p) {
+    for (int p = 0; p < D_NSTAGE; ++p) {
         const int sp = st + DNW * p;
         if (early == p && (sp >= st_end || sp * DKT + DKT - 1 < start)) {
             if (sp < st_end) load_sub(p, sp);
@@ -526,7 +527,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         }
     }
 #pragma unroll
-    for (int p = 0; p < D_NSTAGE - 1; ++p) {
+    for (int p = 0; p < D_NSTAGE; ++p) {
         if (p >= early) {
             if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
             cp_async_commit();
@@ -569,8 +570,11 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     if (stamps) stamps[3] = stamp_ns();                                   // queries staged, first keys requested
     for (int it = 0; st < st_end; st += DNW, ++it) {
         const int stage = it % D_NSTAGE;
-        if (st + DNW * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + DNW * (D_NSTAGE - 1));
-        cp_async_commit();
+        if (it > 0) {
+            // every stage was filled before the loop; the stage read out in the last round takes the sub-tile two on
+            if (st + DNW * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + DNW * (D_NSTAGE - 1));
+            cp_async_commit();
+        }
         cp_async_wait<D_NSTAGE - 1>();
         __syncwarp();
 
