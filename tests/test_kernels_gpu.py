@@ -507,6 +507,82 @@ def test_single_token_attention_merges_key_splits_inside_a_cluster(n_splits, H, 
     assert float((got - 7.0).abs().max()) < 0.2
 
 
+@pytest.mark.parametrize("lens", [[700, 449, 65, 2048], [64, 1, 130, 513, 1000, 33, 257, 900]])
+@pytest.mark.parametrize("in_graph", [False, True])
+def test_single_token_attention_waits_for_the_steps_own_key(lens, in_graph):
+    """The single-token kernel asks for older keys before it waits for the kernel before it, which writes the step's own
+    key and value.  Here that kernel is the real Q/K/V product, launched right before on the same stream, and the place
+    of the new key holds NaN until it writes there: in a page's middle, in a page's first place, in a cluster's last
+    block.  A sub-tile fetched too early shows as NaN, whatever the weights."""
+    H, KV, hd, K = 14, 2, 64, 72
+    B = len(lens)
+    g = torch.Generator().manual_seed(sum(lens))
+    ks = [torch.randn(n, KV, hd, generator=g).to(torch.bfloat16).float() for n in lens]
+    vs = [torch.randn(n, KV, hd, generator=g).to(torch.bfloat16).float() for n in lens]
+    poisoned_k, poisoned_v = [k.clone() for k in ks], [v.clone() for v in vs]
+    for k, v in zip(poisoned_k, poisoned_v):
+        k[-1] = float("nan")
+        v[-1] = float("nan")
+    kv = make_paged(poisoned_k, poisoned_v, torch.bfloat16, seed=B)
+    k_poison, v_poison = kv.k_pool.clone(), kv.v_pool.clone()
+    x = (torch.randn(B, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((H + 2 * KV) * hd, K, generator=g) * 0.3).to(torch.bfloat16)
+    bias = torch.randn((H + 2 * KV) * hd, generator=g)
+    half = hd // 2
+    within = torch.stack([torch.arange(half), torch.arange(half) + half], dim=1).reshape(-1)
+    order = (torch.arange(H + 2 * KV)[:, None] * hd + within[None, :]).reshape(-1)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    full = x.float() @ w.float().t() + bias
+    q_ref = plain_impl.rope_neox(full[:, :H * hd].reshape(B, H, hd), positions, 1e6).to(torch.bfloat16).float()
+    k_new = plain_impl.rope_neox(full[:, H * hd:(H + KV) * hd].reshape(B, KV, hd), positions, 1e6).to(torch.bfloat16).float()
+    v_new = full[:, (H + KV) * hd:].reshape(B, KV, hd).to(torch.bfloat16).float()
+    want = []
+    for b, n in enumerate(lens):
+        kb, vb = ks[b].clone(), vs[b].clone()
+        kb[-1], vb[-1] = k_new[b], v_new[b]
+        qb = torch.zeros(n, H, hd)
+        qb[-1] = q_ref[b]
+        want.append(plain_impl.attention(qb, kb, vb, None)[-1])
+    want = torch.stack(want)
+
+    xd, wd, bd = x.to(DEV), w[order].contiguous().to(DEV), bias[order].contiguous().to(DEV)
+    pos_d, seq_d = positions.to(DEV), torch.arange(B, dtype=torch.int32, device=DEV)
+    table = kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), 4096)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    q = torch.empty(B, H * hd, dtype=torch.bfloat16, device=DEV)
+    out = torch.empty_like(q)
+    n_splits = kernels.attention_decode_splits(hd, B * KV, max(lens))
+
+    def step():
+        kv.k_pool.copy_(k_poison)                  # NaN again where the step's keys and values will go
+        kv.v_pool.copy_(v_poison)
+        kernels.gemm_tcgen05(xd, wd, q, 2, bias=bd, positions=pos_d, tok_seq=seq_d, rope=table, q_heads=H, kv_heads=KV,
+                             head_dim=hd, kv=kv, block_tokens=16)
+        kernels.attention_mma(q, out, cu, pos_d, B, 1, H, kv, 1.0 / math.sqrt(hd), 0, 1, n_splits, None, None)
+
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        step()
+        s.synchronize()
+        if in_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                step()
+        for _ in range(6):                         # what would go wrong is a matter of timing
+            out.fill_(float("nan"))
+            if in_graph:
+                graph.replay()
+            else:
+                step()
+            s.synchronize()
+            kernels.check_gemm_status(DEV)
+            got = out.float().cpu().view(B, H, hd)
+            assert torch.isfinite(got).all()
+            close(got, want, 1e-2)
+    torch.cuda.current_stream().wait_stream(s)
+
+
 def test_cluster_merge_is_refused_for_prompts_and_too_many_splits():
     limit = kernels.attention_decode_cluster_limit(64)
     assert limit in (8, 16)
