@@ -407,8 +407,8 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
 // One decoded token per sequence gives a block at most 16 rows (the query heads of one kv head).
 // With so few rows the work per key is small and what counts is how few instructions a key costs
 // and how many bytes are in flight.  Each warp therefore runs on its own: it copies whole
-// sub-tiles of DKT keys (keys and values) into its own two shared-memory stages, computes all 16
-// rows against them, and never meets the other warps until the end, where the four partial
+// sub-tiles of DKT keys (keys and values) into its own three shared-memory stages, computes all 16
+// rows against them, and never meets the other warps until the end, where the warps' partial
 // results are merged.  Warp w of DNW takes sub-tiles w, w + DNW, w + 2 DNW, ... of the block's key range.
 constexpr int DNW = (HD <= 128) ? 8 : 4;                         // warps per block: two per scheduler hide each other's latencies
 constexpr int DKT = (HD <= 64) ? 32 : 16;                        // keys per sub-tile
@@ -681,7 +681,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
     }
 
-    // ---- merge the four warps' partial results
+    // ---- merge the warps' partial results
     if (stamps) stamps[4] = stamp_ns();                                   // warp 0 is through its keys
     __syncthreads();
     if (stamps) stamps[5] = stamp_ns();                                   // every warp is

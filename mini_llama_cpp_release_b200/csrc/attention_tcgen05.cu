@@ -464,8 +464,10 @@ using namespace mlc;
 // q, out: bfloat16 [n_tokens][q_heads*hd], 16-byte aligned; the cache entry starts `entry_offset` elements into the
 // pools and holds `pool_pages` pages of 64 tokens, [page][kv_head][64][hd].  hd is the head size the library was
 // built for (64 or 128; other sizes and pages of another length are refused with MLC_ERR_UNSUPPORTED).  status: one int on the device, 0 before the call; a bounded wait that
-// ran out leaves 11, 12 or 13 there.  timing: null, or [blocks][16] int64 that receive the clock cycles one softmax
-// warp (0-6; 7 is the block's number of tiles) and the issuing thread (8-13) of each block spent in their phases.
+// ran out leaves 11, 12 or 13 there.  timing: null, or [blocks][16] int64 that receive the clock cycles the first team's
+// first warp of each block spent in its phases (0 waiting for scores, 1 reading them, 2 exponentials and P, 3 hand-over,
+// 4 waiting for the last product), the block's number of tiles (7), and the cycles from the block's entry to that
+// warp's start (14) and end (15).
 extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
                                      int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
                                      int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,

@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_decode_stamps", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -339,6 +339,8 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
         lib.mlc_attention_decode_clusters_resident.restype = c_int
         lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P]
         lib.mlc_attention_tcgen05.restype = c_int
+        lib.mlc_attention_decode_stamps.argtypes = [P]
+        lib.mlc_attention_decode_stamps.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
         _attn_libs[head_dim] = lib
@@ -374,6 +376,16 @@ def attention_decode_splits(head_dim: int, blocks: int, max_kv_len: int, keys_pe
 def attention_decode_cluster_limit(head_dim: int) -> int:
     """The largest cluster the single-token attention kernel can merge key splits in."""
     return max(s for s in range(1, 17) if s == 1 or attention_decode_clusters_resident(head_dim, s) > 0)
+
+
+def attention_decode_stamps(head_dim: int, stamps: Optional[torch.Tensor]) -> None:
+    """Measurement hook of the single-token attention kernel: launches that follow leave nanosecond stamps of their
+    phases in `stamps` (int64 [blocks, 12] on the device); None switches it off again."""
+    lib = attention_library(head_dim)
+    if stamps is not None:
+        require_cuda(stamps)
+        assert stamps.dtype == torch.int64 and stamps.dim() == 2 and stamps.shape[1] == 12 and stamps.is_contiguous()
+    _check(lib.mlc_attention_decode_stamps(stamps.data_ptr() if stamps is not None else None), "attention stamps")
 
 
 def attention_mma_plan(max_q_len: int, n_seqs: int, max_kv_len: int, q_heads: int, kv_heads: int, n_sms: int):

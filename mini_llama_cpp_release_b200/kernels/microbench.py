@@ -213,11 +213,8 @@ PHASE_SLOT = [0, 2, 8, 1, 3, 4, 5, 10, 9, 6, 7]          # where the kernel leav
 
 def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
     """The single-token kernel between small kernels, as it sits between the products of a decode step."""
-    import ctypes
     if args.q_len != 1 or args.impl != "mma":
         raise SystemExit("--phases is for the single-token kernel (--q-len 1, --impl mma)")
-    lib = kernels.attention_library(args.head_dim)
-    lib.mlc_attention_decode_stamps.argtypes = [ctypes.c_void_p]
     C = args.copies
     x = torch.zeros(args.seqs, 896, device=DEV)
     gain = torch.ones(896, device=DEV)
@@ -227,9 +224,9 @@ def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
     def chain(record: bool) -> None:
         for i in range(C):
             kernels.add_rmsnorm(x, None, gain, 1e-6, h)
-            lib.mlc_attention_decode_stamps(stamps[i].data_ptr() if record else None)
+            kernels.attention_decode_stamps(args.head_dim, stamps[i] if record else None)
             fn(i)
-        lib.mlc_attention_decode_stamps(None)
+        kernels.attention_decode_stamps(args.head_dim, None)
 
     s = torch.cuda.Stream()
     with torch.cuda.stream(s):
