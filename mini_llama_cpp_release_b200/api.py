@@ -33,11 +33,12 @@ class LLM:
         self.config = model.config
         self.context = Context(model, max_tokens, max_seqs)
 
-    def generate(self, prompts: Sequence[Sequence[int]], n_predict: int = 16, temperature: float = 0.0,
+    def generate(self, prompts: Sequence[Sequence[int]], n_predict: Union[int, Sequence[int]] = 16, temperature: float = 0.0,
                  top_k: int = 0, seed: int = 0, stop_token_ids: Optional[Sequence[int]] = None,
                  max_batch: Optional[int] = None, return_details: bool = False, on_step=None
                  ) -> Union[List[List[int]], List[GenerationResult]]:
-        """Generated ids for each prompt (lists of token ids).  `stop_token_ids` defaults to the
+        """Generated ids for each prompt (lists of token ids).  `n_predict` is one number for all
+        requests or one per request.  `stop_token_ids` defaults to the
         checkpoint's `eos_token_id`, if it has one.  `on_step(live, chosen, logits)`, if given, is
         called after every choice with the indices of the live requests, their chosen ids and
         the logits they were chosen from."""

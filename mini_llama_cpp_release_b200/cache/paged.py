@@ -64,8 +64,22 @@ def plan_groups(needs: Sequence[Optional[CacheNeed]], reads_cache_of: Sequence[O
             if needs[e] is not None and needs[src] is not None and (
                     needs[e].kv_heads != needs[src].kv_heads or needs[e].head_dim != needs[src].head_dim):
                 raise ValueError(f"schedule entry {e} cannot read the cache of entry {src}: kv heads or head size differ")
+            if needs[e] is not None and needs[src] is not None and needs[src].kind == "window" and (
+                    needs[e].kind != "window" or (needs[e].window or 0) > (needs[src].window or 0)):
+                # the owner gives pages back once its own window has passed them; a reader that looks further back
+                # would find them gone
+                raise ValueError(f"schedule entry {e} cannot read the cache of entry {src}: it reads "
+                                 f"{'all keys' if needs[e].kind != 'window' else f'a window of {needs[e].window}'}, "
+                                 f"the owner keeps a window of {needs[src].window}")
             where[e] = where[src]
     return groups, where
+
+
+def cache_bytes_per_token(needs: Sequence[Optional[CacheNeed]], reads_cache_of: Sequence[Optional[int]], itemsize: int) -> int:
+    """Key and value bytes one token of one sequence occupies over all groups, for elements of `itemsize` bytes
+    (a window group holds at most its window of them)."""
+    groups, _ = plan_groups(needs, reads_cache_of)
+    return sum(2 * len(g.entries) * g.need.kv_heads * g.need.head_dim * itemsize for g in groups)
 
 
 class SlotBook:
@@ -83,13 +97,23 @@ class SlotBook:
         self.pages = [FreeList(self.n_pages, f"page of group {g}") for g in range(len(self.groups))]
         self.length: Dict[int, int] = {}
         self.page_lists: Dict[int, List[List[int]]] = {}          # slot → per group → page per page index (-1: none)
+        # slot → a number that changes whenever the slot's page lists change and is never used twice, so that whoever
+        # keeps a copy of the lists (a captured decode step's page table on the device) can tell that it is stale,
+        # also when the slot was given back and taken again in between
+        self.page_version: Dict[int, int] = {}
+        self._versions = 0
 
     # ---- slots
     def acquire(self) -> int:
         slot = self.slots.take()
         self.length[slot] = 0
         self.page_lists[slot] = [[] for _ in self.groups]
+        self._touch(slot)
         return slot
+
+    def _touch(self, slot: int) -> None:
+        self._versions += 1
+        self.page_version[slot] = self._versions
 
     def release(self, slot: int) -> None:
         if slot not in self.length:
@@ -100,6 +124,7 @@ class SlotBook:
                     self.pages[g].give_back(p)
         del self.page_lists[slot]
         del self.length[slot]
+        del self.page_version[slot]
         self.slots.give_back(slot)
 
     def _require(self, slot: int) -> None:
@@ -120,6 +145,8 @@ class SlotBook:
                     f"{self.pages[g].n_free} of {self.n_pages} are free (the cache was sized for too few tokens)")
         for g, k in enumerate(want):
             self.page_lists[slot][g].extend(self.pages[g].take_many(k))
+        if any(want):
+            self._touch(slot)
 
     def commit(self, slot: int, n_new: int) -> None:
         """The n_new tokens are in the cache now; drop pages a window has left behind."""
@@ -135,6 +162,7 @@ class SlotBook:
                     if plist[i] >= 0:
                         self.pages[g].give_back(plist[i])
                         plist[i] = -1
+                        self._touch(slot)
 
     def tokens_held(self) -> int:
         """Tokens of live sequences, each rounded up to whole pages (the figure the cache is sized by)."""
@@ -173,6 +201,7 @@ class PagedCache(SlotBook):
         self.state: List[Optional[torch.Tensor]] = [
             torch.zeros((self.max_seqs, *s.shape), dtype=s.dtype, device=device) if s is not None else None
             for s in states]
+        self.has_state = any(s is not None for s in self.state)
 
     def acquire(self) -> int:
         slot = super().acquire()
@@ -180,6 +209,19 @@ class PagedCache(SlotBook):
             if s is not None:
                 s[slot].zero_()
         return slot
+
+    def snapshot_state(self, slots_long: torch.Tensor) -> List[Optional[torch.Tensor]]:
+        """Copies of the given slots' rows of every state area; `restore_state` puts them back.  A step that is run
+        once to warm up before it is captured into a graph, and then replayed, would otherwise advance its
+        sequences' state twice (keys and values are written to the same places both times; state is not)."""
+        if not self.has_state:
+            return []
+        return [s.index_select(0, slots_long) if s is not None else None for s in self.state]
+
+    def restore_state(self, saved: Sequence[Optional[torch.Tensor]], slots_long: torch.Tensor) -> None:
+        for s, rows in zip(self.state, saved):
+            if s is not None:
+                s.index_copy_(0, slots_long, rows)
 
     def bytes(self) -> int:
         n = sum(t.numel() * t.element_size() for t in self.k_pools + self.v_pools)

@@ -165,14 +165,17 @@ def cmd_inspect(argv: Sequence[str]) -> int:
     args = ap.parse_args(argv)
     from mini_llama_cpp_release_b200.config import ModelConfig, build_model_spec
     from mini_llama_cpp_release_b200.engine.model import build_parts
+    from mini_llama_cpp_release_b200.cache.paged import cache_bytes_per_token
     from mini_llama_cpp_release_b200.weights import Checkpoint, compare, expected_tensors
+    from mini_llama_cpp_release_b200.weights.loader import ignorable_tensors
     cfg = ModelConfig.from_folder(args.model)
     spec = build_model_spec(cfg)
     print("config:")
     for k, v in cfg.to_dict().items():
         print(f"  {k}: {v}")
     print(f"architecture: {cfg.architecture} -> {len(spec.layers)} layers, {len(spec.schedule)} runs per step")
-    specs = expected_tensors(build_parts(spec).all_parts())
+    parts = build_parts(spec)
+    specs = expected_tensors(parts.all_parts())
     with Checkpoint(args.model) as ck:
         total = params = 0
         print("tensors:")
@@ -182,9 +185,12 @@ def cmd_inspect(argv: Sequence[str]) -> int:
             params += e.numel
             role = specs[name].role if name in specs else "(not used)"
             print(f"  {name:55s} {str(list(e.shape)):18s} {e.dtype:5s} {nbytes:12d} B  {role}")
-        problems = compare(ck.entries, specs, ["lm_head.weight"] if cfg.tie_word_embeddings else [])
+        problems = compare(ck.entries, specs, ignorable_tensors(parts.all_parts()))
     print(f"parameters: {params}   bytes: {total}")
-    kv = 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim
+    # what the runs of the schedule declare that they keep, asked of the cache's own planner
+    mixers = [getattr(parts.blocks[e.layer], "mixer", None) for e in spec.schedule]
+    needs = [m.cache_need() if hasattr(m, "cache_need") else None for m in mixers]
+    kv = cache_bytes_per_token(needs, [e.reads_cache_of for e in spec.schedule], 1)
     print(f"cache per token per sequence: {kv * 2} B in bfloat16, {kv * 4} B in float32")
     for line in problems:
         print("PROBLEM:", line)

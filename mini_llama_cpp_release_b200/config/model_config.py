@@ -2,137 +2,99 @@
 
 The reference keeps an 11-field `ModelConfig` (include/mini_llama/model.h:17-29) filled
 from its own containers (src/loader.cpp:347-362; src/gguf_loader.cpp:243-317) and checks
-it (src/loader.cpp:269-290).  Here the same quantities come from the keys that a Qwen2
-checkpoint's config.json carries; nothing that config.json gives is a constant in code.
+it (src/loader.cpp:269-290).  Here a config.json names its model class in
+`architectures[0]`; that name picks, in the registry, the class that reads the rest of
+the keys.
 
-`ModelConfig` is what every architecture shares; the architecture's builder (see
-`config.registry`) turns it into layer specifications.
+`ModelConfig`, below, is what every architecture shares and all the engine itself reads:
+the architecture's name, the vocabulary, the largest position, the stop and start tokens,
+the stored element type.  Every other key is the architecture's business: an architecture
+registers a subclass with typed fields for its own keys and its own checks (the one of
+this library: `models/qwen2.py`), or none, and then finds its keys in `extra` (also
+readable as attributes).  Nothing that config.json gives is a constant in code.
 """
 from __future__ import annotations
 
+import dataclasses
 import json
-import math
 import os
-from dataclasses import dataclass, field, asdict
-from typing import Any, Dict, List, Optional, Tuple
+from dataclasses import dataclass, field
+from typing import Any, Dict, Optional, Tuple
 
 
 class ConfigError(ValueError):
     """A config.json that cannot be used; the message names the key."""
 
 
-_REQUIRED = (
-    "hidden_size",
-    "intermediate_size",
-    "num_hidden_layers",
-    "num_attention_heads",
-    "vocab_size",
-    "max_position_embeddings",
-)
+def as_int(raw: Dict[str, Any], key: str) -> int:
+    """raw[key] as an integer; a missing key or a value that is not a whole number is an error that names the key."""
+    if key not in raw or raw[key] is None:
+        raise ConfigError(f"missing config key: {key}")                          # src/loader.cpp:26-31
+    v = raw[key]
+    if isinstance(v, bool) or not isinstance(v, (int, float)) or int(v) != v:
+        raise ConfigError(f"config key {key} must be an integer, got {v!r}")
+    return int(v)
 
 
-@dataclass(frozen=True)
+def _token_ids(v: Any) -> Optional[Tuple[int, ...]]:
+    if isinstance(v, bool):
+        return None
+    if isinstance(v, int):
+        return (v,)
+    if isinstance(v, (list, tuple)):
+        return tuple(int(e) for e in v)
+    return None
+
+
+@dataclass(frozen=True, kw_only=True)
 class ModelConfig:
     architecture: str
-    hidden_size: int
-    intermediate_size: int
-    num_hidden_layers: int
-    num_attention_heads: int
-    num_key_value_heads: int
-    head_dim: int
     vocab_size: int
     max_position_embeddings: int
-    rope_theta: float = 10000.0
-    rms_norm_eps: float = 1e-6
-    tie_word_embeddings: bool = False
-    hidden_act: str = "silu"
-    attention_bias: bool = True
-    use_sliding_window: bool = False
-    sliding_window: Optional[int] = None
-    max_window_layers: Optional[int] = None
     torch_dtype: str = "bfloat16"
     bos_token_id: Optional[int] = None
     eos_token_id: Optional[Tuple[int, ...]] = None
-    extra: Dict[str, Any] = field(default_factory=dict, compare=False)
+    extra: Dict[str, Any] = field(default_factory=dict, compare=False)      # every key no field took, as config.json has it
 
-    # ------------------------------------------------------------------ derived sizes
-    @property
-    def q_size(self) -> int:
-        return self.num_attention_heads * self.head_dim
-
-    @property
-    def kv_size(self) -> int:
-        return self.num_key_value_heads * self.head_dim
-
-    def window_of_layer(self, layer: int) -> Optional[int]:
-        """Window (in keys) of a layer, or None for all keys.  The reference has no
-        window (src/forward.cpp:591 loops over every earlier position); when the
-        checkpoint turns it on, layers from `max_window_layers` upward use it."""
-        if not self.use_sliding_window or not self.sliding_window:
-            return None
-        first = self.max_window_layers if self.max_window_layers is not None else self.num_hidden_layers
-        return int(self.sliding_window) if layer >= first else None
+    def __getattr__(self, name: str) -> Any:
+        # only reached when no field or property has the name: an architecture without a class of its own reads
+        # its keys this way
+        extra = self.__dict__.get("extra")
+        if extra is not None and name in extra:
+            return extra[name]
+        raise AttributeError(f"{type(self).__name__} has no field or config.json key {name!r}")
 
     # ------------------------------------------------------------------ construction
-    @staticmethod
-    def from_dict(raw: Dict[str, Any]) -> "ModelConfig":
-        archs = raw.get("architectures")
-        if not archs or not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
-            raise ConfigError("missing config key: architectures (a list whose first entry names the model class)")
-        for key in _REQUIRED:
-            if key not in raw:
-                raise ConfigError(f"missing config key: {key}")              # src/loader.cpp:26-31
-        heads = _as_int(raw, "num_attention_heads")
-        hidden = _as_int(raw, "hidden_size")
-        if raw.get("head_dim") is not None:
-            head_dim = _as_int(raw, "head_dim")
-        else:
-            if heads <= 0 or hidden % heads != 0:                             # src/loader.cpp:274-277
-                raise ConfigError(f"hidden_size {hidden} is not divisible by num_attention_heads {heads} and no head_dim is given")
-            head_dim = hidden // heads
-        eos = raw.get("eos_token_id")
-        if isinstance(eos, int):
-            eos = (eos,)
-        elif isinstance(eos, (list, tuple)):
-            eos = tuple(int(e) for e in eos)
-        else:
-            eos = None
-        if raw.get("rope_scaling") not in (None, {}):
-            raise ConfigError("rope_scaling is not supported: the reference rotates by plain integer positions (src/ops.cpp:125-141)")
-        known = {
-            "architectures", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
-            "num_key_value_heads", "head_dim", "vocab_size", "max_position_embeddings", "rope_theta", "rms_norm_eps",
-            "tie_word_embeddings", "hidden_act", "attention_bias", "use_sliding_window", "sliding_window",
-            "max_window_layers", "torch_dtype", "bos_token_id", "eos_token_id", "rope_scaling",
-        }
-        cfg = ModelConfig(
-            architecture=archs[0],
-            hidden_size=hidden,
-            intermediate_size=_as_int(raw, "intermediate_size"),
-            num_hidden_layers=_as_int(raw, "num_hidden_layers"),
-            num_attention_heads=heads,
-            num_key_value_heads=_as_int(raw, "num_key_value_heads") if raw.get("num_key_value_heads") is not None else heads,
-            head_dim=head_dim,
-            vocab_size=_as_int(raw, "vocab_size"),
-            max_position_embeddings=_as_int(raw, "max_position_embeddings"),
-            rope_theta=float(raw.get("rope_theta", 10000.0)),
-            rms_norm_eps=float(raw.get("rms_norm_eps", 1e-6)),
-            tie_word_embeddings=bool(raw.get("tie_word_embeddings", False)),
-            hidden_act=str(raw.get("hidden_act", "silu")),
-            attention_bias=bool(raw.get("attention_bias", True)),
-            use_sliding_window=bool(raw.get("use_sliding_window", False)),
-            sliding_window=int(raw["sliding_window"]) if raw.get("sliding_window") is not None else None,
-            max_window_layers=int(raw["max_window_layers"]) if raw.get("max_window_layers") is not None else None,
+    @classmethod
+    def shared_fields(cls, raw: Dict[str, Any]) -> Dict[str, Any]:
+        """The fields of this base class from the raw keys."""
+        return dict(
+            architecture=architecture_of(raw),
+            vocab_size=as_int(raw, "vocab_size"),
+            max_position_embeddings=as_int(raw, "max_position_embeddings"),
             torch_dtype=str(raw.get("torch_dtype", "bfloat16")),
             bos_token_id=int(raw["bos_token_id"]) if raw.get("bos_token_id") is not None else None,
-            eos_token_id=eos,
-            extra={k: v for k, v in raw.items() if k not in known},
+            eos_token_id=_token_ids(raw.get("eos_token_id")),
         )
+
+    SHARED_KEYS = ("architectures", "vocab_size", "max_position_embeddings", "torch_dtype", "bos_token_id", "eos_token_id")
+
+    @classmethod
+    def parse(cls, raw: Dict[str, Any]) -> "ModelConfig":
+        """This class's reading of the raw keys.  A subclass overrides it to fill its own fields."""
+        cfg = cls(**cls.shared_fields(raw), extra={k: v for k, v in raw.items() if k not in cls.SHARED_KEYS})
         cfg.validate()
         return cfg
 
     @staticmethod
+    def from_dict(raw: Dict[str, Any]) -> "ModelConfig":
+        """The configuration of `raw`, an instance of the class its architecture registered (this one if none)."""
+        from .registry import config_class_of                     # late: the registry imports this module
+        return config_class_of(architecture_of(raw)).parse(dict(raw))
+
+    @staticmethod
     def from_folder(folder: str) -> "ModelConfig":
+        """From `folder/config.json`, or from the path of a .json file."""
         path = folder if folder.endswith(".json") else os.path.join(folder, "config.json")
         try:
             with open(path) as f:
@@ -146,29 +108,14 @@ class ModelConfig:
         return ModelConfig.from_dict(raw)
 
     def validate(self) -> None:
-        """The reference's checks (src/loader.cpp:269-290; src/gguf_loader.cpp:285-300):
-        sizes positive, heads a multiple of kv heads, head_dim even, theta and eps finite
-        and positive."""
-        for name in ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
-                     "num_key_value_heads", "head_dim", "vocab_size", "max_position_embeddings"):
+        for name in ("vocab_size", "max_position_embeddings"):
             if getattr(self, name) <= 0:
-                raise ConfigError(f"{name} must be positive, got {getattr(self, name)}")
-        if self.num_attention_heads % self.num_key_value_heads != 0:
-            raise ConfigError(
-                f"num_attention_heads {self.num_attention_heads} is not a multiple of num_key_value_heads {self.num_key_value_heads}")
-        if self.head_dim % 2 != 0:
-            raise ConfigError(f"head_dim must be even for rotate-half RoPE, got {self.head_dim}")
-        if not math.isfinite(self.rope_theta) or self.rope_theta <= 0:
-            raise ConfigError(f"rope_theta must be finite and positive, got {self.rope_theta}")
-        if not math.isfinite(self.rms_norm_eps) or self.rms_norm_eps <= 0:
-            raise ConfigError(f"rms_norm_eps must be finite and positive, got {self.rms_norm_eps}")
-        if self.use_sliding_window and (self.sliding_window is None or self.sliding_window <= 0):
-            raise ConfigError("use_sliding_window is true but sliding_window is missing or not positive")
+                raise ConfigError(f"{name} must be positive, got {getattr(self, name)}")    # src/loader.cpp:269-273
 
     # ------------------------------------------------------------------ output
     def to_dict(self) -> Dict[str, Any]:
         """The config.json this configuration round-trips through."""
-        d = asdict(self)
+        d = {f.name: getattr(self, f.name) for f in dataclasses.fields(self)}
         extra = d.pop("extra")
         d["architectures"] = [d.pop("architecture")]
         if d["eos_token_id"] is not None:
@@ -177,6 +124,12 @@ class ModelConfig:
         d.update(extra)
         return d
 
+    def replace(self, **changes: Any) -> "ModelConfig":
+        """A copy with some config.json keys changed, read and checked again by the same class."""
+        d = self.to_dict()
+        d.update(changes)
+        return ModelConfig.from_dict(d)
+
     def save(self, folder: str) -> None:
         os.makedirs(folder, exist_ok=True)
         with open(os.path.join(folder, "config.json"), "w") as f:
@@ -184,8 +137,8 @@ class ModelConfig:
             f.write("\n")
 
 
-def _as_int(raw: Dict[str, Any], key: str) -> int:
-    v = raw[key]
-    if isinstance(v, bool) or not isinstance(v, (int, float)) or int(v) != v:
-        raise ConfigError(f"config key {key} must be an integer, got {v!r}")
-    return int(v)
+def architecture_of(raw: Dict[str, Any]) -> str:
+    archs = raw.get("architectures")
+    if not archs or not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
+        raise ConfigError("missing config key: architectures (a list whose first entry names the model class)")
+    return archs[0]

@@ -8,23 +8,38 @@ architecture or another part without touching this package's files.
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, Tuple, Type
+from typing import Callable, Dict, Optional, Tuple, Type
 
 from .model_config import ModelConfig, ConfigError
 from .specs import ModelSpec, PartSpec
 
 _ARCHITECTURES: Dict[str, Callable[[ModelConfig], ModelSpec]] = {}
+_CONFIG_CLASSES: Dict[str, Type[ModelConfig]] = {}
 _PARTS: Dict[Tuple[str, str], type] = {}
 
 PART_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
 
 
-def register_architecture(name: str):
-    """Decorator: `builder(config) -> ModelSpec` becomes the model for `architectures[0] == name`."""
+def register_architecture(name: str, config_class: Optional[Type[ModelConfig]] = None):
+    """Decorator: `builder(config) -> ModelSpec` becomes the model for `architectures[0] == name`.
+    `config_class`, a subclass of `ModelConfig` with the architecture's own typed keys and checks, reads that
+    architecture's config.json; without one the shared `ModelConfig` does, and the builder finds its keys in
+    `config.extra`."""
     def deco(builder):
         _ARCHITECTURES[name] = builder
+        if config_class is not None:
+            _CONFIG_CLASSES[name] = config_class
+        else:
+            _CONFIG_CLASSES.pop(name, None)
         return builder
     return deco
+
+
+def config_class_of(name: str) -> Type[ModelConfig]:
+    """The class that reads the config.json of architecture `name` (the shared one for a name nobody registered:
+    the unknown name is reported when a model is asked for)."""
+    _load_builtin()
+    return _CONFIG_CLASSES.get(name, ModelConfig)
 
 
 def known_architectures():

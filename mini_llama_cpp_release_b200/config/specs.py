@@ -28,20 +28,33 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (`block`) of a mixer and a feed-forward, each behind its
-    norm.  `name` is the prefix of the layer's tensors in the checkpoint."""
+    """One layer: `block`, a part of category "block" whose parameters hold its own children (part specifications,
+    as many and of whatever kinds that arrangement needs) and whatever else it takes.  `name` is the prefix of the
+    layer's tensors in the checkpoint."""
     name: str
-    block: str                      # kind of the arrangement, e.g. "prenorm"
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    names: Mapping[str, str] = field(default_factory=dict)   # role → the part's prefix below `name`
+    block: PartSpec
 
-    def block_spec(self) -> PartSpec:
-        return PartSpec("block", self.block, dict(mixer=self.mixer, feed_forward=self.feed_forward,
-                                                  mixer_norm=self.mixer_norm,
-                                                  feed_forward_norm=self.feed_forward_norm, names=dict(self.names)))
+    def child(self, role: str) -> Optional[PartSpec]:
+        """The block's child part of that role ("mixer", "feed_forward", ...), if it has one."""
+        v = self.block.params.get(role)
+        return v if isinstance(v, PartSpec) else None
+
+    @property
+    def mixer(self) -> Optional[PartSpec]:
+        return self.child("mixer")
+
+    @property
+    def feed_forward(self) -> Optional[PartSpec]:
+        return self.child("feed_forward")
+
+
+def prenorm_layer(name: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, feed_forward_norm: PartSpec,
+                  names: Optional[Mapping[str, str]] = None) -> LayerSpec:
+    """A layer in the pre-norm arrangement (src/forward.cpp:726-780): norm, mixer, residual; norm, feed-forward,
+    residual.  `names`: role → the part's prefix below `name` in the checkpoint."""
+    return LayerSpec(name, PartSpec("block", "prenorm", dict(
+        mixer=mixer, feed_forward=feed_forward, mixer_norm=mixer_norm, feed_forward_norm=feed_forward_norm,
+        names=dict(names or {}))))
 
 
 @dataclass(frozen=True)
@@ -68,6 +81,9 @@ class ModelSpec:
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
+        for i, layer in enumerate(self.layers):
+            if not isinstance(layer.block, PartSpec) or layer.block.category != "block":
+                raise ValueError(f"layer {i}: `block` must be a part specification of category \"block\"")
         if not self.schedule:
             raise ValueError("the schedule is empty")
         for i, e in enumerate(self.schedule):

@@ -17,8 +17,9 @@
 // What it costs and where its limit is.  The array is
 // MLC_NOALLOC_SCRATCH_FLOATS floats (4 MiB) and is part of the loaded library image: every
 // GPU on which a process loads this library holds those 4 MiB until the process exits.  A
-// call needs n_tokens * q_heads * n_splits * (head_dim + 2) floats of it; a call that needs
-// more is refused with MLC_ERR_BAD_SIZE (-2) and launches nothing.
+// call with n_splits > 1 needs n_tokens * q_heads * n_splits * (head_dim + 2) floats of it; a
+// call that needs more is refused with MLC_ERR_BAD_SIZE (-2) and launches nothing.  A call
+// with n_splits == 1 leaves no partial results, uses none of the array and has no such limit.
 //
 // What the caller must know.
 //   * The first call on each device looks the array's device address up (the name of the

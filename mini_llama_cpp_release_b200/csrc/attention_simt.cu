@@ -225,21 +225,20 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_ml, cons
 
 }  // namespace mlc
 
-#ifndef MLC_KERNELS_ONLY   // a file that includes this one for its kernels defines its own entry points
-using namespace mlc;
-
-// q, out: [n_tokens][q_heads][hd] of `dtype`; the cache pools hold the same type.
-// max_q_len: the longest sequence of this step (sizes the grid).  n_splits > 1 needs
-// part_ml (n_tokens*q_heads*n_splits*2 floats) and part_o (n_tokens*q_heads*n_splits*hd).
-extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int* cu_seqlens,
-                                  const int* start_pos, int n_seqs, int n_tokens, int max_q_len, int q_heads,
-                                  int kv_heads, int hd, float scale, int window, int n_splits, float* part_ml,
-                                  float* part_o, void* k_pool, void* v_pool, const int* page_table,
-                                  long long entry_offset, int pages_per_seq, int page_size, void* stream) {
+// The launch shared by every entry point of the split-key attention (the ordinary one below and the one that keeps
+// its scratch inside the library): checks, the plan of heads and tokens per block, the two kernels.
+// n_splits > 1 needs part_ml (n_tokens*q_heads*n_splits*2 floats) and part_o (n_tokens*q_heads*n_splits*hd).
+namespace mlc {
+static int launch_attention_simt(const void* q, void* out, int dtype, const int* cu_seqlens, const int* start_pos,
+                                 int n_seqs, int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
+                                 int window, int n_splits, float* part_ml, float* part_o, void* k_pool, void* v_pool,
+                                 const int* page_table, long long entry_offset, int pages_per_seq, int page_size,
+                                 cudaStream_t s) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd <= 0 || hd > ATT_MAX_HD || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return MLC_ERR_BAD_SIZE;
     if (n_splits < 1 || (n_splits > 1 && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
     if (n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    if (dtype != MLC_DTYPE_F32 && dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
     AttnArgs a;
     a.q = q;
     a.out = out;
@@ -260,7 +259,6 @@ extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int
     PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, kv_heads, hd};
     dim3 grid((max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, (unsigned)gy, n_seqs);
     const size_t smem = (size_t)(ATT_ROWS * hd + ATT_TILE * (hd + 1) + ATT_TILE * hd) * sizeof(float);
-    cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (dtype == MLC_DTYPE_F32) {
         static size_t allowed_f32 = 48 * 1024;
@@ -270,7 +268,7 @@ extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int
             allowed_f32 = smem;
         }
         attention_simt_kernel<float><<<grid, ATT_WARPS * 32, smem, s>>>(a, c);
-    } else if (dtype == MLC_DTYPE_BF16) {
+    } else {
         static size_t allowed_bf16 = 48 * 1024;
         if (smem > allowed_bf16) {
             e = cudaFuncSetAttribute(attention_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -278,10 +276,10 @@ extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int
             allowed_bf16 = smem;
         }
         attention_simt_kernel<bf16><<<grid, ATT_WARPS * 32, smem, s>>>(a, c);
-    } else {
-        return MLC_ERR_BAD_DTYPE;
     }
     MLC_LAUNCH_CHECK();
+    // With one split the first kernel has written `out` itself and no scratch was touched; with more, every
+    // (row, split) pair of the scratch was written above before the merge reads it.
     if (n_splits > 1) {
         const long long n_rows = (long long)n_tokens * q_heads;
         const unsigned blocks = (unsigned)((n_rows + 3) / 4);
@@ -292,6 +290,23 @@ extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int
         MLC_LAUNCH_CHECK();
     }
     return 0;
+}
+}  // namespace mlc
+
+#ifndef MLC_KERNELS_ONLY   // a file that includes this one for its kernels defines its own entry points
+using namespace mlc;
+
+// q, out: [n_tokens][q_heads][hd] of `dtype`; the cache pools hold the same type.
+// max_q_len: the longest sequence of this step (sizes the grid).  n_splits > 1 needs
+// part_ml (n_tokens*q_heads*n_splits*2 floats) and part_o (n_tokens*q_heads*n_splits*hd).
+extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int* cu_seqlens,
+                                  const int* start_pos, int n_seqs, int n_tokens, int max_q_len, int q_heads,
+                                  int kv_heads, int hd, float scale, int window, int n_splits, float* part_ml,
+                                  float* part_o, void* k_pool, void* v_pool, const int* page_table,
+                                  long long entry_offset, int pages_per_seq, int page_size, void* stream) {
+    return launch_attention_simt(q, out, dtype, cu_seqlens, start_pos, n_seqs, n_tokens, max_q_len, q_heads, kv_heads, hd,
+                                 scale, window, n_splits, part_ml, part_o, k_pool, v_pool, page_table, entry_offset,
+                                 pages_per_seq, page_size, (cudaStream_t)stream);
 }
 
 // Merge partial results that another attention kernel left in part_ml / part_o

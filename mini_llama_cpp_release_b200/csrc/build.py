@@ -135,6 +135,14 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
         if p.returncode != 0:
             raise BuildError(f"linking {name} failed:\n{p.stdout}")
         os.replace(tmp_out, out)
+        # binaries of earlier versions of these sources are never loaded again: drop them
+        prefix = f"lib{name}_"
+        for f in os.listdir(build_dir()):
+            if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out):
+                try:
+                    os.remove(os.path.join(build_dir(), f))
+                except OSError:
+                    pass
     finally:
         shutil.rmtree(work, ignore_errors=True)
     _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")

@@ -157,7 +157,7 @@ class Context:
             n_tokens=n_tokens, n_seqs=B, max_q_len=layout["max_q"], max_kv_len=layout["max_kv"],
             tokens=seg(0, n_tokens), positions=seg(1, n_tokens), tok_seq=seg(2, n_tokens),
             cu_seqlens=seg(3, B + 1), start_pos=seg(4, B), slots=slots_dev, want_rows=seg(6, layout["n_want"]),
-            page_tables=page_tables, slots_long=slots_dev.long(),
+            page_tables=page_tables, slots_long=slots_dev.long() if self.cache.has_state else None,
         )
 
     # A step of many tokens is some two hundred launches issued from Python; when its kernels are fast the host
@@ -209,7 +209,10 @@ class Context:
         stream = torch.cuda.Stream(device=dev)
         stream.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(stream):
-            self.model.forward(self._step_over(own, layout), self.cache)
+            warm = self._step_over(own, layout)
+            saved = self.cache.snapshot_state(warm.slots_long)      # the warm-up run must not count as a step
+            self.model.forward(warm, self.cache)
+            self.cache.restore_state(saved, warm.slots_long)
         torch.cuda.current_stream(dev).wait_stream(stream)
         torch.cuda.synchronize(dev)
         graph = torch.cuda.CUDAGraph()

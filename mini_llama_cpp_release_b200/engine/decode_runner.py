@@ -77,7 +77,7 @@ class DecodeRunner:
         self.launches_per_step = 0
         self.loaded_slots: Optional[List[int]] = None
         self.loaded_ids: Optional[List[int]] = None
-        self.page_counts: Optional[List[List[int]]] = None
+        self.page_versions: Optional[List[int]] = None            # `SlotBook.page_version` of each slot when its pages were copied
 
     # ------------------------------------------------------------------ buffers
     def view(self, name: str) -> torch.Tensor:
@@ -107,12 +107,15 @@ class DecodeRunner:
     def capture(self) -> None:
         """Run the step once eagerly (libraries initialise, tables are built), then capture it.
         Both runs happen on the buffers' current contents, which must describe valid sequences;
-        the caller reloads the buffers afterwards."""
+        the caller reloads the buffers afterwards.  The eager run writes the step's keys and values (the
+        replay writes the same ones again) and leaves the sequences' fixed-size state as it found it."""
         dev = self.model.runtime.device
         stream = torch.cuda.Stream(device=dev)
         stream.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(stream):
+            saved = self.cache.snapshot_state(self.slots_long)      # the warm-up run must not count as a step
             self._body()
+            self.cache.restore_state(saved, self.slots_long)
         torch.cuda.current_stream(dev).wait_stream(stream)
         torch.cuda.synchronize(dev)
         before, lib_before = kernels.launch_count(), kernels.library_launch_count()
@@ -139,38 +142,27 @@ class DecodeRunner:
         h("counter")[:] = 0
         self._fill_pages(slots)
         self.dev_buf.copy_(self.host_buf, non_blocking=True)
-        self.slots_long.copy_(h("slots").long(), non_blocking=True)
+        if self.cache.has_state:
+            self.slots_long.copy_(h("slots").long(), non_blocking=True)
         self.loaded_slots = list(slots)
 
     def _fill_pages(self, slots: Sequence[int]) -> None:
         P = self.pages_per_seq
-        self.page_counts = []
         for g in range(len(self.cache.groups)):
             t = self.host_view(f"pages{g}").view(self.B, P)
-            counts = []
             for b, s in enumerate(slots):
                 pl = self.cache.page_lists[s][g]
                 if len(pl) > P:
                     raise RuntimeError("decode runner: a sequence outgrew the runner's page table")
                 t[b, :len(pl)] = torch.tensor(pl, dtype=torch.int32)
                 t[b, len(pl):] = -1
-                counts.append(len(pl))
-            self.page_counts.append(counts)
+        self.page_versions = [self.cache.page_version[s] for s in slots]
 
     def refresh_pages(self, slots: Sequence[int]) -> int:
-        """Copy the page tables again if any sequence got or lost a page; returns bytes copied."""
-        changed = False
-        page_lists = self.cache.page_lists
-        for g, group in enumerate(self.cache.groups):
-            counts = self.page_counts[g]
-            if group.need.kind == "window":
-                changed = True
-                break
-            for b, s in enumerate(slots):
-                if len(page_lists[s][g]) != counts[b]:
-                    changed = True
-                    break
-        if not changed:
+        """Copy the page tables again if any sequence's pages are not the ones copied last (it got or lost a page, or
+        its slot was given back and taken again by another sequence); returns bytes copied."""
+        version = self.cache.page_version
+        if self.page_versions == [version[s] for s in slots]:
             return 0
         self._fill_pages(slots)
         n = 0

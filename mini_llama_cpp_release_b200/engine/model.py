@@ -8,6 +8,7 @@ cache entry; the final norm and the head run only on the rows whose logits were 
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -37,7 +38,7 @@ def build_parts(spec: ModelSpec) -> ModelParts:
     names = spec.names
     return ModelParts(
         embedding=build_part(spec.embedding, names["embedding"]),
-        blocks=[build_part(layer.block_spec(), layer.name) for layer in spec.layers],
+        blocks=[build_part(layer.block, layer.name) for layer in spec.layers],
         final_norm=build_part(spec.final_norm, names["final_norm"]),
         head=build_part(spec.head, names["head"]),
     )
@@ -54,23 +55,30 @@ class Model:
 
     # ------------------------------------------------------------------ construction
     @staticmethod
-    def from_folder(folder: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0") -> "Model":
-        config = ModelConfig.from_folder(folder)
+    def from_folder(folder: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
+                    config_path: Optional[str] = None) -> "Model":
+        """`folder`: a model folder, or the path of one .safetensors file, whose config.json then lies beside it
+        unless `config_path` says where (the reference's `--model <path|dir>` and `--config`,
+        src/main.cpp:280-281, 452-461)."""
+        if config_path is None:
+            config_path = folder if os.path.isdir(folder) else os.path.join(os.path.dirname(folder) or ".", "config.json")
+        config = ModelConfig.from_folder(config_path)
         spec = build_model_spec(config)
         device = torch.device(device)
         if device.type != "cuda":
             raise RuntimeError("this engine runs on a CUDA device only; there is no CPU path")
         kernels.core()                      # fail now, loudly, if the kernels cannot be built or loaded
         model = Model(spec, Runtime(device, dtype))
-        ignore = ["lm_head.weight"] if config.tie_word_embeddings else []
         with torch.cuda.device(device):
-            model.load_summary = load_weights(model.parts.all_parts(), folder, model.runtime, ignore_extra=ignore)
+            model.load_summary = load_weights(model.parts.all_parts(), folder, model.runtime)
         model.loaded = True
         return model
 
     # ------------------------------------------------------------------ what the cache must provide
-    def schedule_mixers(self) -> List[Part]:
-        return [self.parts.blocks[e.layer].mixer for e in self.spec.schedule]
+    def schedule_mixers(self) -> List[Optional[Part]]:
+        """For every run of the schedule, the part of its block that keeps something per sequence (None: a block
+        without one)."""
+        return [getattr(self.parts.blocks[e.layer], "mixer", None) for e in self.spec.schedule]
 
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         return [m.cache_need() if hasattr(m, "cache_need") else None for m in self.schedule_mixers()]

@@ -28,7 +28,7 @@ class StepInfo:
     slots: torch.Tensor           # [n_seqs] cache slot of each sequence
     want_rows: torch.Tensor       # [n_want] packed token rows whose logits are asked for
     page_tables: List[torch.Tensor]   # per cache group: [n_seqs, pages] page of each page index, -1: none
-    slots_long: Optional[torch.Tensor] = None   # [n_seqs] int64 copy of `slots`, for indexing state tensors
+    slots_long: Optional[torch.Tensor] = None   # [n_seqs] int64 copy of `slots`, for indexing state tensors; None when no mixer of the model declared state
 
     @property
     def is_decode(self) -> bool:

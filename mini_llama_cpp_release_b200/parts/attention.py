@@ -109,8 +109,9 @@ class GQAttention(Part):
     def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
         rt = self.runtime
         n = h.shape[0]
-        self.position.prepare(step.max_kv_len)
-        table = self.position.table
+        if hasattr(self.position, "prepare"):
+            self.position.prepare(step.max_kv_len)
+        table = getattr(self.position, "table", None)
         q = rt.empty(n, self.H * self.hd)
         kv_heads = self.KV if memory.writes_cache else 0
         if memory.writes_cache:
@@ -130,9 +131,23 @@ class GQAttention(Part):
                                  tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
                                  kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms,
                                  block_tokens=16 if n <= 64 else None)     # short epilogues in more blocks beat one long one
-        else:
+        elif getattr(self.position, "fusable", False):
             kernels.qkv_post(proj(h, torch.float32), bias, step.positions, step.tok_seq, table, self.H, kv_heads,
                              self.hd, q, memory.kv if memory.writes_cache else None)
+        else:
+            # an encoding that is not a table of rotate-half angles: the part rotates the float32 queries and keys
+            # itself, after the bias and before the cache write, as the fused forms do
+            qkv = proj(h, torch.float32)
+            if bias is not None:
+                qkv += bias
+            nq, nk = self.H * self.hd, kv_heads * self.hd
+            qkv[:, :nq] = self.position.rotate(qkv[:, :nq].reshape(n, self.H, self.hd), step.positions,
+                                               out_dtype=torch.float32).reshape(n, nq)
+            if nk:
+                qkv[:, nq:nq + nk] = self.position.rotate(qkv[:, nq:nq + nk].reshape(n, kv_heads, self.hd), step.positions,
+                                                          out_dtype=torch.float32).reshape(n, nk)
+            kernels.qkv_post(qkv, None, step.positions, step.tok_seq, None, self.H, kv_heads, self.hd, q,
+                             memory.kv if memory.writes_cache else None)
         o = rt.empty(n, self.H * self.hd)
         self.attend(q, o, step, memory.kv)
         if residual is not None and self.o.can_add_into_stream(n):

@@ -116,6 +116,15 @@ class Part:
             out.extend(c.all_tensors())
         return out
 
+    def ignorable_tensors(self) -> List[str]:
+        """Names a checkpoint may hold although this part (children included) does not read them: the loader passes
+        over them instead of reporting them as unexpected.  A head tied to the embedding names its own untied
+        tensor here, which some exporters write all the same."""
+        out: List[str] = []
+        for c in self.children():
+            out.extend(c.ignorable_tensors())
+        return out
+
     def bind(self, get: Callable[[str], Optional[torch.Tensor]], runtime: Runtime) -> None:
         """Take the tensors (`get(name)` returns the device tensor, or None for an optional
         one that the file does not have) and prepare whatever forward needs."""

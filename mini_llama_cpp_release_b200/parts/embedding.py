@@ -50,6 +50,9 @@ class LinearHead(Part):
             return [TensorSpec(self.tied_to, (self.vocab, self.hidden), role="table", stored=False)]
         return [TensorSpec(self.name + "weight", (self.vocab, self.hidden))]
 
+    def ignorable_tensors(self):
+        return [self.name + "weight"] if self.tied_to else []
+
     def bind(self, get, runtime):
         super().bind(get, runtime)
         self.proj = Linear(get(self.tied_to or (self.name + "weight")), runtime)

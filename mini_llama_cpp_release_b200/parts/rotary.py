@@ -9,7 +9,7 @@ and every kernel reads the table.
 from __future__ import annotations
 
 import math
-from typing import Optional
+from typing import Dict, Optional, Tuple
 
 import numpy as np
 import torch
@@ -28,11 +28,29 @@ def neox_inv_freq(head_dim: int, theta: float) -> torch.Tensor:
     return torch.from_numpy((np.float32(1.0) / power).astype(np.float32))
 
 
+# One table per (head size, theta, positions, device), shared by every layer and every model that asks for it: the
+# attention layers of a model all rotate alike, and a decode step that pulled a private copy per layer through the
+# cache hierarchy would read the same numbers two dozen times.
+_TABLES: Dict[Tuple[int, float, int, str], torch.Tensor] = {}
+
+
+def shared_table(inv_freq: torch.Tensor, head_dim: int, theta: float, max_positions: int) -> torch.Tensor:
+    key = (head_dim, float(theta), max_positions, str(inv_freq.device))
+    table = _TABLES.get(key)
+    if table is None:
+        table = _TABLES[key] = kernels.rope_table(inv_freq, max_positions)
+    return table
+
+
 @register_part("position", "rope_neox")
 class RopeNeox(Part):
     graph_safe = True
 
-    fusable = True        # the attention part applies it inside its Q/K/V epilogue
+    # How the attention part applies a position encoding.  `fusable = True`: the encoding is a rotation of the pairs
+    # (i, i + head_dim/2) by angles that depend on the position alone; it offers `table`, [positions][head_dim/2][2]
+    # float32 cos and sin (or None for "no rotation"), and the Q/K/V kernel's epilogue applies it.  `fusable = False`:
+    # anything else; the attention part then calls `rotate(x, positions)` on the float32 queries and keys itself.
+    fusable = True
 
     def __init__(self, name: str, head_dim: int, theta: float, max_positions: int):
         super().__init__(name, head_dim=head_dim, theta=theta, max_positions=max_positions)
@@ -51,7 +69,7 @@ class RopeNeox(Part):
         """Make sure the table exists.  It is built once, for every position the model allows,
         and never replaced: captured graphs keep reading the same memory."""
         if self.table is None:
-            self.table = kernels.rope_table(self.inv_freq, self.max_positions)
+            self.table = shared_table(self.inv_freq, self.head_dim, self.theta, self.max_positions)
 
     def rotate(self, x: torch.Tensor, positions: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """Rotate float32 x [n, heads, head_dim] by int32 positions [n]; on its own, outside attention."""

@@ -83,10 +83,16 @@ def device_dtype(stored: str, role: str, engine_dtype: torch.dtype) -> torch.dty
     return torch.float32 if stored in ("F32", "F64") else torch.bfloat16
 
 
+def ignorable_tensors(parts: Sequence[Part]) -> List[str]:
+    """Names the parts allow a checkpoint to hold unread (`Part.ignorable_tensors`)."""
+    return [n for part in parts for n in part.ignorable_tensors()]
+
+
 def load_weights(parts: Sequence[Part], folder: str, runtime: Runtime, ignore_extra: Sequence[str] = ()) -> Dict[str, int]:
-    """Check the checkpoint in `folder` against the parts, then bind.  Returns a summary
-    {"tensors", "bytes"} of what was put on the device."""
+    """Check the checkpoint in `folder` (or the .safetensors file of that path) against the parts, then bind.
+    Returns a summary {"tensors", "bytes"} of what was put on the device."""
     specs = expected_tensors(parts)
+    ignore_extra = list(ignore_extra) + ignorable_tensors(parts)
     try:
         ckpt = Checkpoint(folder)
     except SafetensorsError as e:

@@ -146,14 +146,16 @@ class SafetensorsFile:
 
 class Checkpoint:
     """The weights of a model folder: `model.safetensors`, or the shards that
-    `model.safetensors.index.json` lists.  A name stored twice is an error
-    (src/loader.cpp:529-532)."""
+    `model.safetensors.index.json` lists; or one .safetensors file given by its own path.
+    A name stored twice is an error (src/loader.cpp:529-532)."""
 
     def __init__(self, folder: str):
         self.folder = folder
         index = os.path.join(folder, "model.safetensors.index.json")
         single = os.path.join(folder, "model.safetensors")
-        if os.path.exists(single):
+        if os.path.isfile(folder):
+            paths = [folder]
+        elif os.path.exists(single):
             paths = [single]
         elif os.path.exists(index):
             with open(index) as f:

@@ -31,7 +31,12 @@ TINY_W = dict(architectures=["Qwen2ForCausalLM"], hidden_size=72, intermediate_s
               max_position_embeddings=512, rope_theta=50000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
               use_sliding_window=True, sliding_window=24, max_window_layers=1)
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "W": TINY_W}
+# head size 128 (the geometry of the 1.5B and 7B models: two teams in the tcgen05 attention, other epilogue tiles)
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], hidden_size=256, intermediate_size=344, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=128, vocab_size=1000,
+              max_position_embeddings=1024, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "W": TINY_W, "D": TINY_D}
 
 _tmp_root = None
 

@@ -115,3 +115,50 @@ def test_random_traffic_keeps_the_invariants():
         b.release(s)
     b.check()
     assert b.slots.n_free == 9 and all(p.n_free == 40 for p in b.pages)
+
+
+def test_a_reader_must_not_look_further_back_than_the_owner_keeps():
+    """A run of the schedule that reads another run's cache finds only what the owner keeps: a window group gives
+    pages back as positions leave its window."""
+    narrow = CacheNeed("window", 2, 16, window=50)
+    plan_groups([WIN, narrow], [None, 0])                        # a narrower window inside the owner's: fine
+    plan_groups([ALL, WIN], [None, 0])                           # the owner keeps everything: fine
+    with pytest.raises(ValueError, match="all keys"):
+        plan_groups([WIN, ALL], [None, 0])
+    with pytest.raises(ValueError, match="window of 100"):
+        plan_groups([narrow, WIN], [None, 0])
+
+
+def test_page_version_changes_with_every_change_of_a_slots_pages_and_is_never_used_twice():
+    b = book(groups=[GroupLayout(ALL, [0]), GroupLayout(CacheNeed("window", 2, 16, window=70), [1])])
+    s = b.acquire()
+    seen = {b.page_version[s]}
+
+    def changed():
+        v = b.page_version[s]
+        fresh = v not in seen
+        seen.add(v)
+        return fresh
+    b.reserve(s, 60)
+    assert changed()
+    b.commit(s, 60)
+    assert not changed()
+    b.reserve(s, 1)
+    b.commit(s, 1)
+    assert not changed()                                         # 61 tokens: the same page
+    b.reserve(s, 10)
+    assert changed()                                             # a second page
+    b.commit(s, 10)
+    b.reserve(s, 70)
+    b.commit(s, 70)
+    assert changed()                                             # a third page came and the window let the first go
+    # given back and taken again by another sequence of the same length: the same slot, the same number of pages,
+    # another version
+    other = b.acquire()
+    b.reserve(other, 141)
+    b.release(s)
+    again = b.acquire()
+    assert again == s
+    b.reserve(again, 141)
+    assert changed()
+    b.check()

@@ -24,13 +24,15 @@ def confident_greedy(pm, prompt, n, margin=1e-3):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_greedy_generation_matches_plain(name, dtype):
     folder = model_folder(name, std=0.1)                # larger weights: logits of order one, not dominated by one id
     pm = plain_model(folder)
     llm = helpers.engine(folder, dtype)
     vocab = llm.config.vocab_size
     prompts = [random_tokens(n, vocab, 40 + n) for n in ([7, 1, 13] if name == "A" else [1, 5, 31, 64])]
+    if name == "D":
+        prompts.append(random_tokens(150, vocab, 7))      # long enough for the tcgen05 attention at head size 128
     out = llm.generate(prompts, n_predict=12, stop_token_ids=[])
     for p, got in zip(prompts, out):
         want, sure = confident_greedy(pm, p, 12, margin=1e-4 if dtype == "float32" else 2e-2)
@@ -124,9 +126,12 @@ def test_sampled_generation_does_not_depend_on_the_batch():
     llm = helpers.engine(folder, "float32")
     prompts = [random_tokens(n, 1000, 80 + n) for n in (1, 5, 31, 64)]
     together = llm.generate(prompts, n_predict=16, temperature=0.8, seed=1234, stop_token_ids=[])
-    again = llm.generate(prompts, n_predict=16, temperature=0.8, seed=1234, stop_token_ids=[])
+    # a sequence's id is its index in the call, so the same request draws the same numbers however the call is cut
+    # into batches; the 32-bit products give a row the same sum in any batch, so the ids are equal, not just close
+    alone = llm.generate(prompts, n_predict=16, temperature=0.8, seed=1234, stop_token_ids=[], max_batch=1)
+    in_pairs = llm.generate(prompts, n_predict=16, temperature=0.8, seed=1234, stop_token_ids=[], max_batch=2)
     other = llm.generate(prompts, n_predict=16, temperature=0.8, seed=99, stop_token_ids=[])
-    assert together == again and together != other
+    assert together == alone and together == in_pairs and together != other
     assert len({t for seq in together for t in seq}) > 20          # it samples, it does not repeat one id
     topk = llm.generate(prompts, n_predict=8, temperature=1.5, top_k=3, seed=5, stop_token_ids=[])
     assert all(len(s) == 8 for s in topk)
@@ -139,3 +144,131 @@ def test_requests_that_do_not_fit_are_refused_before_anything_runs():
     with pytest.raises(IndexError, match="vocabulary"):
         llm.generate([[1, 600]], n_predict=2)
     assert llm.context.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_every_step_of_a_long_generation_against_plain(name, dtype):
+    """`LLM.generate` decodes through `DecodeRunner` (engine/decode_runner.py), not through `forward_batch`: its own
+    step description, its own page table of a fixed width, a captured graph per (batch size, length bucket).  Here
+    every step's logits, over 300 tokens, are compared with the plain implementation run on the engine's own ids.
+    Guards: `refresh_pages` (the 60-token prompt gains a page at 64, 128, ... in the middle of a run of replays: with
+    a stale table the new keys land on page -1's place and the logits are wrong from position 64 on); the bucket
+    switch in `Context._runner` (the 200-token prompt passes 256 and 512: a new runner with a wider table, loaded
+    from the cache's books); the reload when the batch shrinks (the requests ask for 90, 300 and 210 tokens, `load`
+    with other slots into a runner of another size)."""
+    folder = model_folder(name, std=0.1)
+    pm = plain_model(folder)
+    llm = helpers.engine(folder, dtype)
+    vocab = llm.config.vocab_size
+    prompts = [random_tokens(n, vocab, 500 + n) for n in (60, 1, 200)]
+    N = 300
+    counts = [90, N, 210]
+    run = lambda n, **kw: llm.generate(prompts, n_predict=n, temperature=1.0, seed=77, stop_token_ids=[], **kw)
+    seen, used = [], set()
+    ctx, make_runner = llm.context, llm.context._runner
+
+    def spy(n_seqs, need_len, sampler):
+        runner = make_runner(n_seqs, need_len, sampler)
+        used.add((runner.B, runner.max_len))
+        return runner
+    ctx._runner = spy
+    try:
+        out = run(counts, on_step=lambda live, chosen, logits: seen.append((list(live), logits.float().cpu().clone())))
+    finally:
+        del ctx._runner
+    assert [len(o) for o in out] == counts                          # the batch shrank twice, at different steps
+    assert len({b for b, _ in used}) == 3 and len({m for _, m in used}) >= 2, used    # three batch sizes, two buckets
+    if dtype == "float32":
+        assert out == [f[:n] for f, n in zip(run(N), counts)]        # in 32-bit the others are unchanged, bit for bit, by who left
+    refs = [pm.logits(p + o) for p, o in zip(prompts, out)]
+    worst, where = 0.0, None
+    for step, (live, logits) in enumerate(seen):
+        for row, i in enumerate(live):
+            e = rel_err(logits[row], refs[i][len(prompts[i]) - 1 + step])
+            if e > worst:
+                worst, where = e, (step, i)
+    assert worst <= TOL[dtype], (worst, where)
+    llm.context.cache.check()
+    assert llm.context.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_without_the_host_gives_the_ids_of_generate_and_of_plain(dtype):
+    """`Context.decode_on_device` replays the captured step back to back; `decode_advance_kernel` (csrc/sampling.cu)
+    makes each step's chosen ids the next step's tokens and moves positions, starts and sampling positions on by one.
+    Were any of the four not advanced, the second step would already rewrite the first step's key or read one key
+    too few, and the ids would leave those of `generate` within a few steps.  200 steps cross three page edges."""
+    folder = model_folder("C", std=0.1)
+    pm = plain_model(folder)
+    llm = helpers.engine(folder, dtype)
+    ctx = llm.context
+    prompts = [random_tokens(n, 777, 900 + n) for n in (50, 3, 120)]
+    N = 200
+    by_generate = llm.generate(prompts, n_predict=N, stop_token_ids=[])
+    from mini_llama_cpp_release_b200.sampling import DeviceSampler, SamplingParams
+    sampler = DeviceSampler(SamplingParams(), llm.model.runtime.device)
+    slots = [ctx.acquire() for _ in prompts]
+    logits = ctx.forward_batch(MiniBatch.prefill(slots, prompts))
+    first = logits.argmax(dim=1).tolist()
+    history = ctx.decode_on_device(slots, first, sampler, [0, 1, 2], N - 1).cpu().tolist()
+    for s in slots:
+        ctx.release(s)
+    on_device = [[first[i]] + [row[i] for row in history] for i in range(3)]
+    margin = 1e-4 if dtype == "float32" else 2e-2
+    for i, p in enumerate(prompts):
+        want, sure = confident_greedy(pm, p, N, margin)
+        n_sure = sure.index(False) if False in sure else N
+        assert on_device[i][:n_sure] == want[:n_sure], i
+        assert by_generate[i][:n_sure] == want[:n_sure], i
+        if dtype == "float32":
+            assert on_device[i] == by_generate[i]                   # the 32-bit path has no atomics: bit for bit
+            assert n_sure > 20
+    ctx.cache.check()
+    assert ctx.cache.slots.n_held == 0
+
+
+def test_a_slot_taken_again_by_another_sequence_gets_its_own_pages():
+    """Two calls on one `LLM`: the second call's sequences get the first call's slots, the same batch size and length
+    bucket (so the same captured runner), and page lists of the same lengths but other pages.  The runner must copy
+    the page table again (`SlotBook.page_version`); comparing page counts alone would leave sequence 0 reading and
+    writing through the other call's pages."""
+    folder = model_folder("A", std=0.1)
+    import mini_llama_cpp_release_b200 as ml
+    llm = ml.load(folder, dtype="float32", max_tokens=1024)
+    a = [random_tokens(60, 512, 1), random_tokens(60, 512, 2)]
+    b = [random_tokens(100, 512, 3), random_tokens(100, 512, 4)]
+    llm.generate(a, n_predict=8, stop_token_ids=[])                  # grows past 64: pages [[0, 2], [1, 3]]
+    got = llm.generate(b, n_predict=8, stop_token_ids=[])            # starts with pages [[0, 1], [2, 3]]
+    fresh = ml.load(folder, dtype="float32", max_tokens=1024).generate(b, n_predict=8, stop_token_ids=[])
+    assert got == fresh
+    pm = plain_model(folder)
+    assert got == [pm.greedy(p, 8) for p in b]
+
+
+def test_sampled_ids_are_the_plain_samplers_on_the_plain_logits():
+    """Tiny B's stated workload: prompts of 1, 5, 31 and 64 tokens, 16 steps at temperature 0.8 with a fixed seed.
+    Every chosen id is compared with the plain sampler (the reference's walk, src/sampler.cpp:38-77) fed with the
+    plain implementation's logits and the same uniform number; a draw within rounding of the boundary between two
+    neighbouring candidates may fall either side."""
+    import plain_impl
+    from mini_llama_cpp_release_b200.sampling.rng import uniform_of
+    folder = model_folder("B", std=0.1)
+    pm = plain_model(folder)
+    llm = helpers.engine(folder, "float32")
+    prompts = [random_tokens(n, 1000, 80 + n) for n in (1, 5, 31, 64)]
+    seed, T = 4321, 0.8
+    out = llm.generate(prompts, n_predict=16, temperature=T, seed=seed, stop_token_ids=[])
+    near = 0
+    for i, (p, o) in enumerate(zip(prompts, out)):
+        ref = pm.logits(p + o)
+        for k, tok in enumerate(o):
+            row = ref[len(p) - 1 + k]
+            r = uniform_of(seed, i, len(p) + k)
+            want = plain_impl.sample(row, T, 0, r)
+            if tok != want:
+                cum = torch.cumsum(torch.exp((row.double() - row.double().max()) / T), 0)
+                cum = cum / cum[-1]
+                assert abs(tok - want) == 1 and abs(float(cum[min(tok, want)]) - r) < 2e-5, (i, k, tok, want)
+                near += 1
+    assert near <= 2

@@ -161,3 +161,18 @@ def test_batch_validation():
         MiniBatch.from_tokens(0, [1, 2], want=[2]).validate(10)
     with pytest.raises(ValueError, match="no tokens"):
         MiniBatch.from_tokens(0, [], want=[]).validate(10)
+
+
+def test_n_predict_per_request_ends_each_sequence_at_its_own_count():
+    ctx = FakeContext()
+    prompts = [[1, 2, 3], [5], [8, 8], [7]]
+    seen = []
+    out = generate(ctx, greedy(), prompts, n_predict=[2, 6, 0, 4], max_batch=3,
+                   on_step=lambda live, chosen, logits: seen.append(list(live)))
+    assert [r.tokens for r in out] == [expected(p, n) for p, n in zip(prompts, [2, 6, 0, 4])]
+    # the third request asks for nothing: no slot, no row in the prompt step; the observer hears the requests' indices in
+    # the call, also in the second batch
+    assert ctx.steps[0] == ("prefill", [0, 1]) and seen[0] == [0, 1] and seen[2] == [1] and seen[-1] == [3]
+    assert ctx.cache.slots.n_free == 4
+    with pytest.raises(ValueError, match="3 entries for 4 requests"):
+        generate(ctx, greedy(), prompts, n_predict=[1, 2, 3])

@@ -17,7 +17,8 @@ from mini_llama_cpp_release_b200.engine.replay import Replayer
 
 pytestmark = pytest.mark.gpu
 
-REQUESTS = {"A": [7, 1, 13, 40, 100], "B": [1, 5, 31, 64, 130], "C": [3, 65, 129, 200], "W": [2, 23, 24, 25, 90, 150]}
+REQUESTS = {"A": [7, 1, 13, 40, 100], "B": [1, 5, 31, 64, 130], "C": [3, 65, 129, 200], "W": [2, 23, 24, 25, 90, 150],
+            "D": [4, 66, 131, 260]}
 
 
 def requests_of(name):
@@ -45,7 +46,7 @@ def check(got, want, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "W", "D"])
 def test_each_request_alone_and_whole(name, dtype, tmp_path):
     folder = model_folder(name)
     pm = plain_model(folder)
@@ -58,7 +59,7 @@ def test_each_request_alone_and_whole(name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "W", "D"])
 def test_last_32_tokens_one_by_one(name, dtype, tmp_path):
     folder = model_folder(name)
     pm = plain_model(folder)
@@ -104,7 +105,7 @@ def batched_records(reqs, groups, prompt_frac=0.5):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "W", "D"])
 def test_batches_of_unequal_lengths_one_after_another(name, dtype, tmp_path):
     folder = model_folder(name)
     pm = plain_model(folder)

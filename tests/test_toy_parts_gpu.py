@@ -13,7 +13,7 @@ import torch
 import helpers
 import plain_impl
 import mini_llama_cpp_release_b200 as ml
-from mini_llama_cpp_release_b200.config import LayerSpec, ModelConfig, ModelSpec, PartSpec, sequential_schedule
+from mini_llama_cpp_release_b200.config import ModelConfig, ModelSpec, PartSpec, prenorm_layer, sequential_schedule
 from mini_llama_cpp_release_b200.engine import MiniBatch
 from mini_llama_cpp_release_b200.models.qwen2 import LAYER_NAMES
 from mini_llama_cpp_release_b200.parts import Part, TensorSpec
@@ -86,8 +86,8 @@ def toy_routed_lm(c: ModelConfig) -> ModelSpec:
     swiglu = PartSpec("feed_forward", "swiglu", dict(hidden_size=c.hidden_size, intermediate_size=c.intermediate_size))
     routed = PartSpec("feed_forward", "toy_routed", dict(hidden_size=c.hidden_size, expert_size=c.extra["toy_expert_size"],
                                                          n_experts=c.extra["toy_n_experts"]))
-    layers = (LayerSpec("model.layers.0.", "prenorm", attn(toy_pos), routed, norm, norm, LAYER_NAMES),
-              LayerSpec("model.layers.1.", "prenorm", attn(rope), swiglu, norm, norm, LAYER_NAMES))
+    layers = (prenorm_layer("model.layers.0.", attn(toy_pos), routed, norm, norm, LAYER_NAMES),
+              prenorm_layer("model.layers.1.", attn(rope), swiglu, norm, norm, LAYER_NAMES))
     return ModelSpec(c, PartSpec("embedding", "token_embedding", dict(vocab_size=c.vocab_size, hidden_size=c.hidden_size)),
                      layers, sequential_schedule(len(layers)), norm,
                      PartSpec("head", "linear_head", dict(vocab_size=c.vocab_size, hidden_size=c.hidden_size)))

@@ -50,6 +50,21 @@ def make_case(seed, lens, H, KV, hd, dtype):
     return q, k_pool, v_pool, table.to(DEV), cu, start
 
 
+def plain_result(q, k_pool, v_pool, table, lens, H, KV, hd, window):
+    """What the plain implementation's attention gives for each sequence's last token: the sequence's keys and values
+    are read out of the pages, the query stands in the last row of an otherwise empty whole-sequence problem."""
+    import plain_impl
+    rows = []
+    for b, n in enumerate(lens):
+        pages = table[b, :(n + 63) // 64].long().cpu()
+        k = k_pool[0].cpu().float()[pages].permute(0, 2, 1, 3).reshape(-1, KV, hd)[:n]
+        v = v_pool[0].cpu().float()[pages].permute(0, 2, 1, 3).reshape(-1, KV, hd)[:n]
+        whole_q = torch.zeros(n, H, hd)
+        whole_q[-1] = q[b].cpu().float().view(H, hd)
+        rows.append(plain_impl.attention(whole_q, k, v, window)[-1].reshape(H * hd))
+    return torch.stack(rows)
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-6), (torch.bfloat16, 1e-2)])
 def test_no_alloc_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row(dtype, tol):
     from mini_llama_cpp_release_b200 import kernels
@@ -57,24 +72,50 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row(dty
     H, KV, hd, n_splits = 14, 2, 64, 6
     code = kernels.dtype_code(dtype)
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, lens in [(1, [700, 33, 1, 260]), (2, [90, 515])]:          # the second call is smaller: stale scratch lies behind it
+    # the second call is smaller: stale scratch lies behind it; the third has a window that leaves most splits empty
+    for seed, lens, window in [(1, [700, 33, 1, 260], 0), (2, [90, 515], 0), (3, [700, 300, 5], 40)]:
         q, k_pool, v_pool, table, cu, start = make_case(seed, lens, H, KV, hd, dtype)
         n = len(lens)
         kv = kernels.KVView(k_pool, v_pool, 0, table, 64, KV, hd)
         want = torch.empty_like(q)
         part_ml = torch.empty(n * H * n_splits * 2, device=DEV)
         part_o = torch.empty(n * H * n_splits * hd, device=DEV)
-        kernels.attention_simt(q, want, cu, start, n, 1, H, kv, 1 / math.sqrt(hd), 0, n_splits, part_ml, part_o)
+        kernels.attention_simt(q, want, cu, start, n, 1, H, kv, 1 / math.sqrt(hd), window, n_splits, part_ml, part_o)
         got = torch.full_like(q, float("nan"))
-        before = torch.cuda.memory_allocated()
-        rc = lib.mlc_attention_split_noalloc(q.data_ptr(), got.data_ptr(), code, cu.data_ptr(), start.data_ptr(), n, n, 1,
-                                             H, KV, hd, 1 / math.sqrt(hd), 0, n_splits, k_pool.data_ptr(),
-                                             v_pool.data_ptr(), table.data_ptr(), 0, table.shape[1], 64, stream)
+        args = (q.data_ptr(), got.data_ptr(), code, cu.data_ptr(), start.data_ptr(), n, n, 1, H, KV, hd, 1 / math.sqrt(hd),
+                window, n_splits, k_pool.data_ptr(), v_pool.data_ptr(), table.data_ptr(), 0, table.shape[1], 64, stream)
+        if seed == 1:
+            assert lib.mlc_attention_split_noalloc(*args) == 0         # the device's first call: loads the kernels, finds the array
+        torch.cuda.synchronize()
+        # free device memory as the driver counts it (cudaMemGetInfo): an allocation inside the library would show
+        # here, which a count kept by PyTorch's own allocator would miss
+        free_before = torch.cuda.mem_get_info()[0]
+        torch_before = torch.cuda.memory_allocated()
+        rc = lib.mlc_attention_split_noalloc(*args)
         assert rc == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == torch_before
         err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
         assert err <= tol, (seed, err)
+        plain = plain_result(q, k_pool, v_pool, table, lens, H, KV, hd, window or None)
+        err = float((got.float().cpu() - plain).abs().max() / plain.abs().max())
+        assert err <= tol, (seed, "against the plain implementation", err)
+
+
+def test_no_alloc_entry_point_with_one_split_uses_no_scratch_and_has_no_size_limit():
+    lib = library()
+    H, KV, hd = 8, 2, 64
+    lens = [70] * 3
+    q, k_pool, v_pool, table, cu, start = make_case(5, lens, H, KV, hd, torch.float32)
+    n = len(lens)
+    got = torch.full_like(q, float("nan"))
+    rc = lib.mlc_attention_split_noalloc(q.data_ptr(), got.data_ptr(), 0, cu.data_ptr(), start.data_ptr(), n, n, 1, H, KV, hd,
+                                         1 / math.sqrt(hd), 0, 1, k_pool.data_ptr(), v_pool.data_ptr(), table.data_ptr(), 0,
+                                         table.shape[1], 64, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    plain = plain_result(q, k_pool, v_pool, table, lens, H, KV, hd, None)
+    assert float((got.cpu() - plain).abs().max() / plain.abs().max()) <= 3e-6
 
 
 def test_no_alloc_entry_point_refuses_what_its_array_cannot_hold():
