@@ -1,325 +1,243 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine on one B200, as one JSON line.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
-    python bench.py --impl reference      # prints why the reference arm cannot run here
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--config NAME] [--dtype bfloat16|float32]
+    python bench.py --impl reference      # the reference project's own GPU path on the same work
 
-A "step" is one decode step of the whole batch.  The default run has the layer sizes of a
-Qwen2-0.5B (24 layers, width 896, 14 query heads on 2 kv heads of size 64, feed-forward
-4864, vocabulary 151936, tied head) with random weights written by the library's
-random-weights mode, a batch of 8 sequences, each with a 2,048-token prompt in a cache of
-4,096 tokens per sequence.
+A "step" is one decode step of the whole batch.  The default run (`--config qwen2-0.5b`) has the layer sizes of a
+Qwen2-0.5B (24 layers, width 896, 14 query heads on 2 kv heads of size 64, feed-forward 4864, vocabulary 151936,
+tied head) with random weights written by the library's random-weights mode, a batch of 8 sequences, each with a
+2,048-token prompt in a cache of 4,096 tokens per sequence.  Other configurations:
+  qwen2-1.5b-ragged16   the 1.5B layer sizes; 16 prompts of lengths uniform in [1, 2048], 128 decoded tokens each
+  qwen2-7b              the 7B layer sizes; 2,048-token prompts in a cache of 8,192 tokens per sequence
 
 What the line holds:
-  value      decoded tokens per second, timed on the device with CUDA events around K
-             replays of the captured decode step (tokens chosen on the device feed the next
-             step; the host is not in the loop);
-  e2e        the same through `LLM.generate`: every step the host's tokens are copied to the
-             device from pinned memory and the chosen ids are read back;
-  prefill    one 2,048-token prompt: tokens per second, milliseconds, fraction of the bf16 peak;
-  roofline   the decode step's bytes (every weight once, the cache of the live requests)
-             over its time, against the measured copy bandwidth;
+  value      decoded tokens per second, timed on the device with CUDA events around K replays of the captured decode
+             step (tokens chosen on the device feed the next step; the host is not in the loop);
+  e2e        the same through `LLM.generate`: every step the host's tokens are copied to the device from pinned memory
+             and the chosen ids are read back; `ids_checked` says how many sequences got the same ids both ways;
+  prefill    one 2,048-token prompt: tokens per second, milliseconds, fraction of the bf16 peak; `first_ms` is the step
+             the first time its shape comes (issued kernel by kernel), `ms` its replay from a captured graph;
+  roofline   the decode step's bytes (every weight once, the cache of the live requests) over its time, against the
+             measured copy bandwidth;
   points     decode tokens per second at batch 1 and 64.
-The reference measures the same two things on the CPU clock: one prefill over the prompt,
-then a loop of single-token steps (src/debug.cpp:107-148).
+The reference measures the same two things on the CPU clock: one prefill over the prompt, then a loop of single-token
+steps (src/debug.cpp:107-148).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
-import statistics
+import shutil
 import subprocess
 import sys
-import tempfile
-import threading
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN2_0_5B = dict(architectures=["Qwen2ForCausalLM"], hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
-                  num_attention_heads=14, num_key_value_heads=2, head_dim=64, vocab_size=151936,
-                  max_position_embeddings=32768, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
-                  use_sliding_window=False, attention_bias=True, hidden_act="silu")
-FULL_LAYERS = 24
-PROMPT_LEN = 2048
-CTX_LEN = 4096
-FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
+# name → (preset of the layer sizes, prompt lengths of the batch or None for equal ones, prompt length, tokens per cache slot)
+CONFIGS = {
+    "qwen2-0.5b": dict(preset="qwen2-0.5b", prompt_len=2048, ctx_len=4096, ragged=None, max_steps=1000),
+    "qwen2-1.5b-ragged16": dict(preset="qwen2-1.5b", prompt_len=2048, ctx_len=4096, ragged=16, max_steps=127),
+    "qwen2-7b": dict(preset="qwen2-7b", prompt_len=2048, ctx_len=8192, ragged=None, max_steps=1000),
+}
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_SOURCE = "/root/reference"
+REF_PREFILL_TOKENS = 32
 
 
-def peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    try:
-        with open(path) as f:
-            p = json.load(f)
-        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p.get("bf16_tflops_sustained") or p["bf16_tflops"]),
-                    bf16_tflops_burst=float(p["bf16_tflops"]), source="measured")
-    except (OSError, KeyError, ValueError, TypeError):
-        return dict(FALLBACK_PEAKS, bf16_tflops_burst=FALLBACK_PEAKS["bf16_tflops"], source="fallback")
+# --------------------------------------------------------------------------------------------------- reference arm
+def build_reference() -> str:
+    """The reference's sources (an unmodified copy under baseline/_ref) and baseline/ref_bench.cpp compiled into one
+    program with nvcc, the way its CMakeLists.txt builds its CUDA targets; returns the program's path."""
+    if not os.path.isdir(os.path.join(REF_DIR, "src")):
+        if not os.path.isdir(os.path.join(REF_SOURCE, "src")):
+            raise RuntimeError("no copy of the reference's sources under baseline/_ref and none to copy from")
+        shutil.copytree(REF_SOURCE, REF_DIR, dirs_exist_ok=True)
+    out_dir = os.path.join(ROOT, "baseline", "_build")
+    os.makedirs(out_dir, exist_ok=True)
+    exe = os.path.join(out_dir, "ref_bench")
+    driver = os.path.join(ROOT, "baseline", "ref_bench.cpp")
+    src_dir = os.path.join(REF_DIR, "src")
+    sources = sorted(os.path.join(src_dir, f) for f in os.listdir(src_dir)
+                     if f.endswith((".cpp", ".cu")) and f != "main.cpp")
+    newest = max(os.path.getmtime(p) for p in sources + [driver])
+    if os.path.exists(exe) and os.path.getmtime(exe) >= newest:
+        return exe
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, "-O2", "-std=c++17", "-gencode", "arch=compute_100,code=sm_100", "-DMINI_LLAMA_USE_CUDA=1",
+           "-I", os.path.join(REF_DIR, "include"), driver, *sources, "-lcublas", "-lcudart", "-lpthread", "-o", exe]
+    print("[bench] building the reference with nvcc (about a minute)", file=sys.stderr, flush=True)
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if p.returncode != 0:
+        raise RuntimeError("nvcc could not build the reference: " + p.stdout[-400:].replace("\n", " "))
+    return exe
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int = 0):
-        self.index = index
-        self.proc = None
-        self.lines = []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-        return self
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=sorted(reasons), samples=len(sm))
+def reference_line(args, raw, work) -> dict:
+    """Runs baseline/ref_bench (none of this repository's engine in that process) and shapes its figures like ours."""
+    from mini_llama_cpp_release_b200.measure import ClockSampler
+    exe = build_reference()
+    # a pass of the reference takes a fraction of a second: more than 32 steps would hold the GPU for minutes
+    steps, warmup = max(1, min(args.steps, 32)), max(3, min(args.warmup, 4))
+    layers = args.layers or raw["num_hidden_layers"]
+    cmd = [exe] + [str(v) for v in (
+        raw["vocab_size"], raw["hidden_size"], raw["intermediate_size"], layers, raw["num_attention_heads"],
+        raw["num_key_value_heads"], raw["head_dim"], work["ctx_len"], raw["rope_theta"], raw["rms_norm_eps"],
+        args.batch, work["prompt_len"], steps, warmup, 1234, REF_PREFILL_TOKENS)]
+    clocks = ClockSampler(0).start()
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    clock_info = clocks.stop()
+    if p.returncode != 0:
+        raise RuntimeError("the reference's GPU path failed: " + (p.stderr.strip().splitlines() or ["no message"])[-1])
+    r = json.loads(p.stdout.strip().splitlines()[-1])
+    return {
+        "impl": "reference",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen2-0.5B shape, 2,048-token prompts, context 4,096)",
+        "value": round(r["decode_tokens_per_s"], 3), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(r["decode_ms_per_step"], 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic: seeded uniform token ids, seeded N(0, 0.02) weights",
+        "config": dict(describe(raw, layers, args.batch, work), decode_steps=steps,
+                       reference_path="unmodified src/*.cpp and src/*.cu, forward_batch on one context per sequence, one token per pass",
+                       context_reached="every context starts at position prompt_len over the reference's zero-filled cache: "
+                                       "feeding 8 x 2,048 prompt tokens at its ~0.26 s a pass would take over an hour",
+                       timing="host clock around forward_batch, the reference's own definition; logits return to the host in every pass"),
+        "e2e": {"value": round(r["e2e_tokens_per_s"], 3), "unit": "tokens/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
+        "gpu_launches": 0,
+        "prefill": {"value": round(r["prefill_tokens_per_s"], 3), "tokens": r["prefill_tokens"], "ms": round(r["prefill_ms"], 1)},
+        "clocks": clock_info,
+    }
 
 
-def model_folder(layers: int, seed: int = 1234) -> str:
-    """The benchmark model, written once per machine into the temporary directory."""
-    import torch
-    import mini_llama_cpp_release_b200 as ml
-    from mini_llama_cpp_release_b200.config import ModelConfig
-    cfg = ModelConfig.from_dict(dict(QWEN2_0_5B, num_hidden_layers=layers))
-    folder = os.path.join(tempfile.gettempdir(), f"mlc_bench_qwen2_0.5b_L{layers}_s{seed}_{os.getuid()}")
-    marker = os.path.join(folder, "complete")
-    if not os.path.exists(marker):
-        t0 = time.time()
-        ml.write_random_model(cfg, folder, seed, torch.bfloat16)
-        with open(marker, "w") as f:
-            f.write("ok\n")
-        print(f"[bench] wrote random model ({layers} layers) in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
-    return folder
+def describe(raw, layers, batch, work) -> dict:
+    """The `config` field: every size, flat."""
+    return {
+        "model": f"{work['preset']} layer sizes, random weights", "layers": layers, "layers_full": raw["num_hidden_layers"],
+        "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+        "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+        "tied_head": bool(raw["tie_word_embeddings"]), "global_batch": batch, "prompt_len": work["prompt_len"],
+        "seq_len": work["ctx_len"], "parallelism": "single GPU",
+    }
 
 
-def random_prompts(n: int, length: int, vocab: int, seed: int):
-    import torch
-    g = torch.Generator().manual_seed(seed)
-    return torch.randint(0, vocab, (n, length), generator=g).tolist()
-
-
-def prefill_in_groups(ctx, slots, prompts, group: int = 8):
-    """Prompts into the cache, a few sequences per step; returns each one's first greedy token."""
-    import torch
-    from mini_llama_cpp_release_b200.engine import MiniBatch
-    first = []
-    for i in range(0, len(slots), group):
-        logits = ctx.forward_batch(MiniBatch.prefill(slots[i:i + group], prompts[i:i + group]))
-        first.extend(logits.argmax(dim=-1).tolist())
-    return first
-
-
-def time_decode(llm, batch: int, steps: int, warmup: int, seed: int, sample_clocks: bool = False):
-    """Device-timed decode: returns (ms per step, tokens/s, launches per step, mean cached length, clocks)."""
-    import torch
-    from mini_llama_cpp_release_b200.sampling import DeviceSampler, SamplingParams
-    ctx = llm.context
-    dev = llm.model.runtime.device
-    sampler = DeviceSampler(SamplingParams(), dev)
-    prompts = random_prompts(batch, PROMPT_LEN, llm.config.vocab_size, seed)
-    slots = [ctx.acquire() for _ in range(batch)]
-    try:
-        first = prefill_in_groups(ctx, slots, prompts)
-        ids = list(range(batch))
-        out = ctx.decode_on_device(slots, first, sampler, ids, warmup)
-        tokens = out[-1].tolist()
-        len_before = ctx.length(slots[0])
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        clocks = ClockSampler(dev.index or 0).start() if sample_clocks else None
-        if clocks is not None:
-            time.sleep(0.3)
-
-        def before():
-            torch.cuda.synchronize(dev)
-            start.record()
-
-        def after():
-            end.record()
-            torch.cuda.synchronize(dev)
-
-        ctx.decode_on_device(slots, tokens, sampler, ids, steps, before=before, after=after)
-        ms = start.elapsed_time(end)
-        clock_info = clocks.stop() if clocks is not None else None
-        runner = next(r for r in ctx._runners.values() if r.B == batch)
-        mean_len = len_before + (steps + 1) / 2.0
-        return ms / steps, batch * steps / (ms / 1e3), runner.launches_per_step, runner.library_launches_per_step, mean_len, clock_info
-    finally:
-        for s in slots:
-            ctx.release(s)
-
-
-def time_e2e(llm, batch: int, steps: int, seed: int):
-    """Decode through `LLM.generate`: host tokens in, host tokens out at every step."""
-    import torch
-    prompts = random_prompts(batch, PROMPT_LEN, llm.config.vocab_size, seed)
-    marks = []
-    copies = []
-
-    def on_step(live, chosen, logits):
-        marks.append(time.perf_counter())
-        copies.append(getattr(llm.context, "last_copy_bytes", (0, 0)))
-
-    llm.generate(prompts, n_predict=4, stop_token_ids=[], on_step=on_step)          # warm-up: graph capture
-    marks.clear(); copies.clear()
-    llm.generate(prompts, n_predict=steps + 1, stop_token_ids=[], on_step=on_step)
-    elapsed = marks[-1] - marks[0]
-    per_step = copies[len(copies) // 2]
-    return batch * steps / elapsed, per_step[0], per_step[1]
-
-
-def time_prefill(llm, iters: int = 5, warmup: int = 3):
-    import torch
-    from mini_llama_cpp_release_b200.engine import MiniBatch
-    ctx = llm.context
-    dev = llm.model.runtime.device
-    prompt = random_prompts(1, PROMPT_LEN, llm.config.vocab_size, 77)[0]
-    times = []
-    for i in range(warmup + iters):
-        s = ctx.acquire()
-        torch.cuda.synchronize(dev)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        ctx.forward_batch(MiniBatch.from_tokens(s, prompt))
-        b.record()
-        torch.cuda.synchronize(dev)
-        ctx.release(s)
-        if i >= warmup:
-            times.append(a.elapsed_time(b))
-    return statistics.median(times)
-
-
-def prefill_flops(cfg, layers: int, T: int) -> float:
-    d, I, H, KV, hd, V = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"],
-                          cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"])
-    per_layer_w = (H + 2 * KV) * hd * d + d * H * hd + 3 * I * d
-    linear = 2.0 * T * per_layer_w * layers
-    attention = layers * H * 2.0 * T * T * hd           # causal: half of QK^T and PV over T x T
-    head = 2.0 * V * d                                   # logits at one position
-    return linear + attention + head
-
-
+# --------------------------------------------------------------------------------------------------- our arm
 def main() -> int:
-    global PROMPT_LEN
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--config", default="qwen2-0.5b", choices=sorted(CONFIGS))
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run one part only and print a short line (for profiling a small case)")
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the --only runs")
+    ap.add_argument("--prompt-len", type=int, default=None, help="prompt length of the --only runs")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a C++/CMake project with no Python packaging: pip cannot install it, its CUDA "
-                          "build needs CMake to fetch googletest from the network, and its files cannot express this model"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is outside what this library does (single-GPU engine)")
         return 2
 
-    import torch
-    import mini_llama_cpp_release_b200 as ml
-    from mini_llama_cpp_release_b200 import kernels
+    from mini_llama_cpp_release_b200 import measure
+    work = dict(CONFIGS[args.config])
+    raw = dict(measure.PRESETS[work["preset"]])
+    if args.batch is None:
+        args.batch = work["ragged"] or 8
 
-    if args.only:
-        PROMPT_LEN = max(1, min(args.prompt_len, CTX_LEN - 64))
+    if args.impl == "reference":
+        try:
+            if args.config != "qwen2-0.5b":
+                raise RuntimeError("the reference arm is set up for the headline configuration only")
+            print(json.dumps(reference_line(args, raw, work)))
+        except Exception as e:                                     # noqa: BLE001  (whatever stops it is the reason)
+            print(json.dumps({"impl": "reference", "unavailable": " ".join(str(e).split())[:300]}))
+        return 0
+
+    import mini_llama_cpp_release_b200 as ml
+
+    layers = args.layers or raw["num_hidden_layers"]
+    raw_run = dict(raw, num_hidden_layers=layers)
+    if args.only and args.prompt_len:
+        work["prompt_len"] = max(1, min(args.prompt_len, work["ctx_len"] - 64))
+    prompt_len, ctx_len = work["prompt_len"], work["ctx_len"]
     warmup = max(3, args.warmup)
-    steps = max(1, min(args.steps, CTX_LEN - PROMPT_LEN - warmup - 8, 1000))
-    pk = peaks()
-    folder = model_folder(args.layers)
-    max_batch = max(args.batch, 1 if args.no_points else 64)
-    llm = ml.load(folder, dtype="bfloat16", max_tokens=max_batch * CTX_LEN, max_seqs=max_batch)
-    cache = llm.context.cache
+    steps = max(1, min(args.steps, ctx_len - prompt_len - warmup - 8, work["max_steps"]))
+    pk = measure.peaks(ROOT)
+    folder = measure.random_model_folder(raw_run, tag=f"bench_{work['preset']}_L{layers}")
+    vocab = raw["vocab_size"]
+    if work["ragged"]:
+        import torch
+        g = torch.Generator().manual_seed(5)
+        lengths = torch.randint(1, prompt_len + 1, (args.batch,), generator=g).tolist()
+    else:
+        lengths = [prompt_len] * args.batch
+    max_batch = max(args.batch, 1 if (args.no_points or args.only or work["ragged"]) else 64)
+    llm = ml.load(folder, dtype=args.dtype, max_tokens=max_batch * ctx_len, max_seqs=max_batch, max_batch_tokens=16384)
+    prompts = measure.random_prompts(lengths, vocab, seed=1)
+    one_prompt = measure.random_prompts([prompt_len], vocab, seed=77)
 
     if args.only == "prefill":
-        ms = time_prefill(llm, iters=max(1, min(args.steps, 5)), warmup=min(warmup, 3))
-        print(json.dumps({"only": "prefill", "ms": round(ms, 3), "tokens": PROMPT_LEN, "layers": args.layers}))
+        t = measure.time_prefill(llm, one_prompt, iters=max(1, min(args.steps, 5)), warmup=min(warmup, 3))
+        print(json.dumps({"only": "prefill", "ms": round(t["ms"], 3), "first_ms": round(t["first_ms"], 3), "tokens": prompt_len,
+                          "layers": layers, "dtype": args.dtype}))
         return 0
     if args.only == "decode":
-        ms_step, tok_s, launches, lib_launches, mean_len, _ = time_decode(llm, args.batch, steps, warmup, seed=1)
-        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms_step, 4), "tokens_per_s": round(tok_s, 1),
-                          "launches_per_step": launches, "library_launches_per_step": lib_launches, "layers": args.layers}))
+        d = measure.time_decode(llm, prompts, steps, warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(d["ms_per_step"], 4),
+                          "tokens_per_s": round(d["tokens_per_s"], 1), "launches_per_step": d["launches_per_step"],
+                          "library_launches_per_step": d["library_launches_per_step"], "layers": layers, "dtype": args.dtype,
+                          "hbm_frac": measure.roofline(d["step_bytes"], d["ms_per_step"], pk)["frac"]}))
         return 0
 
-    prefill_ms = time_prefill(llm)
-    flops = prefill_flops(QWEN2_0_5B, args.layers, PROMPT_LEN)
+    pre = measure.time_prefill(llm, one_prompt)
+    flops = measure.prefill_flops(raw, layers, [prompt_len])
+    peak_flops = pk["bf16_tflops_burst"] * 1e12 if args.dtype == "bfloat16" else None
 
-    kernels.reset_launch_count()
-    ms_step, tok_s, launches, lib_launches, mean_len, clocks = time_decode(llm, args.batch, steps, warmup, seed=1, sample_clocks=True)
-    step_bytes = llm.model.weight_bytes_per_step() + args.batch * mean_len * cache.bytes_per_token()
-    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    d = measure.time_decode(llm, prompts, steps, warmup, sample_clocks=True)
 
     points = {}
-    if not args.no_points:
+    if not (args.no_points or work["ragged"]):
         for b in (1, 64):
             if b == args.batch:
-                points[f"decode_b{b}"] = round(tok_s, 1)
+                points[f"decode_b{b}"] = round(d["tokens_per_s"], 1)
                 continue
-            _, t, *_ = time_decode(llm, b, steps, warmup, seed=2 + b)
-            points[f"decode_b{b}"] = round(t, 1)
+            p = measure.time_decode(llm, measure.random_prompts([prompt_len] * b, vocab, seed=2 + b), steps, warmup)
+            points[f"decode_b{b}"] = round(p["tokens_per_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = measure.roofline(p["step_bytes"], p["ms_per_step"], pk)["frac"]
 
-    e2e_tok_s, h2d, d2h = time_e2e(llm, args.batch, min(steps, 128), seed=9)
+    e2e_steps = min(steps, 128)
+    e = measure.time_e2e(llm, prompts, e2e_steps)
+    # the device-fed loop that `value` times and `generate` must choose the same tokens from the same prompts
+    same = measure.agreement(d["chosen"], e["generated"], 32)
+    if same["equal_sequences"] * 2 < same["of"]:
+        print(f"bench.py: the device-fed decode loop and generate() disagree on the ids of {same['of'] - same['equal_sequences']} "
+              f"of {same['of']} sequences within {same['steps']} steps; the timed path is not the product's", file=sys.stderr)
+        return 1
 
+    work_name = "2,048-token prompts" if not work["ragged"] else f"{args.batch} prompts of 1 to 2,048 tokens"
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen2-0.5B shape, 2,048-token prompts, context 4,096)",
-        "value": round(tok_s, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: seeded uniform token ids, seeded N(0, 0.02) weights",
-        "config": {
-            "model": "Qwen2-0.5B shape, random weights", "layers": args.layers, "layers_full": FULL_LAYERS,
-            "hidden": 896, "heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864, "vocab": 151936,
-            "tied_head": True, "global_batch": args.batch, "prompt_len": PROMPT_LEN, "seq_len": CTX_LEN,
-            "decode_steps": steps, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + cache per step)",
-            "peaks": pk["source"], "prefill_step": "the repeated step shape replays a captured CUDA graph",
-        },
-        "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches * steps, "library_gemm_launches": lib_launches * steps,
-        "prefill": {"value": round(PROMPT_LEN / (prefill_ms / 1e3), 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 3),
-                    "frac": round(flops / (prefill_ms / 1e3) / (pk["bf16_tflops_burst"] * 1e12), 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "metric": f"decode tok/s at batch {args.batch} ({work['preset']} shape, {work_name}, context {ctx_len:,})",
+        "value": round(d["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(d["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "data": "synthetic: seeded uniform token ids, seeded N(0, 0.02) weights",
+        "config": dict(describe(raw, layers, args.batch, work), decode_steps=steps,
+                       l2="inputs larger than L2 (weights + cache per step)", peaks=pk["source"],
+                       prefill_step="ms: the repeated step shape replays a captured CUDA graph; first_ms: issued kernel by kernel"),
+        "e2e": {"value": round(e["tokens_per_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ids_checked": same},
+        "gpu_launches": d["launches_per_step"] * steps, "library_gemm_launches": d["library_launches_per_step"] * steps,
+        "prefill": {"value": round(prompt_len / (pre["ms"] / 1e3), 1), "tokens": prompt_len, "ms": round(pre["ms"], 3),
+                    "first_ms": round(pre["first_ms"], 3),
+                    "frac": round(flops / (pre["ms"] / 1e3) / peak_flops, 4) if peak_flops else None},
+        "roofline": measure.roofline(d["step_bytes"], d["ms_per_step"], pk),
         "points": points,
-        "clocks": clocks,
+        "clocks": d["clocks"],
     }
     print(json.dumps(line))
     return 0

@@ -11,6 +11,7 @@ weights.  `python -m mini_llama_cpp_release_b200 generate|bench|inspect|replay` 
 command line; `bin/trace_run` replays token traces.
 """
 from .api import LLM, load  # noqa: F401
+from .engine.engine_config import EngineConfig  # noqa: F401
 from .config import ConfigError, ModelConfig, register_architecture, register_part  # noqa: F401
 from .engine import Context, MiniBatch, Model  # noqa: F401
 from .sampling import SamplingParams  # noqa: F401

@@ -12,26 +12,17 @@ from typing import List, Optional, Sequence, Union
 import torch
 
 from .engine.context import Context
+from .engine.engine_config import EngineConfig, parse_dtype  # noqa: F401
 from .engine.generate import GenerationResult, generate
 from .engine.model import Model
 from .sampling.sampler import DeviceSampler, SamplingParams
 
-_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
-           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
-
-
-def parse_dtype(dtype) -> torch.dtype:
-    try:
-        return _DTYPES[dtype]
-    except KeyError:
-        raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}") from None
-
-
 class LLM:
-    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None):
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
+                 max_batch_tokens: int = EngineConfig.max_batch_tokens):
         self.model = model
         self.config = model.config
-        self.context = Context(model, max_tokens, max_seqs)
+        self.context = Context(model, max_tokens, max_seqs, max_batch_tokens=max_batch_tokens)
 
     def generate(self, prompts: Sequence[Sequence[int]], n_predict: Union[int, Sequence[int]] = 16, temperature: float = 0.0,
                  top_k: int = 0, seed: int = 0, stop_token_ids: Optional[Sequence[int]] = None,
@@ -51,12 +42,20 @@ class LLM:
 
 
 def load(folder: str, dtype="bfloat16", device: str = "cuda:0", max_tokens: int = 8192,
-         max_seqs: Optional[int] = None) -> LLM:
-    """A model folder (config.json + model.safetensors) → an `LLM` on `device`.  `max_tokens`
-    sizes the cache: the most tokens live sequences hold at any time, each rounded up to 64."""
+         max_seqs: Optional[int] = None, max_batch_tokens: Optional[int] = None, engine: Optional[EngineConfig] = None,
+         config_path: Optional[str] = None) -> LLM:
+    """A model folder (config.json + model.safetensors) → an `LLM` on a CUDA device.  How it runs is an `EngineConfig`,
+    given whole as `engine` or by its fields as keywords: `max_tokens` sizes the cache (the most tokens live sequences
+    hold at any time, each rounded up to 64), `max_seqs` the number of slots, `max_batch_tokens` the largest step.
+    `folder` may also be the path of one .safetensors file; its config.json is then `config_path`, or lies beside it."""
+    if engine is None:
+        engine = EngineConfig(dtype=dtype, device=device, max_tokens=max_tokens, max_seqs=max_seqs,
+                              **({} if max_batch_tokens is None else {"max_batch_tokens": max_batch_tokens}))
     # float32 products must be float32: no TF32, no reduced-precision accumulation
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
-    model = Model.from_folder(folder, parse_dtype(dtype), device)
-    return LLM(model, max_tokens, max_seqs)
+    model = Model.from_folder(folder, engine.dtype, engine.device, config_path=config_path)
+    llm = LLM(model, engine.max_tokens, engine.max_seqs, engine.max_batch_tokens)
+    llm.engine = engine
+    return llm

@@ -148,6 +148,21 @@ class SlotBook:
         if any(want):
             self._touch(slot)
 
+    def reserve_all(self, wishes: Sequence[Tuple[int, int]]) -> None:
+        """`reserve` for several (slot, n_new) at once: all of them, or none and `CacheFull`."""
+        need = [0] * len(self.groups)
+        for slot, n_new in wishes:
+            self._require(slot)
+            n_needed = (self.length[slot] + n_new + self.page_size - 1) // self.page_size
+            for g, pl in enumerate(self.page_lists[slot]):
+                need[g] += max(0, n_needed - len(pl))
+        for g, k in enumerate(need):
+            if k > self.pages[g].n_free:
+                raise CacheFull(f"the batch needs {k} more page(s) of {self.page_size} tokens in group {g}, "
+                                f"{self.pages[g].n_free} of {self.n_pages} are free (the cache was sized for too few tokens)")
+        for slot, n_new in wishes:
+            self.reserve(slot, n_new)
+
     def commit(self, slot: int, n_new: int) -> None:
         """The n_new tokens are in the cache now; drop pages a window has left behind."""
         self._require(slot)

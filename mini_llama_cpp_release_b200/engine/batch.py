@@ -9,7 +9,7 @@ positions follow from that and are not given twice.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 
 @dataclass
@@ -72,3 +72,31 @@ class MiniBatch:
             for w in c.want:
                 if not 0 <= w < len(c.tokens):
                     raise IndexError(f"forward_batch: wanted place {w} is outside the {len(c.tokens)} tokens of slot {c.slot}")
+
+    def split(self, max_tokens: int) -> List[Tuple["MiniBatch", List[Tuple[int, int]]]]:
+        """The batch cut into steps of at most `max_tokens` tokens, sequence by sequence in order: a step takes whole
+        sequences while they fit and then the first part of the next one, whose rest opens the following step (it
+        continues where the cache then stands, so nothing but the cut differs).  With each step comes, for every
+        row of logits it will return, which wanted place of the original batch it is: (index of the sequence,
+        index into that sequence's `want`)."""
+        if max_tokens < 1:
+            raise ValueError("a step must be allowed at least one token")
+        pieces: List[Tuple[MiniBatch, List[Tuple[int, int]]]] = []
+        cur: List[SequenceChunk] = []
+        keys: List[Tuple[int, int]] = []
+        room = max_tokens
+        for e, c in enumerate(self.chunks):
+            lo = 0
+            while lo < len(c.tokens):
+                take = min(room, len(c.tokens) - lo)
+                here = [(j, w - lo) for j, w in enumerate(c.want) if lo <= w < lo + take]
+                cur.append(SequenceChunk(c.slot, c.tokens[lo:lo + take], [w for _, w in here]))
+                keys.extend((e, j) for j, _ in here)
+                lo += take
+                room -= take
+                if room == 0:
+                    pieces.append((MiniBatch(cur), keys))
+                    cur, keys, room = [], [], max_tokens
+        if cur:
+            pieces.append((MiniBatch(cur), keys))
+        return pieces

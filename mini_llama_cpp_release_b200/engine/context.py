@@ -26,10 +26,15 @@ class ContextOverflow(ValueError):
 
 
 class Context:
-    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = PAGE_SIZE):
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = PAGE_SIZE,
+                 max_batch_tokens: int = 16384):
         """`max_tokens`: the most tokens live sequences hold at any time, each sequence's
-        count rounded up to whole pages of `page_size` tokens."""
+        count rounded up to whole pages of `page_size` tokens.  `max_batch_tokens`: the most
+        tokens one step runs at once; a larger batch is run as several steps."""
         self.model = model
+        if max_batch_tokens < 1:
+            raise ValueError("max_batch_tokens must be positive")
+        self.max_batch_tokens = int(max_batch_tokens)
         rt = model.runtime
         if max_seqs is None:
             max_seqs = min((max_tokens + page_size - 1) // page_size, 4096)
@@ -170,8 +175,35 @@ class Context:
 
     def forward_batch(self, batch: MiniBatch) -> torch.Tensor:
         """Run the batch's tokens; returns float32 logits [number of wanted places, vocab], in
-        the order of the batch's sequences and of each one's `want`."""
+        the order of the batch's sequences and of each one's `want`.  A batch of more than
+        `max_batch_tokens` tokens runs as several steps, cut sequence by sequence; the later
+        part of a cut sequence continues from the cache like any later chunk of it would."""
         batch.validate(self.model.config.vocab_size)
+        if batch.n_tokens <= self.max_batch_tokens:
+            return self._forward_step(batch)
+        # everything that can be refused is refused before the first piece runs
+        for c in batch.chunks:
+            if c.slot not in self.cache.length:
+                raise ValueError(f"forward_batch: slot {c.slot} is not held")
+            if self.cache.length[c.slot] + len(c.tokens) > self.max_position:
+                raise ContextOverflow(f"slot {c.slot}: {self.cache.length[c.slot]} cached + {len(c.tokens)} new tokens pass "
+                                      f"max_position_embeddings {self.max_position}")
+        self.cache.reserve_all([(c.slot, len(c.tokens)) for c in batch.chunks])
+        outs, keys = [], []
+        for piece, piece_keys in batch.split(self.max_batch_tokens):
+            outs.append(self._forward_step(piece))
+            keys.extend(piece_keys)
+        self.n_steps -= len(outs) - 1                      # one call, one step in the count
+        wanted = [(e, j) for e, c in enumerate(batch.chunks) for j in range(len(c.want))]
+        logits = torch.cat(outs, dim=0)
+        if keys == wanted:
+            return logits
+        row_of = {k: r for r, k in enumerate(keys)}
+        order = torch.tensor([row_of[k] for k in wanted], dtype=torch.long, device=logits.device)
+        return logits.index_select(0, order)
+
+    def _forward_step(self, batch: MiniBatch) -> torch.Tensor:
+        """One step: all of the batch's tokens at once."""
         dev = self.model.runtime.device
         with torch.cuda.device(dev):
             n_new = sum(len(c.tokens) for c in batch.chunks)

@@ -11,6 +11,16 @@ For a step with wanted places, `<out>/<step>.f32` gets the logits, little-endian
 [wanted, vocab], in the order of the entries and of each entry's `want`.  After every step
 `done <step>` is printed and flushed.  Requests named in `end` give their slot and pages
 back after the step.
+
+Beside the logits, `<out>/index.jsonl` gets one line per request and step: the step, the
+request's id, the cache slot it holds, the positions its tokens took, and which rows of
+`<step>.f32` are its wanted places (the reference writes `generation_tokens.txt` beside its
+per-step files for the same purpose: to say what the files hold, src/main.cpp:322-337).
+Slots that are used again by later requests show there.
+
+The plain implementation under tests/ is not driven from here: it is test code, and the
+package imports nothing from the tests.  A test that wants both runs the same trace through
+it itself (tests/test_replay_gpu.py does).
 """
 from __future__ import annotations
 
@@ -31,6 +41,8 @@ class Replayer:
         self.out_dir = out_dir
         os.makedirs(out_dir, exist_ok=True)
         self.slot_of: Dict[str, int] = {}
+        self.index_path = os.path.join(out_dir, "index.jsonl")
+        open(self.index_path, "w").close()
 
     def step(self, record: dict) -> Optional[torch.Tensor]:
         step_id = record["step"]
@@ -45,6 +57,7 @@ class Replayer:
                 chunks.append(SequenceChunk(self.slot_of[rid], [int(t) for t in e["tokens"]],
                                             [int(w) for w in e.get("want", [])]))
             logits = None
+            starts = [self.ctx.length(c.slot) for c in chunks]
             if chunks:
                 logits = self.ctx.forward_batch(MiniBatch(chunks))
         except Exception:
@@ -57,6 +70,13 @@ class Replayer:
             with open(path + ".tmp", "wb") as f:
                 f.write(data.astype("<f4", copy=False).tobytes())
             os.replace(path + ".tmp", path)
+        with open(self.index_path, "a") as f:
+            row = 0
+            for e, c, start in zip(record.get("entries", []), chunks, starts):
+                f.write(json.dumps({"step": step_id, "id": str(e["id"]), "slot": c.slot,
+                                    "positions": [start, start + len(c.tokens)],
+                                    "rows": list(range(row, row + len(c.want)))}) + "\n")
+                row += len(c.want)
         for rid in record.get("end", []):
             rid = str(rid)
             if rid in self.slot_of:

@@ -12,6 +12,7 @@ if os.path.dirname(os.path.abspath(__file__)) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    config.addinivalue_line("markers", "slow: takes tens of seconds (a model of real width and vocabulary)")
 
 
 def pytest_collection_modifyitems(config, items):

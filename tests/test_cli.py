@@ -72,5 +72,79 @@ def test_bench_command_prints_the_references_report():
     p = run("bench", helpers.model_folder("B"), "-n", "8", "--prompt-len", "20", "--batch", "3", "--verbose")
     assert p.returncode == 0, p.stderr[-2000:]
     for key in ("prompt tokens:     60", "generated tokens:  24", "decode tokens:     21", "prefill ms:", "tokens/s (decode):",
-                "logits shape: [3, 1000]"):
+                "logits shape: [3, 1000]", "GB/s of weights and cache", "limited by", "TFLOP/s"):
         assert key in p.stdout
+
+
+def test_model_comes_from_a_folder_a_file_or_a_random_configuration(tmp_path, monkeypatch):
+    """`--model <path|dir>` and `--config` as the reference resolves them (src/main.cpp:280-281, 452-461), and
+    `--random <preset|config.json>`, which writes a model folder from the configuration and a seed."""
+    import argparse
+    from mini_llama_cpp_release_b200 import measure
+
+    def parse(*argv, positional=False):
+        ap = argparse.ArgumentParser()
+        cli.add_model_options(ap, positional=positional)
+        cli.add_engine_options(ap)
+        return ap.parse_args(list(argv))
+
+    assert cli.resolve_model(parse("--model", "some/dir")) == ("some/dir", None)
+    assert cli.resolve_model(parse("--model", "w.safetensors", "--config", "c.json")) == ("w.safetensors", "c.json")
+    assert cli.resolve_model(parse("some/dir", positional=True)) == ("some/dir", None)
+    with pytest.raises(SystemExit, match="--model"):
+        cli.resolve_model(parse())
+    with pytest.raises(SystemExit, match="not both"):
+        cli.resolve_model(parse("--model", "x", "--random", "tiny-a"))
+    with pytest.raises(SystemExit, match="neither a preset"):
+        cli.resolve_model(parse("--random", "qwen9"))
+    monkeypatch.setattr("tempfile.gettempdir", lambda: str(tmp_path))
+    folder, cfg_path = cli.resolve_model(parse("--random", "tiny-a", "--weights-seed", "5"))
+    assert cfg_path is None and os.path.exists(os.path.join(folder, "model.safetensors"))
+    assert helpers.ml.ModelConfig.from_folder(folder).hidden_size == 64
+    assert cli.resolve_model(parse("--random", "tiny-a", "--weights-seed", "5"))[0] == folder       # found again, not rewritten
+    assert cli.resolve_model(parse("--random", "tiny-a", "--weights-seed", "6"))[0] != folder
+    # a configuration of one's own, by the path of its config.json
+    helpers.ml.ModelConfig.from_dict(helpers.TINY_B).save(str(tmp_path / "mine"))
+    folder_b, _ = cli.resolve_model(parse("--random", str(tmp_path / "mine" / "config.json")))
+    assert helpers.ml.ModelConfig.from_folder(folder_b).vocab_size == 1000
+    # the five presets are the five configurations the measurements are quoted on
+    assert sorted(measure.PRESETS) == ["qwen2-0.5b", "qwen2-1.5b", "qwen2-7b", "tiny-a", "tiny-b"]
+    for raw in measure.PRESETS.values():
+        helpers.ml.ModelConfig.from_dict(raw)
+    # the engine's sizes
+    e = cli.engine_config(parse("--model", "x", "--slots", "3", "--dtype", "fp32", "--max-batch-tokens", "100"), need_tokens=640)
+    assert (e.max_tokens, e.max_seqs, e.slots, e.dtype, e.max_batch_tokens) == (640, 3, 3, torch.float32, 100)
+    with pytest.raises(SystemExit, match="max_batch_tokens"):
+        cli.engine_config(parse("--model", "x", "--max-batch-tokens", "0"), need_tokens=64)
+
+
+def test_engine_configuration_is_checked():
+    from mini_llama_cpp_release_b200 import EngineConfig
+    e = EngineConfig()
+    assert (e.dtype, e.device, e.max_tokens, e.max_seqs, e.max_batch_tokens, e.slots) == (torch.bfloat16, "cuda:0", 8192, None, 16384, 128)
+    assert EngineConfig(max_tokens=100, max_seqs=50).slots == 2          # never more slots than pages
+    for bad, word in [(dict(device="cpu"), "CUDA"), (dict(dtype="float16"), "dtype"), (dict(max_tokens=0), "max_tokens"),
+                      (dict(max_seqs=0), "max_seqs"), (dict(max_batch_tokens=-4), "max_batch_tokens"), (dict(max_tokens=2.5), "max_tokens")]:
+        with pytest.raises(ValueError, match=word):
+            EngineConfig(**bad)
+
+
+@pytest.mark.gpu
+def test_generate_from_random_weights_of_a_preset_with_no_model_on_disk(tmp_path):
+    env_tmp = str(tmp_path)
+    p = subprocess.run([sys.executable, "-m", "mini_llama_cpp_release_b200", "generate", "--random", "tiny-b", "--tokens", "1,2,3;7",
+                        "-n", "8", "--slots", "2"], cwd=ROOT, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, TMPDIR=env_tmp))
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.splitlines() if l.startswith("generated ids:")]
+    assert len(lines) == 2 and all(len(l.split()) == 10 for l in lines)
+    # the same through a weights file and a config.json that lie apart
+    folder = helpers.model_folder("A", std=0.1)
+    import shutil
+    shutil.copy(os.path.join(folder, "model.safetensors"), str(tmp_path / "w.safetensors"))
+    shutil.copy(os.path.join(folder, "config.json"), str(tmp_path / "c.json"))
+    p = run("--model", str(tmp_path / "w.safetensors"), "--config", str(tmp_path / "c.json"), "--tokens", "5,17,3,200", "-n", "5",
+            "--dtype", "float32", "--stop-ids", "511")
+    assert p.returncode == 0, p.stderr[-2000:]
+    ids = helpers.plain_model(folder).greedy([5, 17, 3, 200], 5)
+    assert f"generated ids: {' '.join(map(str, ids))}" in p.stdout

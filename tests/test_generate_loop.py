@@ -176,3 +176,18 @@ def test_n_predict_per_request_ends_each_sequence_at_its_own_count():
     assert ctx.cache.slots.n_free == 4
     with pytest.raises(ValueError, match="3 entries for 4 requests"):
         generate(ctx, greedy(), prompts, n_predict=[1, 2, 3])
+
+
+def test_a_batch_is_cut_into_steps_sequence_by_sequence_and_rows_keep_their_places():
+    from mini_llama_cpp_release_b200.engine.batch import SequenceChunk
+    b = MiniBatch([SequenceChunk(0, list(range(5)), [4, 1]), SequenceChunk(1, list(range(3)), [2]),
+                   SequenceChunk(2, list(range(7)), [0, 6, 3])])
+    pieces = b.split(4)
+    assert [[(c.slot, c.tokens, c.want) for c in sub.chunks] for sub, _ in pieces] == [
+        [(0, [0, 1, 2, 3], [1])], [(0, [4], [0]), (1, [0, 1, 2], [2])], [(2, [0, 1, 2, 3], [0, 3])], [(2, [4, 5, 6], [2])]]
+    assert [keys for _, keys in pieces] == [[(0, 1)], [(0, 0), (1, 0)], [(2, 0), (2, 2)], [(2, 1)]]
+    assert all(sub.n_tokens <= 4 for sub, _ in pieces) and sum(sub.n_tokens for sub, _ in pieces) == b.n_tokens
+    whole = b.split(100)
+    assert len(whole) == 1 and whole[0][1] == [(0, 0), (0, 1), (1, 0), (2, 0), (2, 1), (2, 2)]
+    with pytest.raises(ValueError):
+        b.split(0)

@@ -150,3 +150,111 @@ def test_a_cache_too_small_for_the_trace_says_so(tmp_path):
     rp.step(dict(step=2, entries=[dict(id="a", tokens=[2], want=[0])], end=["a"]))
     rp.step(dict(step=3, entries=[dict(id="b", tokens=[1] * 120, want=[119])], end=["b"]))
     llm.context.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_larger_than_the_engine_allows_runs_in_pieces_with_the_same_result(dtype, tmp_path):
+    """`max_batch_tokens` bounds a step; a larger batch is cut sequence by sequence (`MiniBatch.split`) and the rest of
+    a cut sequence continues from the cache.  Wanted places on both sides of a cut, given out of order."""
+    import mini_llama_cpp_release_b200 as ml
+    folder = model_folder("C")
+    pm = plain_model(folder)
+    reqs = {f"r{i}": random_tokens(n, 777, 300 + i) for i, n in enumerate([130, 7, 95, 64])}
+    want = {"r0": [129, 3, 70], "r1": [6], "r2": [], "r3": [0, 63]}
+    record = dict(step=0, entries=[dict(id=r, tokens=t, want=want[r]) for r, t in reqs.items()], end=list(reqs))
+    ref = torch.stack([pm.logits(reqs[r])[w] for r in reqs for w in want[r]])
+    for limit in (50, 64, 296, 10 ** 6):
+        llm = ml.load(folder, dtype=dtype, max_tokens=1024, max_batch_tokens=limit)
+        rp = Replayer(llm.context, str(tmp_path / f"o{limit}"))
+        got = rp.step(record)
+        check(got.cpu(), ref, dtype, f"pieces of at most {limit} tokens")
+        assert llm.context.n_steps == 1 and llm.context.cache.slots.n_held == 0
+    # too much for the cache: refused before any piece runs, nothing kept
+    from mini_llama_cpp_release_b200.cache import CacheFull
+    llm = ml.load(folder, dtype=dtype, max_tokens=256, max_batch_tokens=50)
+    with pytest.raises(CacheFull):
+        Replayer(llm.context, str(tmp_path / "small")).step(record)
+    assert llm.context.cache.slots.n_held == 0 and all(p.n_held == 0 for p in llm.context.cache.pages)
+
+
+def test_the_index_says_which_slot_and_positions_every_row_came_from(tmp_path):
+    folder = model_folder("A")
+    reqs = requests_of("A")
+    ids = list(reqs)
+    records, keys = batched_records(reqs, [ids[:3], ids[3:], ids[::-1][:3]])
+    replay(folder, "float32", records, tmp_path)
+    lines = [json.loads(l) for l in open(tmp_path / "out_float32" / "index.jsonl")]
+    assert len(lines) == sum(len(r["entries"]) for r in records)
+    by_req = {}
+    for l in lines:
+        by_req.setdefault(l["id"], []).append(l)
+    for rid, ls in by_req.items():
+        runs = []                                              # a request replayed again later starts again at position 0
+        for l in ls:
+            if l["positions"][0] == 0:
+                runs.append([])
+            runs[-1].append(l)
+        for run_ in runs:
+            assert len({l["slot"] for l in run_}) == 1                                  # one slot while it lives
+            assert all(a["positions"][1] == b["positions"][0] for a, b in zip(run_, run_[1:]))   # positions continue
+            assert run_[-1]["positions"][1] == len(reqs[rid])
+    # rows: the entries of a step share out its file's rows in order
+    for rec in records:
+        rows = [r for l in lines if l["step"] == rec["step"] for r in l["rows"]]
+        assert rows == list(range(sum(len(e["want"]) for e in rec["entries"])))
+    # the second batch took the slots the first gave back
+    first = {l["slot"] for l in lines if l["id"] in ids[:3] and l["step"] < records[len(records) // 3]["step"]}
+    later = {l["slot"] for l in lines if l["id"] in ids[3:]}
+    assert later & first
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_width_and_vocabulary_in_all_three_cuts(dtype, tmp_path):
+    """The layer sizes of a Qwen2-0.5B (width 896, 14 query heads on 2 kv heads of 64, feed-forward 4864, the full
+    vocabulary of 151,936, tied head) with 2 layers: whole, with the last 32 tokens one by one, and as a batch of
+    unequal lengths.  In 32-bit the logits agree with the plain implementation to 1e-4 absolute."""
+    import mini_llama_cpp_release_b200 as ml
+    from mini_llama_cpp_release_b200.measure import PRESETS
+    raw = dict(PRESETS["qwen2-0.5b"], num_hidden_layers=2, max_position_embeddings=2048)
+    folder = ml.write_random_model(ml.ModelConfig.from_dict(raw), str(tmp_path / "m"), 3)
+    pm = plain_model(folder)
+    vocab = raw["vocab_size"]
+    reqs = {f"r{i}": random_tokens(n, vocab, 700 + i) for i, n in enumerate([150, 1, 70, 40])}
+    ref = {rid: pm.logits(t) for rid, t in reqs.items()}
+    records, keys = [], []
+    step = 0
+    for rid, toks in reqs.items():                              # whole, only the last four places wanted (the head is wide)
+        want = list(range(max(0, len(toks) - 4), len(toks)))
+        records.append(dict(step=step, entries=[dict(id=rid, tokens=toks, want=want)], end=[rid]))
+        keys.append((step, [(rid, w) for w in want]))
+        step += 1
+    for rid, toks in reqs.items():                              # the last 32 one by one
+        if len(toks) <= 32:
+            continue
+        head = len(toks) - 32
+        records.append(dict(step=step, entries=[dict(id=rid, tokens=toks[:head], want=[head - 1])], end=[]))
+        keys.append((step, [(rid, head - 1)]))
+        step += 1
+        for j in range(head, len(toks)):
+            records.append(dict(step=step, entries=[dict(id=rid, tokens=[toks[j]], want=[0])], end=[rid] if j == len(toks) - 1 else []))
+            keys.append((step, [(rid, j)]))
+            step += 1
+    batch_records, batch_keys = batched_records(reqs, [list(reqs)], prompt_frac=0.8)
+    for r, (s, rows) in zip(batch_records, batch_keys):
+        r["step"] += step
+        keys.append((s + step, rows))
+    records += batch_records
+    llm = ml.load(folder, dtype=dtype, max_tokens=1024)
+    rp = Replayer(llm.context, str(tmp_path / "out"))
+    worst_abs = worst_rel = 0.0
+    for rec, (s, rows) in zip(records, keys):
+        got = rp.step(rec).cpu()
+        want = torch.stack([ref[rid][pos] for rid, pos in rows])
+        worst_abs = max(worst_abs, float((got - want).abs().max()))
+        worst_rel = max(worst_rel, max(rel_err(got[i], want[i]) for i in range(len(rows))))
+    assert worst_rel <= TOL[dtype], worst_rel
+    if dtype == "float32":
+        assert worst_abs <= 1e-4, worst_abs
+    llm.context.cache.check()
+    assert llm.context.cache.slots.n_held == 0
