@@ -130,7 +130,8 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
                     if int(time.time() - t0) % 10 == 0:
                         _say(f"  ... still compiling ({int(time.time() - t0)} s, {len(pending)} file(s) left)")
         tmp_out = os.path.join(work, "lib.so")
-        p = subprocess.run([nvcc, "-shared", "-o", tmp_out, *objs, "-lcudart"],
+        libs = ["-lcudart"]
+        p = subprocess.run([nvcc, "-shared", "-o", tmp_out, *objs, *libs],
                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if p.returncode != 0:
             raise BuildError(f"linking {name} failed:\n{p.stdout}")

@@ -508,10 +508,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // ------------------------------------------------------------------ host side
 // A row-major bfloat16 matrix [rows][cols] read in boxes of box_rows x 64 columns.
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)G_BK, (cuuint32_t)box_rows};
-    return make_tensor_map(map, ptr, 2, dims, strides, box);
+    return cached_map_2d(map, ptr, rows, cols, G_BK, box_rows);
 }
 
 template <int BN, int EPI>

@@ -18,8 +18,10 @@
 //   QKV       rows of each head alternate dim i, dim i + hd/2: adds the bias, rotates q and k by the token's
 //             position (src/ops.cpp:125-141), writes q as [token][head][hd] and k, v into the token's place in
 //             the paged cache (src/forward.cpp:553);
-//   ADD       adds y into a float32 [token][row] tensor, the residual stream (src/forward.cpp:772, 779); every
-//             element belongs to one thread, so these are plain reads and writes.
+//   ADD       adds y into a float32 [token][row] tensor, the residual stream (src/forward.cpp:772, 779).  Without a K
+//             split every element belongs to one thread and these are plain reads and writes; with one (the K range
+//             shared out over blocks, for products whose tiles alone would leave most SMs idle) they are 16-byte
+//             atomic adds, which also spare the read.
 //
 // Every wait on an mbarrier is bounded by a clock; a wait that runs out records a code in `status` (21 loader,
 // 22 tensor cores, 23 epilogue), the block skips its stores, frees its tensor memory and returns.
@@ -36,6 +38,8 @@ struct RowsArgs {
     int n_tok;
     int k_blocks;              // ceil(K / 64)
     int m_tiles, n_tiles;
+    int n_splits;              // blocks that share out a tile's K range (ADD only); 1: none
+    int k_blocks_per_split;
     int* status;
     // QKV epilogue
     const float* bias;         // [n_out] in the stored row order, or null
@@ -88,10 +92,12 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 20);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles_total = g.m_tiles * g.n_tiles;
+    const int n_tiles_total = g.m_tiles * g.n_tiles * g.n_splits;
     // consecutive blocks take the token tiles of one W tile: the W tile is fetched from memory once and then found in L2
     auto tile_m0 = [&](int t) { return (t % g.m_tiles) * R_BM; };
-    auto tile_n0 = [&](int t) { return (t / g.m_tiles) * BN; };
+    auto tile_n0 = [&](int t) { return ((t / g.m_tiles) % g.n_tiles) * BN; };
+    auto tile_kb0 = [&](int t) { return (t / (g.m_tiles * g.n_tiles)) * g.k_blocks_per_split; };       // first K block of the tile's share
+    auto tile_nkb = [&](int t) { return min(g.k_blocks, tile_kb0(t) + g.k_blocks_per_split) - tile_kb0(t); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) {
@@ -121,25 +127,25 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             int it = 0;
             bool alive = true;
             for (int t = blockIdx.x; t < n_tiles_total && alive; t += gridDim.x) {
-                const int m0 = tile_m0(t), n0 = tile_n0(t);
+                const int m0 = tile_m0(t), n0 = tile_n0(t), kb0 = tile_kb0(t), n_kb = tile_nkb(t);
                 int i = 0;
                 if (it == 0) {
-                    const int early = min(g.k_blocks, S::STAGES);
+                    const int early = min(n_kb, S::STAGES);
                     for (; i < early; ++i) {
                         mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
-                        tma_load_2d(b_base + i * S::B_BYTES, &map_w, i * R_BK, n0, full_bar(i));
+                        tma_load_2d(b_base + i * S::B_BYTES, &map_w, (kb0 + i) * R_BK, n0, full_bar(i));
                     }
                     grid_dependency_wait();
-                    for (int e = 0; e < early; ++e) tma_load_2d(a_base + e * R_A_BYTES, &map_x, e * R_BK, m0, full_bar(e));
+                    for (int e = 0; e < early; ++e) tma_load_2d(a_base + e * R_A_BYTES, &map_x, (kb0 + e) * R_BK, m0, full_bar(e));
                     it = early;
                 }
-                for (; i < g.k_blocks; ++i, ++it) {
+                for (; i < n_kb; ++i, ++it) {
                     const int s = it % S::STAGES;
                     const unsigned phase = (it / S::STAGES) & 1;
                     if (!mbar_wait(empty_bar(s), phase ^ 1u, g.status, 21)) { alive = false; break; }
                     mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
-                    tma_load_2d(a_base + s * R_A_BYTES, &map_x, i * R_BK, m0, full_bar(s));
-                    tma_load_2d(b_base + s * S::B_BYTES, &map_w, i * R_BK, n0, full_bar(s));
+                    tma_load_2d(a_base + s * R_A_BYTES, &map_x, (kb0 + i) * R_BK, m0, full_bar(s));
+                    tma_load_2d(b_base + s * S::B_BYTES, &map_w, (kb0 + i) * R_BK, n0, full_bar(s));
                 }
             }
         }
@@ -155,7 +161,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (!ok) break;
                 tcgen05_fence_after();
                 const unsigned d_tmem = tmem_base + (unsigned)(buf * BN);
-                for (int i = 0; i < g.k_blocks; ++i, ++it) {
+                const int n_kb = tile_nkb(t);
+                for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % S::STAGES;
                     const unsigned phase = (it / S::STAGES) & 1;
                     ok = mbar_wait(full_bar(s), phase, g.status, 22);
@@ -278,6 +285,11 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             for (int u = 0; u < 8; ++u)
                                 if (u < 4 || second) dst[u] = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
                         }
+                    } else if (EPI == R_EPI_ADD && g.n_splits > 1) {
+                        float4* dst = reinterpret_cast<float4*>((float*)g.out + (long long)tok * g.n_out + n);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (u < 4 || second) atomicAdd(dst + u, make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]));
                     } else if (EPI == R_EPI_ADD) {
                         float4* dst = reinterpret_cast<float4*>((float*)g.out + (long long)tok * g.n_out + n);
                         float4 old[8];
@@ -324,10 +336,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
 // A row-major bfloat16 matrix [rows][cols] read in boxes of box_rows x 64 columns.
 static int rows_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)R_BK, (cuuint32_t)box_rows};
-    return make_tensor_map(map, ptr, 2, dims, strides, box);
+    return cached_map_2d(map, ptr, rows, cols, R_BK, box_rows);
 }
 
 template <int BN, int EPI>
@@ -339,7 +348,7 @@ static int launch_rows(const CUtensorMap& mx, const CUtensorMap& mw, const RowsA
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const long long tiles = (long long)g.m_tiles * g.n_tiles;
+    const long long tiles = (long long)g.m_tiles * g.n_tiles * g.n_splits;
     const unsigned blocks = (unsigned)(tiles < n_sms ? tiles : n_sms);
     cudaError_t e = launch_pdl(gemm_rows_kernel<BN, EPI>, dim3(blocks), dim3(S::THREADS), (size_t)S::SMEM_BYTES, s, mx, mw, g);
     return e == cudaSuccess ? 0 : (int)e;
@@ -362,10 +371,11 @@ using namespace mlc;
 // x: bfloat16 [n_tok][K]; w: bfloat16 [n_out][K]; K a multiple of 8, n_out a multiple of 16, everything 16-byte
 // aligned.  block_rows: 128, 160, 192, 224 or 256 rows of W per tile.  epilogue 0: out [n_tok][n_out] float32 or bfloat16; 1: out
 // [n_tok][n_out/2]; 2: out = q [n_tok][q_heads*hd] bfloat16, k and v go to the bfloat16 cache (hd a multiple of 16; block_rows 128);
-// 3: adds into out, float32 [n_tok][n_out].  status: one int on the device, 0 before the call; a bounded wait that
+// 3: adds into out, float32 [n_tok][n_out]; n_splits > 1 (this epilogue only) shares the K range out over that many
+// blocks per tile, which then add atomically.  status: one int on the device, 0 before the call; a bounded wait that
 // ran out leaves 21 (loader), 22 (tensor cores) or 23 (epilogue) there.  n_sms: blocks to launch at most.
 extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, int out_dtype, int n_tok, int n_out, int K,
-                                     int block_rows, int epilogue, int* status, int n_sms, const float* bias,
+                                     int block_rows, int n_splits, int epilogue, int* status, int n_sms, const float* bias,
                                      const int* positions, const int* tok_seq, const void* rope_table, int rope_positions,
                                      int q_heads, int kv_heads, int hd, void* k_pool, void* v_pool, const int* page_table,
                                      long long entry_offset, int pages_per_seq, int page_size, void* stream) {
@@ -374,6 +384,7 @@ extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, in
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
     if (status == nullptr || n_sms < 1) return MLC_ERR_BAD_SIZE;
     if (epilogue == R_EPI_ADD && out_dtype != MLC_DTYPE_F32) return MLC_ERR_BAD_DTYPE;
+    if (n_splits < 1 || (n_splits > 1 && epilogue != R_EPI_ADD)) return MLC_ERR_BAD_SIZE;
     RowsArgs g{};
     g.out = out;
     g.out_dtype = out_dtype;
@@ -382,6 +393,9 @@ extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, in
     g.k_blocks = (K + R_BK - 1) / R_BK;
     g.m_tiles = (n_tok + R_BM - 1) / R_BM;
     g.n_tiles = (n_out + block_rows - 1) / block_rows;
+    g.n_splits = n_splits;
+    g.k_blocks_per_split = (g.k_blocks + n_splits - 1) / n_splits;
+    if ((long long)(n_splits - 1) * g.k_blocks_per_split >= g.k_blocks) return MLC_ERR_BAD_SIZE;   // an empty split
     g.status = status;
     if (epilogue == R_EPI_QKV) {
         if (out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;

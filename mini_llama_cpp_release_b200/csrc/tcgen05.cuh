@@ -8,6 +8,10 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <functional>
+#include <mutex>
+#include <unordered_map>
+
 namespace mlc {
 
 constexpr unsigned long long TC_WAIT_NS = 2000000000ull;     // a wait on a barrier gives up after two seconds
@@ -35,6 +39,9 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* st
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
         if ((spin & 63u) == 63u) {
+            // a wait that another thread, block or earlier kernel already gave up: what this one waits for will not
+            // come either, and a chain of kernels must not spend the full time in each of its waits
+            if (spin > 4096u && *reinterpret_cast<volatile int*>(status) != 0) return false;
             const unsigned long long now = global_ns();
             if (deadline == 0) deadline = now + TC_WAIT_NS;
             else if (now > deadline) {
@@ -61,6 +68,7 @@ __device__ __forceinline__ bool mbar_wait_polling(unsigned bar, unsigned parity,
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
         if ((spin & 1023u) == 1023u) {
+            if (spin > 65536u && *reinterpret_cast<volatile int*>(status) != 0) return false;
             const unsigned long long now = global_ns();
             if (deadline == 0) deadline = now + TC_WAIT_NS;
             else if (now > deadline) {
@@ -215,6 +223,48 @@ static int make_tensor_map(CUtensorMap* map, const void* ptr, int rank, const cu
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : MLC_ERR_BAD_SIZE;
+}
+
+// The map of a row-major bfloat16 matrix [rows][cols] read in boxes of box_rows x box_cols, remembered by what defines
+// it: a step launches hundreds of products over the same weights, and its scratch tensors come back at the same
+// addresses step after step, so the driver is asked once per matrix, not once per launch.
+static int cached_map_2d(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_cols, int box_rows) {
+    struct Key {
+        const void* ptr;
+        long long rows, cols;
+        int box_cols, box_rows;
+        bool operator==(const Key& o) const {
+            return ptr == o.ptr && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows;
+        }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const {
+            size_t h = std::hash<const void*>()(k.ptr);
+            h = h * 1000003u ^ std::hash<long long>()(k.rows * 131 + k.cols);
+            return h * 1000003u ^ std::hash<int>()(k.box_cols * 1024 + k.box_rows);
+        }
+    };
+    static std::unordered_map<Key, CUtensorMap, Hash> cache;
+    static std::mutex lock;
+    const Key key{ptr, rows, cols, box_cols, box_rows};
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *map = it->second;
+            return 0;
+        }
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const int rc = make_tensor_map(map, ptr, 2, dims, strides, box);
+    if (rc == 0) {
+        std::lock_guard<std::mutex> guard(lock);
+        if (cache.size() > 8192) cache.clear();
+        cache.emplace(key, *map);
+    }
+    return rc;
 }
 
 }  // namespace mlc

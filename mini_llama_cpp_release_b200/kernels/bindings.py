@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_decode_stamps", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_decode_stamps", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -95,7 +95,7 @@ def core() -> ctypes.CDLL:
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
-            "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
+            "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
@@ -472,6 +472,24 @@ EPI_STORE, EPI_SILU_MUL, EPI_QKV, EPI_ADD = 0, 1, 2, 3
 _status = {}
 
 
+def library_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out [n, rows] (float32 or bfloat16) = x [n, K] · w [rows, K]ᵀ, added to `out` if `accumulate`: the library's
+    (cuBLAS's, through PyTorch) product with float32 accumulation, for the bfloat16 products whose sizes this
+    package's tcgen05 kernels do not take (an inner size that is no multiple of 8, a row count that is no multiple of
+    16 in a prompt).  The reference's engine calls cuBLAS for all of its linear layers (src/cuda_matmul.cpp:216-233).
+    Counted apart from this package's own kernels."""
+    require_cuda(x, w, out)
+    if accumulate and out.dtype == torch.float32:
+        torch.addmm(out, x, w.t(), out_dtype=torch.float32, out=out)
+    elif accumulate:
+        out.add_(torch.mm(x, w.t()))
+    elif out.dtype == torch.float32:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        torch.mm(x, w.t(), out=out)
+    count_library_launches(1)
+
+
 def gemm_status(device: torch.device) -> torch.Tensor:
     """One int32 per device that the tensor-core kernels leave non-zero when a bounded wait ran out."""
     key = torch.device(device).index or 0
@@ -533,8 +551,33 @@ def gemm_rows_block(n_tok: int, n_out: int, n_sms: int) -> int:
     return best
 
 
+def gemm_rows_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):
+    """(rows of W per tile, K splits) for a prompt product that adds into the stream.  Such products (the output and down
+    projections) have few columns, so their tiles alone leave SMs idle: the K range is then shared out over several
+    blocks per tile, which add atomically.  The cost of a plan is its number of rounds of `n_sms` blocks times what a
+    block does per round: its K steps and a fixed part for filling the pipeline and writing the tile out (the
+    constants are fitted to measurements on a B200 at 2,048 tokens: 896 x 896, 896 x 4,864 and 1,536 x 8,960)."""
+    m_tiles = (n_tok + 127) // 128
+    k_blocks = (k + 63) // 64
+    best, best_cost = (128, 1), None
+    for bn in (128, 160, 192, 224, 256):
+        tiles = m_tiles * ((n_out + bn - 1) // bn)
+        step = 2.6 * bn + 380.0                                               # clocks per K step
+        fixed = 9000.0 + 20.0 * bn                                            # clocks per tile
+        for splits in (1, 2, 3, 4, 6, 8):
+            per = (k_blocks + splits - 1) // splits
+            real = (k_blocks + per - 1) // per
+            if real != splits or (splits > 1 and per < 4):
+                continue
+            rounds = (tiles * splits + n_sms - 1) // n_sms
+            cost = rounds * (per * step + fixed)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = (bn, splits), cost
+    return best
+
+
 def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0,
-                      block_rows: Optional[int] = None, bias: Optional[torch.Tensor] = None,
+                      block_rows: Optional[int] = None, n_splits: Optional[int] = None, bias: Optional[torch.Tensor] = None,
                       positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
                       rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
                       kv: Optional[KVView] = None, n_sms: int = 0) -> None:
@@ -553,8 +596,12 @@ def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
     if K % 8 or n_out % 16:
         raise KernelError(f"the prompt form of the tcgen05 product needs an inner size that is a multiple of 8 and "
                           f"a multiple of 16 rows, got {K} and {n_out}")
+    if epilogue == EPI_ADD and block_rows is None and n_splits is None:
+        block_rows, n_splits = gemm_rows_add_plan(n_tok, n_out, K, n_sms)
     if block_rows is None:
         block_rows = 128 if epilogue == EPI_QKV else gemm_rows_block(n_tok, n_out, n_sms)
+    if n_splits is None:
+        n_splits = 1
     if epilogue == EPI_STORE:
         assert out.numel() == n_tok * n_out
     elif epilogue == EPI_ADD:
@@ -571,7 +618,7 @@ def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
         cache = (None, None, None, 0, 0, 1)
     status = gemm_status(x.device)
     _check(core().mlc_gemm_tcgen05_rows(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
-                                        block_rows, epilogue, status.data_ptr(), n_sms, _ptr(bias), _ptr(positions),
+                                        block_rows, n_splits, epilogue, status.data_ptr(), n_sms, _ptr(bias), _ptr(positions),
                                         _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
                                         kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product (prompt form)")
 

@@ -9,10 +9,14 @@ Which kernel runs is decided by the operand types and sizes, never by the model:
     csrc/gemm_tcgen05.cu, always when an epilogue is fused (Q/K/V with bias, rotation and
     cache write; gate/up with SiLU·mul), and for plain products of up to 64 rows (decoding),
     where the K range is split over blocks and the partial sums are left to the consumer.
-  * plain bfloat16 products of more rows (prompts): the library's tensor-core product with
-    float32 accumulation, as the reference calls cuBLAS for its linears
-    (src/cuda_matmul.cpp:216-233); where the product is a branch's last, it adds into the
-    float32 residual stream in the same call.
+  * plain bfloat16 products of more rows (prompts): the tokens-as-M tcgen05 kernel of
+    csrc/gemm_tcgen05_rows.cu; where the product is a branch's last it adds into the float32
+    residual stream in its epilogue, with the K range shared out over blocks when the tiles
+    alone would leave SMs idle.
+  * bfloat16 products whose sizes those kernels do not take (an inner size that is no
+    multiple of 8; in a prompt, a row count of W that is no multiple of 16): the library's
+    product with float32 accumulation, as the reference calls cuBLAS for all of its linears
+    (src/cuda_matmul.cpp:216-233).
 """
 from __future__ import annotations
 
@@ -53,18 +57,22 @@ class Linear:
         return self.weight.numel() * self.weight.element_size()
 
     def can_add_into_stream(self, n_rows: int) -> bool:
-        """Whether `add_into` has a kernel for these operands: the tcgen05 product with atomic adds for few rows, the
-        library's product with the stream as the matrix it adds to for more."""
+        """Whether `add_into` has a kernel for these operands: the tcgen05 products (atomic adds for few rows; plain or
+        atomic adds for more), else the library's product with the stream as the matrix it adds to."""
         return self.tensor_core_ok
 
     def add_into(self, x: torch.Tensor, stream: torch.Tensor) -> None:
-        """stream (float32 [n, out]) += x · Wᵀ.  Few rows: the K range shared out over as many blocks as is useful.
-        More rows: the library's product reads and writes the stream in its epilogue, so the norm that follows has one
-        tensor to read, not two."""
+        """stream (float32 [n, out]) += x · Wᵀ.  Few rows: the weights-as-M tcgen05 product, the K range shared out over
+        as many blocks as is useful.  More rows: the tokens-as-M tcgen05 product, with a K split when its tiles alone
+        would leave SMs idle (the library's product only for a row count that kernel does not take: no multiple of
+        16).  Either way the stream is updated in the product's epilogue, so the norm that follows has one tensor to
+        read, not two."""
         m = x.shape[0]
+        if m > SMALL_BATCH and kernels.gemm_rows_takes(m, self.out_features, self.in_features):
+            kernels.gemm_tcgen05_rows(x, self.weight, stream, kernels.bindings.EPI_ADD, n_sms=self.runtime.n_sms)
+            return
         if m > SMALL_BATCH:
-            torch.addmm(stream, x, self.weight.t(), out_dtype=torch.float32, out=stream)
-            kernels.count_library_launches(1)
+            kernels.library_gemm(x, self.weight, stream, accumulate=True)
             return
         splits = split_count(self.out_features, self.in_features, m, self.runtime.n_sms, max_splits=ADD_MAX_SPLITS)
         kernels.gemm_tcgen05(x, self.weight, stream, kernels.bindings.EPI_ADD, splits, n_sms=self.runtime.n_sms)
@@ -86,9 +94,8 @@ class Linear:
             kernels.gemm_tcgen05(x, self.weight, out, kernels.bindings.EPI_STORE, splits, n_sms=rt.n_sms)
             return out if splits > 1 else out[0]
         out = rt.empty(m, self.out_features, dtype=out_dtype)
-        if out.dtype == torch.float32:
-            torch.mm(x, self.weight.t(), out_dtype=torch.float32, out=out)
+        if self.tensor_core_ok and kernels.gemm_rows_takes(m, self.out_features, self.in_features):
+            kernels.gemm_tcgen05_rows(x, self.weight, out, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
         else:
-            torch.mm(x, self.weight.t(), out=out)
-        kernels.count_library_launches(1)
+            kernels.library_gemm(x, self.weight, out)
         return out

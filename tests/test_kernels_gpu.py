@@ -423,17 +423,33 @@ def test_prompt_product_with_bias_rotation_and_cache_write(H, KV, hd, T, bn):
     assert torch.isnan(kv.k_pool[0].float()).all()
 
 
-@pytest.mark.parametrize("T,N,K,bn", [(128, 896, 4864, None), (70, 144, 896, 128), (300, 272, 1000, 256), (300, 464, 200, 224)])
-def test_prompt_product_adding_into_the_stream(T, N, K, bn):
+@pytest.mark.parametrize("T,N,K,bn,splits", [(128, 896, 4864, None, None), (70, 144, 896, 128, 1), (300, 272, 1000, 256, 1),
+                                              (300, 464, 200, 224, 1), (2048, 896, 896, None, None), (300, 272, 1000, 160, 3),
+                                              (129, 48, 4864, 128, 8), (1000, 896, 4864, 224, 5), (70, 144, 520, 128, 2)])
+def test_prompt_product_adding_into_the_stream(T, N, K, bn, splits):
+    """Without a K split plain reads and writes; with one (given, or chosen by the plan when the tiles alone would leave
+    SMs idle) 16-byte atomic adds.  A last split shorter than the others, tiles beyond the matrix's edge in both
+    directions, more tiles than blocks."""
     g = torch.Generator().manual_seed(N + K)
     x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
     stream0 = torch.randn(T, N, generator=g)
     stream = stream0.clone().to(DEV)
-    kernels.gemm_tcgen05_rows(x.to(DEV), w.to(DEV), stream, 3, bn)
+    kernels.gemm_tcgen05_rows(x.to(DEV), w.to(DEV), stream, 3, bn, splits)
     kernels.check_gemm_status(DEV)
-    # one float32 accumulator runs over all K terms here (no K splits): rounding grows like sqrt(K) * 2^-24
+    # float32 accumulators over the K terms: rounding grows like sqrt(K) * 2^-24
     close(stream, stream0.double() + x.double() @ w.double().t(), 3 * math.sqrt(K) * 2.0 ** -24)
+
+
+def test_prompt_product_shares_out_the_k_range_when_its_tiles_are_few():
+    assert kernels.gemm_rows_add_plan(2048, 896, 4864, 148)[1] > 1            # 64 tiles on 148 SMs
+    assert kernels.gemm_rows_add_plan(65536, 896, 4864, 148)[1] == 1          # tiles enough
+    assert kernels.gemm_rows_add_plan(128, 64, 176, 148) == (128, 1)          # three K steps: nothing to share
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(kernels.KernelError, match="size"):                     # a K split is for the adding epilogue only
+        kernels.gemm_tcgen05_rows(x, torch.zeros(48, 64, dtype=torch.bfloat16, device=DEV), torch.empty(128, 48, device=DEV), 0, 128, 2)
+    with pytest.raises(kernels.KernelError, match="size"):                     # an empty split
+        kernels.gemm_tcgen05_rows(x, torch.zeros(48, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(128, 48, device=DEV), 3, 128, 2)
 
 
 def test_prompt_product_refuses_what_it_cannot_take():

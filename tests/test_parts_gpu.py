@@ -13,7 +13,7 @@ from mini_llama_cpp_release_b200.config import ModelConfig, PartSpec, ScheduleEn
 from mini_llama_cpp_release_b200.config.specs import ModelSpec
 from mini_llama_cpp_release_b200.engine import Context, MiniBatch, Model
 from mini_llama_cpp_release_b200.engine.batch import SequenceChunk
-from mini_llama_cpp_release_b200.models.qwen2 import qwen2
+from mini_llama_cpp_release_b200.models.qwen2 import Qwen2Config, qwen2
 from mini_llama_cpp_release_b200.parts import MixerMemory, Runtime
 from mini_llama_cpp_release_b200.weights.random_init import random_tensor
 
@@ -176,7 +176,7 @@ def plain_twice_and_shared(cfg, w, tokens):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_schedule_runs_a_layer_twice_and_shares_a_cache(dtype, tmp_path):
     import mini_llama_cpp_release_b200 as ml
-    register_architecture("TwiceAndShared")(twice_and_shared)
+    register_architecture("TwiceAndShared", config_class=Qwen2Config)(twice_and_shared)      # Qwen2's keys, another schedule
     raw = dict(helpers.TINY_A, architectures=["TwiceAndShared"])
     folder = ml.write_random_model(ModelConfig.from_dict(raw), str(tmp_path / "m"), 3, std=0.1)
     llm = ml.load(folder, dtype=dtype, max_tokens=1024)
