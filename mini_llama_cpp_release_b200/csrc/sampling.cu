@@ -163,7 +163,7 @@ __device__ __forceinline__ int block_scan_int(int v, int* scratch, int* total) {
 // contiguous run of ids so that prefix sums follow the index order.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int vocab, float temperature,
-                          unsigned long long seed, const int* __restrict__ seq_ids,
+                          unsigned long long seed, const unsigned long long* __restrict__ seed_ptr, const int* __restrict__ seq_ids,
                           const int* __restrict__ positions, int* __restrict__ out) {
     __shared__ float fscratch[32];
     __shared__ int first_thread;
@@ -178,7 +178,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, float tem
     for (int i = begin; i < end; ++i) mine += expf((row[i] - mx) / temperature);
     float total;
     const float incl = block_scan(mine, fscratch, &total);
-    const float r = uniform_of(seed, seq_ids[blockIdx.x], positions[blockIdx.x]);
+    const float r = uniform_of(seed_ptr != nullptr ? *seed_ptr : seed, seq_ids[blockIdx.x], positions[blockIdx.x]);
     const float target = r * total;
     if (threadIdx.x == 0) first_thread = 0x7fffffff;
     __syncthreads();
@@ -212,7 +212,7 @@ __device__ __forceinline__ unsigned int float_key(float f) {
 // threshold by lowest id), sort them by (logit descending, id ascending), walk.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_top_k_kernel(const float* __restrict__ logits, int vocab, float temperature, int top_k,
-                    unsigned long long seed, const int* __restrict__ seq_ids,
+                    unsigned long long seed, const unsigned long long* __restrict__ seed_ptr, const int* __restrict__ seq_ids,
                     const int* __restrict__ positions, int* __restrict__ out) {
     __shared__ unsigned int hist[256];
     __shared__ float cand_v[TOPK_MAX];
@@ -318,7 +318,7 @@ sample_top_k_kernel(const float* __restrict__ logits, int vocab, float temperatu
     const float w = (t < k) ? expf((cand_v[t] - mx) / temperature) : 0.0f;
     float total;
     const float incl = block_scan(w, fscratch, &total);
-    const float r = uniform_of(seed, seq_ids[blockIdx.x], positions[blockIdx.x]);
+    const float r = uniform_of(seed_ptr != nullptr ? *seed_ptr : seed, seq_ids[blockIdx.x], positions[blockIdx.x]);
     const float target = r * total;
     if (threadIdx.x == 0) first_slot = k - 1;
     __syncthreads();
@@ -351,19 +351,21 @@ extern "C" int mlc_argmax_split(const float* logits, int rows, int vocab, int* o
     return e == cudaSuccess ? 0 : (int)e;
 }
 
+// seed_ptr: null, or where on the device the seed stands (8-byte aligned): it is then read at every launch, so a
+// captured launch serves any seed.
 extern "C" int mlc_sample(const float* logits, int rows, int vocab, float temperature, int top_k,
-                          unsigned long long seed, const int* seq_ids, const int* positions, int* out,
-                          void* stream) {
+                          unsigned long long seed, const unsigned long long* seed_ptr, const int* seq_ids,
+                          const int* positions, int* out, void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || !(temperature > 0.0f) || top_k < 0 || top_k == 1) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (top_k == 0) {
-        sample_temperature_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, vocab, temperature, seed, seq_ids,
+        sample_temperature_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, vocab, temperature, seed, seed_ptr, seq_ids,
                                                                   positions, out);
     } else {
         const int k = top_k < vocab ? top_k : vocab;
         if (k > TOPK_MAX) return MLC_ERR_UNSUPPORTED;
-        sample_top_k_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, vocab, temperature, top_k, seed, seq_ids,
+        sample_top_k_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, vocab, temperature, top_k, seed, seed_ptr, seq_ids,
                                                             positions, out);
     }
     MLC_LAUNCH_CHECK();

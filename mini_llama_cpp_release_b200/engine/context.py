@@ -16,7 +16,7 @@ import torch
 from .. import kernels
 from ..cache.paged import PAGE_SIZE, PagedCache
 from .batch import MiniBatch, SequenceChunk
-from .decode_runner import DecodeRunner
+from .decode_runner import DecodeRunner, padded_batch
 from .model import Model
 from .step_info import StepInfo
 
@@ -264,13 +264,18 @@ class Context:
             bucket *= 2
         bucket = min(bucket, max(need_len, self.max_position))
         p = sampler.params
-        key = (n_seqs, bucket, p.greedy) if p.greedy else (n_seqs, bucket, p.temperature, p.top_k, sampler.seed)
+        # the rows of the captured step: the batch's size rounded up to one of a few (the spare rows repeat a sequence,
+        # which is only sound while no mixer keeps state of its own); the seed is data in the runner's buffer
+        rows = n_seqs if self.cache.has_state else padded_batch(n_seqs)
+        key = (rows, bucket, p.greedy) if p.greedy else (rows, bucket, p.temperature, p.top_k)
         runner = self._runners.get(key)
         if runner is None:
-            if len(self._runners) >= 12:
+            if len(self._runners) >= 24:
                 self._runners.pop(next(iter(self._runners)))
-            runner = DecodeRunner(self, n_seqs, bucket, sampler)
+            runner = DecodeRunner(self, rows, bucket, sampler)
             self._runners[key] = runner
+        else:
+            self._runners[key] = self._runners.pop(key)            # most recently used last
         return runner
 
     def _check_decode(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int) -> None:
@@ -302,25 +307,25 @@ class Context:
         runner = self._runner(len(slots), max(lengths) + 1, sampler)
         h2d = 0
         if runner.graph is None:
-            runner.load(slots, tokens, seq_ids)
+            runner.load(slots, tokens, seq_ids, sampler.seed)
             runner.capture()
             runner.loaded_slots = None
-        if runner.loaded_slots != slots or runner.loaded_ids != list(seq_ids):
-            runner.load(slots, tokens, seq_ids)
-            runner.loaded_ids = list(seq_ids)
+        if runner.loaded_slots != slots or runner.loaded_ids != list(seq_ids) or runner.loaded_seed != sampler.seed:
+            runner.load(slots, tokens, seq_ids, sampler.seed)
             h2d += runner.host_buf.numel() * 4
         else:
             h2d += runner.load_step(tokens, lengths)
             h2d += runner.refresh_pages(slots)
         runner.replay()
         chosen = runner.read_chosen()
+        logits = runner.logits[:len(slots)]
         history = self.token_history
         for s, t in zip(slots, tokens):
             cache.commit(s, 1)
             history[s].append(int(t))
         self.n_steps += 1
         self.last_copy_bytes = (h2d, 4 * len(slots))
-        return chosen, runner.logits
+        return chosen, logits
 
     def decode_on_device(self, slots: Sequence[int], tokens: Sequence[int], sampler, seq_ids: Sequence[int],
                          n_steps: int, before=None, after=None) -> torch.Tensor:
@@ -336,9 +341,9 @@ class Context:
                 self.cache.reserve(s, n_steps)
             runner = self._runner(len(slots), max(self.cache.length[s] for s in slots) + n_steps, sampler)
             if runner.graph is None:
-                runner.load(slots, tokens, seq_ids)
+                runner.load(slots, tokens, seq_ids, sampler.seed)
                 runner.capture()
-            runner.load(slots, tokens, seq_ids)
+            runner.load(slots, tokens, seq_ids, sampler.seed)
             runner.loaded_slots = None                 # the buffers will not describe a host-known state afterwards
             if before is not None:
                 before()
@@ -346,7 +351,7 @@ class Context:
                 runner.replay()
             if after is not None:
                 after()
-            out = runner.history[:n_steps].clone()
+            out = runner.history[:n_steps, :len(slots)].clone()
         for s in slots:
             self.cache.commit(s, n_steps)
         self.n_steps += n_steps

@@ -30,9 +30,24 @@ def _round_up_pow2(n: int) -> int:
     return p
 
 
+BATCH_SIZES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+def padded_batch(n: int) -> int:
+    """The batch size a captured step is made for when `n` sequences decode: a batch that shrinks one sequence at a
+    time then goes through a dozen captured graphs, not one per size."""
+    for b in BATCH_SIZES:
+        if n <= b:
+            return b
+    return (n + 63) // 64 * 64
+
+
 class DecodeRunner:
-    """Buffers and graph for `n_seqs` sequences decoding together, valid while no sequence
-    grows beyond `max_len` tokens."""
+    """Buffers and graph for `n_seqs` rows decoding together, valid while no sequence grows beyond `max_len` tokens.
+    A batch of fewer sequences fills the remaining rows with copies of its last one: a copy computes the same
+    values from the same inputs and writes the same keys and values to the same places, so it changes no result; its
+    chosen token is dropped.  (A mixer that keeps state could not tell a copy from a second step, so models with
+    state get a runner of the batch's exact size.)  The sampler's seed stands in the buffer, not in the graph."""
 
     HISTORY_STEPS = 1024
 
@@ -51,7 +66,7 @@ class DecodeRunner:
         # one int32 buffer; the per-step inputs come first so that one copy brings them
         names = [("tokens", B), ("positions", B), ("start_pos", B), ("sample_pos", B),
                  ("tok_seq", B), ("cu_seqlens", B + 1), ("slots", B), ("want_rows", B), ("seq_ids", B), ("chosen", B),
-                 ("counter", 1)] + [(f"pages{g}", B * self.pages_per_seq) for g in range(n_groups)]
+                 ("counter", 1), ("seed", 2)] + [(f"pages{g}", B * self.pages_per_seq) for g in range(n_groups)]
         self.offsets = {}
         total = 0
         for name, n in names:
@@ -77,6 +92,8 @@ class DecodeRunner:
         self.launches_per_step = 0
         self.loaded_slots: Optional[List[int]] = None
         self.loaded_ids: Optional[List[int]] = None
+        self.loaded_seed: Optional[int] = None
+        self.n_live = n_seqs                                        # rows that are sequences of their own, not copies
         self.page_versions: Optional[List[int]] = None            # `SlotBook.page_version` of each slot when its pages were copied
 
     # ------------------------------------------------------------------ buffers
@@ -100,7 +117,8 @@ class DecodeRunner:
     def _body(self) -> None:
         step = self.step_info()
         self.logits = self.model.forward(step, self.cache)
-        self.sampler.sample_device(self.logits, self.view("seq_ids"), self.view("sample_pos"), out=self.view("chosen"))
+        self.sampler.sample_device(self.logits, self.view("seq_ids"), self.view("sample_pos"), out=self.view("chosen"),
+                                   seed_on_device=self.view("seed"))
         kernels.decode_advance(self.view("chosen"), self.view("tokens"), self.view("positions"), self.view("start_pos"),
                                self.view("sample_pos"), self.history, self.view("counter"))
 
@@ -127,11 +145,19 @@ class DecodeRunner:
         torch.cuda.synchronize(dev)
 
     # ------------------------------------------------------------------ loading a batch
-    def load(self, slots: Sequence[int], tokens: Sequence[int], seq_ids: Sequence[int]) -> None:
-        """Everything about the batch: called when the set of sequences changes."""
+    def load(self, slots: Sequence[int], tokens: Sequence[int], seq_ids: Sequence[int], seed: Optional[int] = None) -> None:
+        """Everything about the batch: called when the set of sequences (or the seed) changes.  Fewer sequences than
+        rows: the last one is repeated."""
         B = self.B
-        assert len(slots) == B
+        self.n_live = len(slots)
+        assert 0 < self.n_live <= B
+        pad = B - self.n_live
+        slots, tokens, seq_ids = (list(v) + [v[-1]] * pad for v in (slots, tokens, seq_ids))
+        seed = self.sampler.seed if seed is None else seed
         h = self.host_view
+        h("seed")[0] = (seed & 0xFFFFFFFF) - (1 << 32 if seed & 0x80000000 else 0)
+        h("seed")[1] = ((seed >> 32) & 0xFFFFFFFF) - (1 << 32 if (seed >> 32) & 0x80000000 else 0)
+        self.loaded_seed = seed
         lengths = [self.cache.length[s] for s in slots]
         h("tokens")[:] = torch.tensor(list(tokens), dtype=torch.int32)
         h("positions")[:] = torch.tensor(lengths, dtype=torch.int32)
@@ -144,7 +170,9 @@ class DecodeRunner:
         self.dev_buf.copy_(self.host_buf, non_blocking=True)
         if self.cache.has_state:
             self.slots_long.copy_(h("slots").long(), non_blocking=True)
-        self.loaded_slots = list(slots)
+        self.loaded_slots = list(slots[:self.n_live])
+        self.loaded_ids = list(seq_ids[:self.n_live])
+        self._padded_slots = list(slots)
 
     def _fill_pages(self, slots: Sequence[int]) -> None:
         P = self.pages_per_seq
@@ -162,6 +190,7 @@ class DecodeRunner:
         """Copy the page tables again if any sequence's pages are not the ones copied last (it got or lost a page, or
         its slot was given back and taken again by another sequence); returns bytes copied."""
         version = self.cache.page_version
+        slots = self._padded_slots
         if self.page_versions == [version[s] for s in slots]:
             return 0
         self._fill_pages(slots)
@@ -175,6 +204,9 @@ class DecodeRunner:
     def load_step(self, tokens: Sequence[int], lengths: Sequence[int]) -> int:
         """The per-step inputs from the host: tokens and positions.  Returns bytes copied."""
         B = self.B
+        pad = B - self.n_live
+        if pad:
+            tokens, lengths = list(tokens) + [tokens[-1]] * pad, list(lengths) + [lengths[-1]] * pad
         np_buf = self.host_np
         o_tok, o_pos, o_start, o_samp = (self.offsets[n][0] for n in ("tokens", "positions", "start_pos", "sample_pos"))
         np_buf[o_tok:o_tok + B] = tokens
@@ -197,4 +229,4 @@ class DecodeRunner:
         self.reads = getattr(self, "reads", 0) + 1
         if self.reads % 64 == 1:
             kernels.check_gemm_status(self.model.runtime.device)
-        return self.chosen_host.tolist()
+        return self.chosen_host[:self.n_live].tolist()

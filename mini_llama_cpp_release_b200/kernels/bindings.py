@@ -98,7 +98,7 @@ def core() -> ctypes.CDLL:
             "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
-            "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P],
+            "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P, P],
             "mlc_decode_advance": [P, I, P, P, P, P, P, P, I, P],
         }
         for name, args in sigs.items():
@@ -286,14 +286,19 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, seq_ids: torch.Tensor,
-           positions: torch.Tensor, out: torch.Tensor) -> None:
-    require_cuda(logits, seq_ids, positions, out)
+           positions: torch.Tensor, out: torch.Tensor, seed_on_device: Optional[torch.Tensor] = None) -> None:
+    """`seed_on_device`: two int32 (the seed's low and high half, 8-byte aligned) that the kernel reads instead of
+    `seed`, so that a captured launch serves whatever seed stands there when it is replayed."""
+    require_cuda(logits, seq_ids, positions, out, seed_on_device)
+    assert seed_on_device is None or (seed_on_device.dtype == torch.int32 and seed_on_device.numel() == 2
+                                      and seed_on_device.data_ptr() % 8 == 0)
     assert logits.dtype == torch.float32 and out.dtype == torch.int32
     rows, vocab = logits.shape
     if top_k > 1 and min(top_k, vocab) > 1024:
         raise KernelError(f"top-k sampling on the device keeps at most 1024 candidates; got top_k={top_k}")
     _check(core().mlc_sample(logits.data_ptr(), rows, vocab, float(temperature), int(top_k), int(seed) & (2**64 - 1),
-                             seq_ids.data_ptr(), positions.data_ptr(), out.data_ptr(), _stream()), "sampling")
+                             _ptr(seed_on_device), seq_ids.data_ptr(), positions.data_ptr(), out.data_ptr(), _stream()),
+           "sampling")
 
 
 def decode_advance(chosen: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, start_pos: torch.Tensor,

@@ -90,15 +90,16 @@ class DeviceSampler:
         self.device = device
 
     def sample_device(self, logits: torch.Tensor, seq_ids: torch.Tensor, positions: torch.Tensor,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """int32 ids [rows] on the device; seq_ids and positions are int32 device tensors."""
+                      out: Optional[torch.Tensor] = None, seed_on_device: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """int32 ids [rows] on the device; seq_ids and positions are int32 device tensors.  `seed_on_device`
+        (two int32: the seed's halves), if given, is read by the kernel in place of this sampler's seed."""
         if out is None:
             out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
         p = self.params
         if p.greedy:
             self.kernels.argmax(logits, out)
         else:
-            self.kernels.sample(logits, p.temperature, p.top_k, self.seed, seq_ids, positions, out)
+            self.kernels.sample(logits, p.temperature, p.top_k, self.seed, seq_ids, positions, out, seed_on_device)
         return out
 
     def sample(self, logits: torch.Tensor, seq_ids: Sequence[int], positions: Sequence[int]) -> List[int]:

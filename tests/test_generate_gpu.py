@@ -272,3 +272,57 @@ def test_sampled_ids_are_the_plain_samplers_on_the_plain_logits():
                 assert abs(tok - want) == 1 and abs(float(cum[min(tok, want)]) - r) < 2e-5, (i, k, tok, want)
                 near += 1
     assert near <= 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_batch_between_two_captured_sizes_is_padded_with_copies_that_change_nothing(dtype):
+    """Captured decode steps exist for a few batch sizes (`decode_runner.BATCH_SIZES`); five sequences run in a step of
+    six rows whose last row repeats the fifth sequence.  Every step's logits against the plain implementation, while the
+    batch shrinks from five to one."""
+    from mini_llama_cpp_release_b200.engine.decode_runner import BATCH_SIZES, padded_batch
+    assert [padded_batch(n) for n in (1, 2, 3, 5, 7, 9, 33, 64, 65, 300)] == [1, 2, 3, 6, 8, 12, 48, 64, 96, 320]
+    folder = model_folder("C")
+    pm = plain_model(folder)
+    llm = helpers.engine(folder, dtype)
+    prompts = [random_tokens(n, 777, 600 + n) for n in (70, 3, 20, 64, 9)]
+    counts = [6, 9, 12, 15, 18]
+    seen, used = [], set()
+    ctx, make_runner = llm.context, llm.context._runner
+
+    def spy(n_seqs, need_len, sampler):
+        runner = make_runner(n_seqs, need_len, sampler)
+        used.add((n_seqs, runner.B))
+        return runner
+    ctx._runner = spy
+    try:
+        out = llm.generate(prompts, n_predict=counts, temperature=1.0, seed=3, stop_token_ids=[],
+                           on_step=lambda live, chosen, logits: seen.append((list(live), logits.float().cpu().clone())))
+    finally:
+        del ctx._runner
+    assert [len(o) for o in out] == counts
+    assert used == {(5, 6), (4, 4), (3, 3), (2, 2), (1, 1)} and all(b in BATCH_SIZES for _, b in used)
+    refs = [pm.logits(p + o) for p, o in zip(prompts, out)]
+    for step, (live, logits) in enumerate(seen):
+        assert logits.shape[0] == len(live)
+        for row, i in enumerate(live):
+            assert rel_err(logits[row], refs[i][len(prompts[i]) - 1 + step]) <= TOL[dtype], (step, i)
+    ctx.cache.check()
+    assert ctx.cache.slots.n_held == 0
+
+
+def test_the_seed_is_data_of_the_captured_step_not_part_of_it():
+    folder = model_folder("B", std=0.1)
+    llm = helpers.engine(folder, "float32")
+    prompts = [random_tokens(n, 1000, 90 + n) for n in (4, 17)]
+    first = llm.generate(prompts, n_predict=12, temperature=0.9, seed=11, stop_token_ids=[])
+    n_runners = len(llm.context._runners)
+    others = [llm.generate(prompts, n_predict=12, temperature=0.9, seed=s, stop_token_ids=[]) for s in (12, 2 ** 40 + 5, 0, 0)]
+    assert len(llm.context._runners) == n_runners                   # no graph captured for a new seed
+    assert llm.generate(prompts, n_predict=12, temperature=0.9, seed=11, stop_token_ids=[]) == first
+    assert all(o != first for o in others) and others[2] != others[3]    # seed 0: a fresh seed each time
+    # and the ids are the host sampler's for that seed
+    from mini_llama_cpp_release_b200.sampling import HostSampler, SamplingParams
+    from mini_llama_cpp_release_b200.engine.generate import generate
+    big = 2 ** 40 + 5
+    host = generate(llm.context, HostSampler(SamplingParams(0.9, 0, big)), prompts, 12, [])
+    assert sum(a == b for h, o in zip(host, others[1]) for a, b in zip(h.tokens, o)) >= 22     # a draw on a boundary may differ
