@@ -92,7 +92,7 @@ def core() -> ctypes.CDLL:
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
             "mlc_convert": [P, I, LL, P, I, P],
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
-            "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P],
+            "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P, LL, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
@@ -105,6 +105,8 @@ def core() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        lib.mlc_linear_simt_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+        lib.mlc_linear_simt_scratch_floats.restype = c_longlong
         lib.mlc_set_pdl.argtypes = [c_int]
         lib.mlc_set_pdl.restype = c_int
         lib.mlc_uniform_of.argtypes = [c_ulonglong, c_int, c_int]
@@ -252,14 +254,23 @@ def gather_rows(x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tens
                                   out_x.data_ptr(), _ptr(out_delta), _stream()), "gather")
 
 
-def linear_simt(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
-    """y = x @ w.T with float32 multiply-adds on the CUDA cores."""
+def linear_simt(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, n_sms: int = 0) -> None:
+    """y = x @ w.T with float32 multiply-adds on the CUDA cores, every output the same sum in the same order
+    whatever the number of rows (csrc/linear_simt.cu).  A product of few rows and few columns shares its K range out
+    over blocks; the scratch memory for that is allocated here, per call."""
     require_cuda(x, w, y)
     m, k = x.shape
     n = w.shape[0]
     assert w.shape[1] == k and y.shape == (m, n)
-    _check(core().mlc_linear_simt(x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype), y.data_ptr(),
-                                  dtype_code(y.dtype), m, n, k, _stream()), "linear")
+    if n_sms <= 0:
+        n_sms = _sm_count(x.device)
+    lib = core()
+    need = lib.mlc_linear_simt_scratch_floats(m, n, k, n_sms)
+    scratch = torch.empty(need, dtype=torch.float32, device=x.device) if need > 0 else None
+    if scratch is not None:
+        count_launches(1)                       # the kernel that adds the chunks
+    _check(lib.mlc_linear_simt(x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype), y.data_ptr(),
+                               dtype_code(y.dtype), m, n, k, _ptr(scratch), need, n_sms, _stream()), "linear")
 
 
 _argmax_scratch = {}

@@ -242,17 +242,23 @@ def test_gather_rows():
 
 @pytest.mark.parametrize("xd,wd,yd", [("float32", "float32", "float32"), ("bfloat16", "float32", "float32"),
                                       ("float32", "bfloat16", "bfloat16"), ("bfloat16", "bfloat16", "float32")])
-@pytest.mark.parametrize("M,N,K", [(1, 70, 33), (5, 1000, 896), (130, 64, 344), (64, 129, 16)])
+@pytest.mark.parametrize("M,N,K", [(1, 70, 33), (5, 1000, 896), (130, 64, 344), (64, 129, 16), (300, 200, 1000), (17, 896, 4864),
+                                   (16, 896, 4863), (3, 40000, 515)])
 def test_float32_linear_takes_any_size_and_gives_each_row_the_same_sum(M, N, K, xd, wd, yd):
+    """Three kernels share the work by the number of rows (over 64, over 16, fewer; the last with the K range shared out
+    over blocks when the columns are few): every one adds an output's terms in the same order, so a row's result is the
+    same bits in any batch.  Inner sizes that are no multiple of 4 take the loads one element at a time."""
     g = torch.Generator().manual_seed(M * N)
     x = torch.randn(M, K, generator=g).to(DT[xd])
     w = torch.randn(N, K, generator=g).to(DT[wd])
     y = torch.empty(M, N, dtype=DT[yd], device=DEV)
     kernels.linear_simt(x.to(DEV), w.to(DEV), y)
     close(y.float(), x.double() @ w.double().t(), 3e-6 if yd == "float32" else 5e-3)
-    y1 = torch.empty(1, N, dtype=DT[yd], device=DEV)
-    kernels.linear_simt(x[M - 1:].contiguous().to(DEV), w.to(DEV), y1)
-    assert torch.equal(y1[0], y[M - 1])                               # bit for bit, whatever the batch
+    for rows in (1, 16, 20, 70):                                          # the last row alone, and in batches that other kernels take
+        lo = max(0, M - rows)
+        part = torch.empty(M - lo, N, dtype=DT[yd], device=DEV)
+        kernels.linear_simt(x[lo:].contiguous().to(DEV), w.to(DEV), part)
+        assert torch.equal(part, y[lo:])                                  # bit for bit, whatever the batch
 
 
 @pytest.mark.parametrize("T,N,K,bn,splits", [(16, 128, 64, 16, 1), (1, 1000, 344, None, 1), (8, 896, 4864, 16, 19),
