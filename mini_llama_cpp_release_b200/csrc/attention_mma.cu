@@ -434,8 +434,8 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     // where the cluster's other blocks write; nothing else of this block lives here, so they may write at any time
     unsigned char* recv = smem_raw + (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
 
-    unsigned long long* stamps = (a.stamps != nullptr && threadIdx.x == 0)
-        ? a.stamps + 12ull * (blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z)) : nullptr;
+    unsigned long long* const stamps = MLC_STAMPS_OR_NULL((a.stamps != nullptr && threadIdx.x == 0)
+        ? a.stamps + 12ull * (blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z)) : nullptr);
     if (stamps) stamps[0] = stamp_ns();                                   // entry
     grid_launch_dependents();
     const int b = blockIdx.z;
@@ -888,8 +888,15 @@ extern "C" int mlc_attention_mma_head_dim() { return HD; }
 // cannot be launched.  Key splits merged inside a cluster (n_splits > 1 without part_ml / part_o) need at least 1.
 extern "C" int mlc_attention_decode_clusters_resident(int size) { return decode_clusters_resident(size); }
 
-// Measurement hook: later launches of the decode kernel leave nanosecond stamps of their phases in p ([blocks][12] on
-// the device; null switches it off again).
+// Measurement hook, effective only in builds with -DMLC_PHASE_STAMPS: later launches of the decode kernel leave
+// nanosecond stamps of their phases in p ([blocks][12] on the device; null switches it off again).
+extern "C" int mlc_phase_stamps_built() {
+#ifdef MLC_PHASE_STAMPS
+    return 1;
+#else
+    return 0;
+#endif
+}
 static unsigned long long* g_decode_stamps = nullptr;
 extern "C" int mlc_attention_decode_stamps(unsigned long long* p) {
     g_decode_stamps = p;

@@ -1,5 +1,5 @@
 // Prompt attention on the fifth-generation tensor cores: softmax(q·kᵀ·scale)·v of many tokens over
-// a paged bfloat16 cache (src/ops.cpp:143-196 gives the arithmetic), scores and outputs accumulated in
+// a paged bfloat16 cache (src/forward.cpp:585-611 and src/ops.cpp:43-70 give the arithmetic), scores and outputs accumulated in
 // tensor memory, operands staged in shared memory by TMA.
 //
 // A block owns 128 rows of one key/value head: the group's query heads of 128 / group successive
@@ -283,7 +283,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // is the output in tensor memory rescaled, so that after the first tiles the rescaling almost never runs.
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
+#ifdef MLC_PHASE_STAMPS
         const bool stamp = a.timing != nullptr && warp == 3;      // the whole warp keeps time, so that it stays converged
+#else
+        constexpr bool stamp = false;                             // phase clocks are compiled in only with -DMLC_PHASE_STAMPS
+#endif
         int ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t0 = 0, t1;        // 32-bit clocks: differences survive the wrap
 #define MLC_PHASE(k) if (stamp) { t1 = (int)clock(); ph[k] += t1 - t0; t0 = t1; }
         if (stamp) t0 = (int)clock();

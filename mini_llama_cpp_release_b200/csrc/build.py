@@ -84,6 +84,12 @@ def _headers() -> List[str]:
 INCLUDED_SOURCES = {"attention_noalloc.cu": ["attention_simt.cu"]}
 
 
+def extra_flags() -> List[str]:
+    """Further nvcc flags from the environment (MLC_NVCC_FLAGS), for tuning builds such as -DMLC_PHASE_STAMPS; a library
+    built with them has a name of its own and never replaces the engine's."""
+    return os.environ.get("MLC_NVCC_FLAGS", "").split()
+
+
 def _digest(sources: Sequence[str], defines: Sequence[str]) -> str:
     h = hashlib.sha256()
     extra = [inc for s in sources for inc in INCLUDED_SOURCES.get(s, [])]
@@ -91,7 +97,7 @@ def _digest(sources: Sequence[str], defines: Sequence[str]) -> str:
         h.update(name.encode())
         with open(os.path.join(_HERE, name), "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS + list(defines)).encode())
+    h.update(" ".join(NVCC_FLAGS + list(defines) + extra_flags()).encode())
     return h.hexdigest()[:16]
 
 
@@ -100,7 +106,7 @@ def library_path(name: str, sources: Sequence[str], defines: Sequence[str] = ())
 
 
 def _compile_one(nvcc: str, src: str, obj: str, defines: Sequence[str]) -> None:
-    cmd = [nvcc, *NVCC_FLAGS, *defines, "-I", _HERE, "-c", os.path.join(_HERE, src), "-o", obj]
+    cmd = [nvcc, *NVCC_FLAGS, *defines, *extra_flags(), "-I", _HERE, "-c", os.path.join(_HERE, src), "-o", obj]
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if p.returncode != 0:
         raise BuildError(f"nvcc failed on {src}:\n{p.stdout}")
@@ -136,8 +142,9 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
         if p.returncode != 0:
             raise BuildError(f"linking {name} failed:\n{p.stdout}")
         os.replace(tmp_out, out)
-        # binaries of earlier versions of these sources are never loaded again: drop them
-        prefix = f"lib{name}_"
+        # binaries of earlier versions of these sources are never loaded again: drop them (a tuning build keeps its hands
+        # off: the engine's library of the same name is still wanted)
+        prefix = f"lib{name}_" if not extra_flags() else "\0"
         for f in os.listdir(build_dir()):
             if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out):
                 try:

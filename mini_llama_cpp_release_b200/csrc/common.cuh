@@ -24,6 +24,14 @@
         if (e_ != cudaSuccess) return (int)e_;          \
     } while (0)
 
+// Per-phase time stamps inside the large kernels are a tuning aid: they are compiled in only with -DMLC_PHASE_STAMPS,
+// which the package's own build does not set; without it the pointers that would receive them are ignored.
+#ifdef MLC_PHASE_STAMPS
+#define MLC_STAMPS_OR_NULL(expr) (expr)
+#else
+#define MLC_STAMPS_OR_NULL(expr) nullptr
+#endif
+
 namespace mlc {
 
 typedef __nv_bfloat16 bf16;

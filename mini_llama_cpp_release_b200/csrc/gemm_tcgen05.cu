@@ -52,7 +52,7 @@ struct GemmArgs {
     long long split_stride;    // elements between the output slices of two splits
     int* status;
     int m_tiles, n_tiles, n_splits;   // the grid of output tiles the persistent blocks walk
-    unsigned long long* timing;  // optional [blocks][8] nanosecond stamps of a block's phases (for tuning), or null
+    unsigned long long* timing;  // [blocks][8] nanosecond stamps of a block's phases, or null; read only in builds with -DMLC_PHASE_STAMPS
     // QKV epilogue
     const float* bias;         // [n_out] in the stored row order, or null
     const int* positions;      // [tokens]
@@ -137,7 +137,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles_total = g.m_tiles * g.n_tiles * g.n_splits;
-    unsigned long long* stamps = g.timing == nullptr ? nullptr : g.timing + 8ull * blockIdx.x;
+    unsigned long long* const stamps = MLC_STAMPS_OR_NULL(g.timing == nullptr ? nullptr : g.timing + 8ull * blockIdx.x);
     if (stamps != nullptr && threadIdx.x == 0) stamps[0] = global_ns();                 // block start
 
     if (threadIdx.x == 0) {

@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_decode_stamps", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -355,8 +355,6 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
         lib.mlc_attention_decode_clusters_resident.restype = c_int
         lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P]
         lib.mlc_attention_tcgen05.restype = c_int
-        lib.mlc_attention_decode_stamps.argtypes = [P]
-        lib.mlc_attention_decode_stamps.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
         _attn_libs[head_dim] = lib
@@ -392,16 +390,6 @@ def attention_decode_splits(head_dim: int, blocks: int, max_kv_len: int, keys_pe
 def attention_decode_cluster_limit(head_dim: int) -> int:
     """The largest cluster the single-token attention kernel can merge key splits in."""
     return max(s for s in range(1, 17) if s == 1 or attention_decode_clusters_resident(head_dim, s) > 0)
-
-
-def attention_decode_stamps(head_dim: int, stamps: Optional[torch.Tensor]) -> None:
-    """Measurement hook of the single-token attention kernel: launches that follow leave nanosecond stamps of their
-    phases in `stamps` (int64 [blocks, 12] on the device); None switches it off again."""
-    lib = attention_library(head_dim)
-    if stamps is not None:
-        require_cuda(stamps)
-        assert stamps.dtype == torch.int64 and stamps.dim() == 2 and stamps.shape[1] == 12 and stamps.is_contiguous()
-    _check(lib.mlc_attention_decode_stamps(stamps.data_ptr() if stamps is not None else None), "attention stamps")
 
 
 def attention_mma_plan(max_q_len: int, n_seqs: int, max_kv_len: int, q_heads: int, kv_heads: int, n_sms: int):
@@ -443,7 +431,7 @@ def attention_tcgen05_blocks(max_q_len: int, n_seqs: int, q_heads: int, kv_heads
 
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
                       max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int,
-                      timing: Optional[torch.Tensor] = None) -> None:
+                      ) -> None:
     """Prompt attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry on the tcgen05 tensor cores
     (head sizes 64 and 128, pages of 64 tokens).  Keys are not shared out over blocks: meant for steps whose rows fill
     the GPU; a block itself works on two key tiles at a time."""
@@ -455,7 +443,7 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tens
     _check(lib.mlc_attention_tcgen05(q.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), start_pos.data_ptr(), n_seqs,
                                      q.shape[0], max_q_len, q_heads, kv.kv_heads, kv.head_dim, float(scale), int(window),
                                      status.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
-                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, kv.k_pool.shape[1], _ptr(timing), _stream()),
+                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, kv.k_pool.shape[1], None, _stream()),
            "tcgen05 attention")
 
 
@@ -643,7 +631,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
                  block_tokens: Optional[int] = None, bias: Optional[torch.Tensor] = None,
                  positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
                  rope: Optional[torch.Tensor] = None, q_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
-                 kv: Optional[KVView] = None, n_sms: int = 0, timing: Optional[torch.Tensor] = None) -> None:
+                 kv: Optional[KVView] = None, n_sms: int = 0) -> None:
     """bfloat16 x [n, K] times bfloat16 w [rows, K] transposed on the tcgen05 tensor cores, with
     the epilogue done before anything is stored (see csrc/gemm_tcgen05.cu).  Epilogue EPI_ADD adds the
     product into `out` (float32 [n, rows]) with atomic adds.  `n_sms` bounds the number of (persistent) blocks."""
@@ -676,7 +664,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
         cache = (None, None, None, 0, 0, 1)
     status = gemm_status(x.device)
     _check(core().mlc_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
-                                   block_tokens, n_splits, epilogue, status.data_ptr(), _ptr(timing), n_sms,
+                                   block_tokens, n_splits, epilogue, status.data_ptr(), None, n_sms,
                                    _ptr(bias), _ptr(positions),
                                    _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
                                    kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product")

@@ -11,12 +11,16 @@ of `--copies` launches captured back to back in one CUDA graph, each on its own 
 weights or cache so that the data comes from HBM as it does in a model with that many layers.
 The second figure is what a decode step pays.  `--library` times the library's matrix product
 on the same operands for comparison.  With `--once` the kernel runs a single time (the mode to
-put under a profiler).  `attention --q-len 1 --cluster --phases` prints where the single-token attention kernel's
-time goes: nanosecond stamps that thread 0 of every block takes between the kernel's phases, inside the chain.
+put under a profiler).  This is the package's timing tool for single kernels: the summaries under profiles/ give the
+command line that made each of them.  `attention --q-len 1 --cluster --phases` prints where the single-token attention
+kernel's time goes (nanosecond stamps that thread 0 of every block takes between the kernel's phases); the stamps are
+compiled into the kernels only with `MLC_NVCC_FLAGS=-DMLC_PHASE_STAMPS` in the environment, which builds a library of
+its own beside the engine's.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import math
 import statistics
@@ -215,6 +219,13 @@ def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
     """The single-token kernel between small kernels, as it sits between the products of a decode step."""
     if args.q_len != 1 or args.impl != "mma":
         raise SystemExit("--phases is for the single-token kernel (--q-len 1, --impl mma)")
+    lib = kernels.attention_library(args.head_dim)
+    lib.mlc_phase_stamps_built.restype = ctypes.c_int
+    if not lib.mlc_phase_stamps_built():
+        raise SystemExit("--phases needs kernels that take time stamps: run with MLC_NVCC_FLAGS=-DMLC_PHASE_STAMPS in the "
+                         "environment (a library of its own is built with that flag; the engine's build never has it)")
+    lib.mlc_attention_decode_stamps.argtypes = [ctypes.c_void_p]
+    lib.mlc_attention_decode_stamps.restype = ctypes.c_int
     C = args.copies
     x = torch.zeros(args.seqs, 896, device=DEV)
     gain = torch.ones(896, device=DEV)
@@ -224,9 +235,9 @@ def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
     def chain(record: bool) -> None:
         for i in range(C):
             kernels.add_rmsnorm(x, None, gain, 1e-6, h)
-            kernels.attention_decode_stamps(args.head_dim, stamps[i] if record else None)
+            lib.mlc_attention_decode_stamps(stamps[i].data_ptr() if record else None)
             fn(i)
-        kernels.attention_decode_stamps(args.head_dim, None)
+        lib.mlc_attention_decode_stamps(None)
 
     s = torch.cuda.Stream()
     with torch.cuda.stream(s):
@@ -249,7 +260,7 @@ def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
     print(json.dumps(out, indent=1))
 
 
-def main(argv=None) -> int:
+def parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["gemm", "norm", "attention"])
     ap.add_argument("--tokens", type=int, default=8)
@@ -272,8 +283,13 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--cluster", action="store_true", help="single tokens: merge key splits inside a thread-block cluster")
     ap.add_argument("--impl", default="mma", choices=["mma", "tcgen05"], help="attention kernel")
-    ap.add_argument("--phases", action="store_true", help="single-token attention: time stamps of the kernel's phases")
-    args = ap.parse_args(argv)
+    ap.add_argument("--phases", action="store_true",
+                    help="single-token attention: time stamps of the kernel's phases (needs MLC_NVCC_FLAGS=-DMLC_PHASE_STAMPS)")
+    return ap
+
+
+def main(argv=None) -> int:
+    args = parser().parse_args(argv)
     kernels.set_pdl(not args.no_pdl)
     if args.kernel == "gemm":
         args.splits = max(1, args.splits)

@@ -229,13 +229,17 @@ def time_e2e(llm, prompts: Sequence[Sequence[int]], steps: int) -> Dict[str, Any
 
 
 def agreement(chosen_on_device: Sequence[Sequence[int]], generated: Sequence[Sequence[int]], steps: int) -> Dict[str, int]:
-    """How many sequences got the same first `steps` ids from the device-fed loop ([step][sequence]) and from
-    `generate` ([sequence][step]).  The two run the same captured step; in bfloat16 the few-row products add into the
-    residual stream with atomics, so a near-tie between two logits may fall differently, and then that sequence goes
-    its own way: most sequences must agree, not all."""
+    """How far the device-fed loop ([step][sequence]) and `generate` ([sequence][step]) chose the same ids from the same
+    prompts: over the first `steps` ids, the number of sequences that agree throughout, and the number that agree on
+    their first eight.  The two run the same captured step; in bfloat16 the few-row products add into the residual
+    stream with atomics, so a near-tie between two logits (common with random weights, whose logits are nearly flat)
+    may fall differently, and from there that sequence goes its own way.  A loop that fed the wrong token or position
+    back would part from `generate` at the second id of every sequence."""
     n = min(steps, len(chosen_on_device), min(len(g) for g in generated))
+    head = min(8, n)
     equal = sum(1 for i, g in enumerate(generated) if [row[i] for row in chosen_on_device[:n]] == list(g[:n]))
-    return dict(steps=n, equal_sequences=equal, of=len(generated))
+    first = sum(1 for i, g in enumerate(generated) if [row[i] for row in chosen_on_device[:head]] == list(g[:head]))
+    return dict(steps=n, equal_sequences=equal, equal_first_8=first, of=len(generated))
 
 
 def time_prefill(llm, prompts: Sequence[Sequence[int]], iters: int = 5, warmup: int = 3) -> Dict[str, float]:

@@ -67,6 +67,9 @@ def test_roofline_names_what_limits_the_step():
 def test_ids_of_the_two_decode_loops_are_compared_sequence_by_sequence():
     from mini_llama_cpp_release_b200 import measure
     on_device = [[1, 5], [2, 6], [3, 7], [4, 8]]                   # [step][sequence]
-    assert measure.agreement(on_device, [[1, 2, 3, 4], [5, 6, 7, 8]], 32) == dict(steps=4, equal_sequences=2, of=2)
+    assert measure.agreement(on_device, [[1, 2, 3, 4], [5, 6, 7, 8]], 32) == dict(steps=4, equal_sequences=2, equal_first_8=2, of=2)
     assert measure.agreement(on_device, [[1, 2, 3, 4], [5, 6, 0, 8]], 32)["equal_sequences"] == 1
     assert measure.agreement(on_device, [[1, 2, 3, 4], [5, 6, 0, 8]], 2)["equal_sequences"] == 2
+    long_run = [[7, 9]] * 8 + [[7, 1]] * 24                          # the second sequence parts at its ninth id
+    got = measure.agreement(long_run, [[7] * 32, [9] * 32], 32)
+    assert (got["equal_sequences"], got["equal_first_8"]) == (1, 2)

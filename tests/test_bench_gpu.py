@@ -24,7 +24,7 @@ def test_our_arm_prints_the_contracts_line_and_checks_the_ids_of_the_timed_loop(
     assert line["config"]["layers"] == 1 and line["config"]["layers_full"] == 24 and len(line["config"]) <= 20
     assert line["gpu_launches"] > 0 and line["library_gemm_launches"] == 0
     checked = line["e2e"]["ids_checked"]
-    assert checked["steps"] == 32 and checked["equal_sequences"] * 2 >= checked["of"] == 8
+    assert checked["steps"] == 32 and checked["equal_first_8"] * 2 >= checked["of"] == 8
     assert line["roofline"]["bound"] == "hbm" and 0 < line["roofline"]["frac"] < 1.5
     assert line["prefill"]["tokens"] == 2048 and line["prefill"]["first_ms"] > 0
 

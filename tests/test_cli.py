@@ -148,3 +148,29 @@ def test_generate_from_random_weights_of_a_preset_with_no_model_on_disk(tmp_path
     assert p.returncode == 0, p.stderr[-2000:]
     ids = helpers.plain_model(folder).greedy([5, 17, 3, 200], 5)
     assert f"generated ids: {' '.join(map(str, ids))}" in p.stdout
+
+
+def test_the_kernel_timing_tool_reads_its_arguments():
+    """`python -m mini_llama_cpp_release_b200.kernels.microbench` is the tool the summaries under profiles/ were made
+    with; the command lines quoted there must keep parsing."""
+    from mini_llama_cpp_release_b200.kernels import microbench
+    ap = microbench.parser()
+    a = ap.parse_args("gemm --tokens 8 --rows 9728 --k 896 --epilogue silu --copies 1 --once".split())
+    assert (a.kernel, a.tokens, a.rows, a.k, a.epilogue, a.copies, a.once, a.rows_form, a.library) == ("gemm", 8, 9728, 896, "silu", 1, True, False, False)
+    a = ap.parse_args("gemm --tokens 2048 --rows 1152 --k 896 --epilogue qkv --rows-form".split())
+    assert a.rows_form and a.copies == 24
+    a = ap.parse_args("attention --seqs 8 --context 4096 --cluster".split())
+    assert (a.seqs, a.context, a.q_len, a.cluster, a.impl, a.heads, a.kv_heads, a.head_dim) == (8, 4096, 1, True, "mma", 14, 2, 64)
+    a = ap.parse_args("norm --tokens 8 --k 896 --slices 19".split())
+    assert a.slices == 19
+    assert ap.parse_args("attention --seqs 8 --context 4096 --cluster --phases --copies 8".split()).phases
+    for bad in (["conv"], ["gemm", "--epilogue", "relu"], ["attention", "--impl", "library"]):
+        with pytest.raises(SystemExit):
+            ap.parse_args(bad)
+    root = os.path.join(ROOT, "profiles")
+    import re, shlex
+    for name in os.listdir(root):
+        for line in open(os.path.join(root, name)):
+            m = re.search(r"kernels\.microbench ((?:gemm|norm|attention)[^`#]*)", line)
+            if m:
+                ap.parse_args(shlex.split(m.group(1).strip()))
