@@ -100,9 +100,12 @@ def bench_gemm(args) -> None:
     flops = 2.0 * T * N * K
     epi = {"store": 0, "silu": 1, "qkv": 2, "add": 3}[args.epilogue]
     if args.library:
-        out = torch.empty(T, N, dtype=torch.float32, device=DEV)
-        report(f"library product T={T} N={N} K={K}", lambda i: torch.mm(x, ws[i % C].t(), out_dtype=torch.float32, out=out),
-               args, nbytes + T * N * 4, flops)
+        out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+        if epi == 3:            # adding into the output, as the output and down projections do
+            lib = lambda i: torch.addmm(out, x, ws[i % C].t(), out_dtype=torch.float32, out=out)
+        else:
+            lib = lambda i: torch.mm(x, ws[i % C].t(), out_dtype=torch.float32, out=out)
+        report(f"library product T={T} N={N} K={K} epilogue={args.epilogue}", lib, args, nbytes + T * N * 4, flops)
         return
     if args.rows_form:
         hd, KV = args.head_dim, args.kv_heads
@@ -127,8 +130,9 @@ def bench_gemm(args) -> None:
                       rope=kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), max(T, 64)), q_heads=H, kv_heads=KV, head_dim=hd,
                       kv=bindings.KVView(k_pool, v_pool, 0, table, 64, KV, hd))
             out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
-        fn = lambda i: kernels.gemm_tcgen05_rows(x, ws[i % C], out, epi, args.block_tokens, **kw)
-        report(f"tcgen05 product, prompt form T={T} N={N} K={K} epilogue={args.epilogue}", fn, args, nbytes + out.numel() * out.element_size(), flops)
+        splits = args.splits_given or None       # None: the plan's choice (adding epilogue) or none
+        fn = lambda i: kernels.gemm_tcgen05_rows(x, ws[i % C], out, epi, args.block_tokens, splits, **kw)
+        report(f"tcgen05 product, prompt form T={T} N={N} K={K} epilogue={args.epilogue} tile rows={args.block_tokens} splits={splits}", fn, args, nbytes + out.numel() * out.element_size(), flops)
         return
     if epi == 0:
         out = torch.empty(args.splits, T, N, dtype=torch.float32, device=DEV)
@@ -269,7 +273,7 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--epilogue", default="store", choices=["store", "silu", "qkv", "add"])
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--slices", type=int, default=0)
-    ap.add_argument("--block-tokens", type=int, default=None)
+    ap.add_argument("--block-tokens", type=int, default=None, help="tokens per tile (rows of W per tile with --rows-form)")
     ap.add_argument("--copies", type=int, default=24)
     ap.add_argument("--library", action="store_true")
     ap.add_argument("--rows-form", action="store_true", help="the prompt form of the product (tokens as the M operand)")
@@ -292,6 +296,7 @@ def main(argv=None) -> int:
     args = parser().parse_args(argv)
     kernels.set_pdl(not args.no_pdl)
     if args.kernel == "gemm":
+        args.splits_given = args.splits
         args.splits = max(1, args.splits)
         bench_gemm(args)
     elif args.kernel == "norm":

@@ -242,10 +242,11 @@ def agreement(chosen_on_device: Sequence[Sequence[int]], generated: Sequence[Seq
     return dict(steps=n, equal_sequences=equal, equal_first_8=first, of=len(generated))
 
 
-def time_prefill(llm, prompts: Sequence[Sequence[int]], iters: int = 5, warmup: int = 3) -> Dict[str, float]:
+def time_prefill(llm, prompts: Sequence[Sequence[int]], iters: int = 5, warmup: int = 3, settle_ms: float = 300.0) -> Dict[str, float]:
     """A prompt step (all `prompts` at once), device-timed.  The first time a shape of step comes it is issued kernel by
     kernel from the host (`first_ms`); from its second coming on it is a replay of a captured graph (`ms`, the median of
-    `iters` runs after `warmup`)."""
+    `iters` runs after `warmup` runs and `settle_ms` of further untimed runs, so that the figure does not depend on what
+    the GPU did before this process: clocks and power state follow the load with some delay)."""
     import torch
     from .engine import MiniBatch
     ctx = llm.context
@@ -256,7 +257,17 @@ def time_prefill(llm, prompts: Sequence[Sequence[int]], iters: int = 5, warmup: 
     ctx.forward_batch(MiniBatch.from_tokens(slot, list(prompts[0][:max(1, len(prompts[0]) - 64)])))
     ctx.release(slot)
     times = []
-    for i in range(warmup + iters):
+    settle_until = None
+    while len(times) < warmup + iters:
+        if len(times) == warmup and settle_ms > 0:            # untimed runs between the warm-up and the timed ones
+            now = time.perf_counter()
+            settle_until = settle_until or now + settle_ms / 1e3
+            if now < settle_until:
+                slots = [ctx.acquire() for _ in prompts]
+                ctx.forward_batch(MiniBatch.prefill(slots, prompts))
+                for s in slots:
+                    ctx.release(s)
+                continue
         slots = [ctx.acquire() for _ in prompts]
         torch.cuda.synchronize(dev)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
