@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 ]
 
 # library name → (sources, extra -D flags may be added per variant)
-CORE_SOURCES = ["elementwise.cu", "attention_simt.cu", "sampling.cu", "linear_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_rows.cu"]
+CORE_SOURCES = ["elementwise.cu", "attention_simt.cu", "sampling.cu", "linear_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_rows.cu", "gemm_tcgen05_pair.cu"]
 # compiled once per head size (-DMLC_HEAD_DIM=...): the mma.sync kernels for every size, the tcgen05 kernel for 64 and 128
 ATTENTION_SOURCES = ["attention_mma.cu", "attention_tcgen05.cu"]
 

@@ -25,35 +25,9 @@
 //
 // Every wait on an mbarrier is bounded by a clock; a wait that runs out records a code in `status` (21 loader,
 // 22 tensor cores, 23 epilogue), the block skips its stores, frees its tensor memory and returns.
-#include "tcgen05.cuh"
+#include "gemm_rows_common.cuh"
 
 namespace mlc {
-
-enum { R_EPI_STORE = 0, R_EPI_SILU_MUL = 1, R_EPI_QKV = 2, R_EPI_ADD = 3 };
-
-struct RowsArgs {
-    void* out;
-    int out_dtype;
-    int n_out;                 // rows of W = columns of the product; a multiple of 16
-    int n_tok;
-    int k_blocks;              // ceil(K / 64)
-    int m_tiles, n_tiles;
-    int n_splits;              // blocks that share out a tile's K range (ADD only); 1: none
-    int k_blocks_per_split;
-    int* status;
-    // QKV epilogue
-    const float* bias;         // [n_out] in the stored row order, or null
-    const int* positions;      // [tokens]
-    const int* tok_seq;        // [tokens]
-    const float2* rope;        // [positions][hd/2] cos, sin; or null
-    int rope_positions;
-    int q_heads, kv_heads, hd;
-    PagedKV cache;
-};
-
-constexpr int R_BM = 128;
-constexpr int R_BK = 64;
-constexpr int R_A_BYTES = R_BM * R_BK * 2;
 
 template <int BN> struct RowsShape {
     static constexpr int B_BYTES = BN * R_BK * 2;
@@ -67,11 +41,6 @@ template <int BN> struct RowsShape {
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of a block");
     static_assert(BN % 32 == 0 && BN >= 128 && BN <= 256, "rows of W per tile");
 };
-
-__device__ __forceinline__ unsigned pack2(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<unsigned*>(&h);
-}
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(RowsShape<BN>::THREADS, 1)
@@ -271,54 +240,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     // n_out and the group's share of the tile are multiples of 16: the chunk has 16 or 32 columns
                     const bool second = n + 16 < g.n_out && c0 + 32 <= COLS_PER_GROUP;
                     if (!tok_ok) continue;
-                    if (EPI == R_EPI_STORE) {
-                        if (g.out_dtype == MLC_DTYPE_BF16) {
-                            uint4* dst = reinterpret_cast<uint4*>((bf16*)g.out + (long long)tok * g.n_out + n);
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-                                if (u < 2 || second)
-                                    dst[u] = make_uint4(pack2(v[8 * u], v[8 * u + 1]), pack2(v[8 * u + 2], v[8 * u + 3]),
-                                                        pack2(v[8 * u + 4], v[8 * u + 5]), pack2(v[8 * u + 6], v[8 * u + 7]));
-                        } else {
-                            float4* dst = reinterpret_cast<float4*>((float*)g.out + (long long)tok * g.n_out + n);
-#pragma unroll
-                            for (int u = 0; u < 8; ++u)
-                                if (u < 4 || second) dst[u] = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
-                        }
-                    } else if (EPI == R_EPI_ADD && g.n_splits > 1) {
-                        float4* dst = reinterpret_cast<float4*>((float*)g.out + (long long)tok * g.n_out + n);
-#pragma unroll
-                        for (int u = 0; u < 8; ++u)
-                            if (u < 4 || second) atomicAdd(dst + u, make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]));
-                    } else if (EPI == R_EPI_ADD) {
-                        float4* dst = reinterpret_cast<float4*>((float*)g.out + (long long)tok * g.n_out + n);
-                        float4 old[8];
-#pragma unroll
-                        for (int u = 0; u < 8; ++u)
-                            if (u < 4 || second) old[u] = dst[u];
-#pragma unroll
-                        for (int u = 0; u < 8; ++u)
-                            if (u < 4 || second)
-                                dst[u] = make_float4(old[u].x + v[4 * u], old[u].y + v[4 * u + 1], old[u].z + v[4 * u + 2], old[u].w + v[4 * u + 3]);
-                    } else {                                          // SILU_MUL: columns alternate gate_j, up_j
-                        float act[16];
-#pragma unroll
-                        for (int u = 0; u < 16; ++u) {
-                            const float gate = v[2 * u], up = v[2 * u + 1];
-                            act[u] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
-                        }
-                        const long long at = (long long)tok * (g.n_out >> 1) + (n >> 1);
-                        if (g.out_dtype == MLC_DTYPE_BF16) {
-                            uint4* dst = reinterpret_cast<uint4*>((bf16*)g.out + at);
-                            dst[0] = make_uint4(pack2(act[0], act[1]), pack2(act[2], act[3]), pack2(act[4], act[5]), pack2(act[6], act[7]));
-                            if (second) dst[1] = make_uint4(pack2(act[8], act[9]), pack2(act[10], act[11]), pack2(act[12], act[13]), pack2(act[14], act[15]));
-                        } else {
-                            float4* dst = reinterpret_cast<float4*>((float*)g.out + at);
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-                                if (u < 2 || second) dst[u] = make_float4(act[4 * u], act[4 * u + 1], act[4 * u + 2], act[4 * u + 3]);
-                        }
-                    }
+                    rows_epilogue_chunk<EPI>(g, v, tok, n, second);
                 }
             }
             // the accumulator has been read: the tensor cores may fill it again

@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -96,6 +96,7 @@ def core() -> ctypes.CDLL:
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
+            "mlc_gemm_tcgen05_pair": [P, P, P, I, I, I, I, I, I, I, P, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P, P],
@@ -515,7 +516,8 @@ def check_gemm_status(device: torch.device) -> None:
                    3: "the matrix product's epilogue", 11: "the attention kernel's TMA loader",
                    12: "the attention kernel's tensor-core issuer", 13: "the attention kernel's softmax rows",
                    21: "the prompt product's TMA loader", 22: "the prompt product's tensor-core issuer",
-                   23: "the prompt product's epilogue"}.get(code, str(code))
+                   23: "the prompt product's epilogue", 41: "the paired prompt product's TMA loader",
+                   42: "the paired prompt product's tensor-core issuer or relay", 43: "the paired prompt product's epilogue"}.get(code, str(code))
             raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier ({who}); its output is not valid")
 
 
@@ -553,6 +555,54 @@ def gemm_rows_block(n_tok: int, n_out: int, n_sms: int) -> int:
         if best_cost is None or cost <= best_cost:
             best, best_cost = bn, cost
     return best
+
+
+def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, block_rows: int = 256,
+                      n_splits: int = 1, n_sms: int = 0) -> None:
+    """The tcgen05 product for prompts with a pair of SMs on every tile of 256 tokens x `block_rows` rows of w
+    (csrc/gemm_tcgen05_pair.cu): epilogues EPI_STORE, EPI_SILU_MUL, EPI_ADD as `gemm_tcgen05_rows`."""
+    require_cuda(x, w, out)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 matrix product takes bfloat16 operands")
+    if epilogue == EPI_QKV:
+        raise KernelError("the paired form of the tcgen05 product has no Q/K/V epilogue")
+    if n_sms <= 0:
+        n_sms = _sm_count(x.device)
+    n_tok, K = x.shape
+    n_out = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    if K % 8 or n_out % 16:
+        raise KernelError(f"the prompt form of the tcgen05 product needs an inner size that is a multiple of 8 and "
+                          f"a multiple of 16 rows, got {K} and {n_out}")
+    if epilogue == EPI_SILU_MUL:
+        assert out.numel() == n_tok * (n_out // 2)
+    else:
+        assert out.numel() == n_tok * n_out and (epilogue != EPI_ADD or out.dtype == torch.float32)
+    status = gemm_status(x.device)
+    _check(core().mlc_gemm_tcgen05_pair(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n_tok, n_out, K,
+                                        block_rows, n_splits, epilogue, status.data_ptr(), n_sms, _stream()),
+           "tcgen05 matrix product (paired prompt form)")
+
+
+def gemm_pair_takes(n_tok: int, n_out: int, k: int, n_sms: int) -> bool:
+    """Whether a prompt product is better off with a pair of SMs on every tile of 256 tokens x 256 rows of w
+    (csrc/gemm_tcgen05_pair.cu): when those tiles fill the GPU at least twice over.  Measured on a B200: gate/up of
+    2,048 tokens 29.1 against 30.8 us at the Qwen2-0.5B sizes, 79 against 87 us at the 1.5B sizes, 345 against 383 us
+    at the 7B sizes (1,612 TFLOP/s); with fewer tiles than that the one-SM form, which has twice as many, wins."""
+    if n_tok <= 64 or n_out % 16 or k % 8 or n_sms < 2:
+        return False
+    return ((n_tok + 255) // 256) * ((n_out + 255) // 256) >= n_sms
+
+
+def gemm_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, n_sms: int = 0) -> None:
+    """A prompt product with epilogue EPI_STORE, EPI_SILU_MUL or EPI_ADD on whichever form suits its sizes."""
+    if n_sms <= 0:
+        n_sms = _sm_count(x.device)
+    if gemm_pair_takes(x.shape[0], w.shape[0], x.shape[1], n_sms):
+        gemm_tcgen05_pair(x, w, out, epilogue, 256, 1, n_sms)
+    else:
+        gemm_tcgen05_rows(x, w, out, epilogue, n_sms=n_sms)
 
 
 def gemm_rows_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):

@@ -242,11 +242,12 @@ def agreement(chosen_on_device: Sequence[Sequence[int]], generated: Sequence[Seq
     return dict(steps=n, equal_sequences=equal, equal_first_8=first, of=len(generated))
 
 
-def time_prefill(llm, prompts: Sequence[Sequence[int]], iters: int = 5, warmup: int = 3, settle_ms: float = 300.0) -> Dict[str, float]:
+def time_prefill(llm, prompts: Sequence[Sequence[int]], iters: int = 5, warmup: int = 3, settle_ms: float = 100.0) -> Dict[str, float]:
     """A prompt step (all `prompts` at once), device-timed.  The first time a shape of step comes it is issued kernel by
     kernel from the host (`first_ms`); from its second coming on it is a replay of a captured graph (`ms`, the median of
     `iters` runs after `warmup` runs and `settle_ms` of further untimed runs, so that the figure does not depend on what
-    the GPU did before this process: clocks and power state follow the load with some delay)."""
+    the GPU did before this process: its clocks follow the load with some delay; much longer, and a large model's step
+    would be measured under the power cap instead)."""
     import torch
     from .engine import MiniBatch
     ctx = llm.context

@@ -55,7 +55,7 @@ class SwiGLU(Part):
         rt = self.runtime
         a = rt.empty(h.shape[0], self.inter)
         if self.fused and kernels.gemm_rows_takes(h.shape[0], 2 * self.inter, self.hidden):
-            kernels.gemm_tcgen05_rows(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)    # prompts
+            kernels.gemm_prompt(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)    # prompts
         elif self.fused:
             kernels.gemm_tcgen05(h, self.gate_up.weight, a, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
         else:

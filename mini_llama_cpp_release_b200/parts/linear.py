@@ -9,10 +9,11 @@ Which kernel runs is decided by the operand types and sizes, never by the model:
     csrc/gemm_tcgen05.cu, always when an epilogue is fused (Q/K/V with bias, rotation and
     cache write; gate/up with SiLU·mul), and for plain products of up to 64 rows (decoding),
     where the K range is split over blocks and the partial sums are left to the consumer.
-  * plain bfloat16 products of more rows (prompts): the tokens-as-M tcgen05 kernel of
-    csrc/gemm_tcgen05_rows.cu; where the product is a branch's last it adds into the float32
-    residual stream in its epilogue, with the K range shared out over blocks when the tiles
-    alone would leave SMs idle.
+  * plain bfloat16 products of more rows (prompts): the tokens-as-M tcgen05 kernels, one SM
+    per tile (csrc/gemm_tcgen05_rows.cu) or, when tiles of 256 x 256 fill the GPU twice
+    over, a pair of SMs per tile (csrc/gemm_tcgen05_pair.cu); where the product is a
+    branch's last it adds into the float32 residual stream in its epilogue, with the K range
+    shared out over blocks when the tiles alone would leave SMs idle.
   * bfloat16 products whose sizes those kernels do not take (an inner size that is no
     multiple of 8; in a prompt, a row count of W that is no multiple of 16): the library's
     product with float32 accumulation, as the reference calls cuBLAS for all of its linears
@@ -69,7 +70,7 @@ class Linear:
         read, not two."""
         m = x.shape[0]
         if m > SMALL_BATCH and kernels.gemm_rows_takes(m, self.out_features, self.in_features):
-            kernels.gemm_tcgen05_rows(x, self.weight, stream, kernels.bindings.EPI_ADD, n_sms=self.runtime.n_sms)
+            kernels.gemm_prompt(x, self.weight, stream, kernels.bindings.EPI_ADD, n_sms=self.runtime.n_sms)
             return
         if m > SMALL_BATCH:
             kernels.library_gemm(x, self.weight, stream, accumulate=True)
@@ -95,7 +96,7 @@ class Linear:
             return out if splits > 1 else out[0]
         out = rt.empty(m, self.out_features, dtype=out_dtype)
         if self.tensor_core_ok and kernels.gemm_rows_takes(m, self.out_features, self.in_features):
-            kernels.gemm_tcgen05_rows(x, self.weight, out, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
+            kernels.gemm_prompt(x, self.weight, out, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
         else:
             kernels.library_gemm(x, self.weight, out)
         return out

@@ -744,3 +744,56 @@ def test_refusals_are_errors_not_wrong_results():
         kernels.attention_simt(q, torch.empty_like(q), z, z, 1, 1, 4, kv, 1.0)
     with pytest.raises(kernels.KernelError, match="CUDA device only"):
         kernels.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+@pytest.mark.parametrize("T,N,K,epi,bn,splits,out_dtype", [
+    (256, 128, 64, 0, 128, 1, "float32"), (300, 464, 200, 0, 224, 1, "float32"), (70, 144, 520, 0, 128, 1, "bfloat16"),
+    (2048, 896, 896, 3, 224, 2, "float32"), (1000, 272, 1000, 3, 160, 3, "float32"), (257, 48, 4864, 3, 128, 8, "float32"),
+    (2048, 9728, 896, 1, 256, 1, "bfloat16"), (700, 688, 136, 1, 192, 1, "bfloat16"), (513, 400, 72, 1, 256, 1, "float32"),
+    (5000, 2560, 128, 0, 256, 1, "bfloat16")])
+def test_paired_prompt_product(T, N, K, epi, bn, splits, out_dtype):
+    """The prompt product with a pair of SMs on every tile of 256 tokens (tcgen05.mma.cta_group::2,
+    csrc/gemm_tcgen05_pair.cu): plain store, SiLU·mul and adding into a float32 stream, with and without a K split;
+    token counts and row counts that are no multiple of the tiles (a last tile whose second block has no tokens at
+    all), an inner size that is no multiple of 64, and more tiles than pairs, so that rings and accumulators are used
+    again."""
+    g = torch.Generator().manual_seed(T + N + K)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    if epi == 3:
+        base = torch.randn(T, N, generator=g)
+        out = base.clone().to(DEV)
+        ref = ref + base.double()
+    elif epi == 1:
+        out = torch.full((T, N // 2), float("nan"), dtype=DT[out_dtype], device=DEV)
+        gg, uu = ref[:, 0::2], ref[:, 1::2]
+        ref = gg * (1 / (1 + torch.exp(-gg))) * uu
+    else:
+        out = torch.full((T, N), float("nan"), dtype=DT[out_dtype], device=DEV)
+    kernels.gemm_tcgen05_pair(x.to(DEV), w.to(DEV), out, epi, bn, splits)
+    kernels.check_gemm_status(DEV)
+    close(out, ref, 3 * math.sqrt(K) * 2.0 ** -24 if out_dtype == "float32" else 8e-3)
+
+
+def test_paired_prompt_product_is_chosen_when_its_tiles_fill_the_gpu_and_refuses_what_it_cannot_take():
+    assert kernels.gemm_pair_takes(2048, 9728, 896, 148) and kernels.gemm_pair_takes(16384, 896, 4864, 148)
+    assert not kernels.gemm_pair_takes(512, 9728, 896, 148) and not kernels.gemm_pair_takes(2048, 896, 4864, 148)
+    assert not kernels.gemm_pair_takes(64, 100000, 896, 148) and not kernels.gemm_pair_takes(4096, 9720, 896, 148)
+    x = torch.zeros(256, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(kernels.KernelError, match="Q/K/V"):
+        kernels.gemm_tcgen05_pair(x, w, torch.empty(256, 128, dtype=torch.bfloat16, device=DEV), 2)
+    with pytest.raises(kernels.KernelError, match="size"):                     # a K split is for the adding epilogue only
+        kernels.gemm_tcgen05_pair(x, w, torch.empty(256, 128, device=DEV), 0, 128, 2)
+    with pytest.raises(kernels.KernelError, match="size"):                     # a tile width the kernel is not built for
+        kernels.gemm_tcgen05_pair(x, w, torch.empty(256, 128, device=DEV), 0, 96, 1)
+    # both forms give the same product (the sums run in the same order: K ascending in one accumulator)
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(600, 200, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(320, 200, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    a, b = torch.empty(600, 320, device=DEV), torch.empty(600, 320, device=DEV)
+    kernels.gemm_tcgen05_pair(x, w, a, 0, 160, 1)
+    kernels.gemm_tcgen05_rows(x, w, b, 0, 160)
+    kernels.check_gemm_status(DEV)
+    assert torch.equal(a, b)
