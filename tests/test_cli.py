@@ -171,6 +171,6 @@ def test_the_kernel_timing_tool_reads_its_arguments():
     import re, shlex
     for name in os.listdir(root):
         for line in open(os.path.join(root, name)):
-            m = re.search(r"kernels\.microbench ((?:gemm|norm|attention)[^`#]*)", line)
+            m = re.search(r"kernels\.microbench ((?:gemm|norm|attention)[^`#\"]*)", line)
             if m:
                 ap.parse_args(shlex.split(m.group(1).strip()))
