@@ -39,8 +39,9 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 }
 
 // One token's 32 (or, at the matrix's edge, 16) accumulator columns n .. n+31 leave the block.  `second`: the upper 16
-// exist too.  STORE: y as float32 or bfloat16; ADD: added into the float32 stream (atomically when the K range is
-// shared out over blocks); SILU_MUL: columns alternate gate_j, up_j and gate·sigmoid(gate)·up goes to [token][n/2].
+// exist too.  STORE: y as float32 or bfloat16; ADD: added into the float32 stream with 16-byte atomic adds (one
+// per element and launch unless the K range is shared out over blocks); SILU_MUL: columns alternate gate_j, up_j
+// and gate·sigmoid(gate)·up goes to [token][n/2].
 template <int EPI>
 __device__ __forceinline__ void rows_epilogue_chunk(const RowsArgs& g, const float (&v)[32], int tok, int n, bool second) {
     if (EPI == R_EPI_STORE) {
@@ -57,21 +58,11 @@ __device__ __forceinline__ void rows_epilogue_chunk(const RowsArgs& g, const flo
             for (int u = 0; u < 8; ++u)
                 if (u < 4 || second) dst[u] = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
         }
-    } else if (EPI == R_EPI_ADD && g.n_splits > 1) {
+    } else if (EPI == R_EPI_ADD) {                    // a reduction that returns nothing: the thread does not wait for the old value
         float4* dst = reinterpret_cast<float4*>((float*)g.out + (long long)tok * g.n_out + n);
 #pragma unroll
         for (int u = 0; u < 8; ++u)
             if (u < 4 || second) atomicAdd(dst + u, make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]));
-    } else if (EPI == R_EPI_ADD) {
-        float4* dst = reinterpret_cast<float4*>((float*)g.out + (long long)tok * g.n_out + n);
-        float4 old[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-            if (u < 4 || second) old[u] = dst[u];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-            if (u < 4 || second)
-                dst[u] = make_float4(old[u].x + v[4 * u], old[u].y + v[4 * u + 1], old[u].z + v[4 * u + 2], old[u].w + v[4 * u + 3]);
     } else {                                          // SILU_MUL: columns alternate gate_j, up_j
         float act[16];
 #pragma unroll

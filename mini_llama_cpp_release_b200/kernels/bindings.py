@@ -13,7 +13,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -599,34 +599,63 @@ def gemm_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     """A prompt product with epilogue EPI_STORE, EPI_SILU_MUL or EPI_ADD on whichever form suits its sizes."""
     if n_sms <= 0:
         n_sms = _sm_count(x.device)
-    if gemm_pair_takes(x.shape[0], w.shape[0], x.shape[1], n_sms):
+    if epilogue == EPI_ADD:
+        form, block_rows, n_splits = gemm_add_plan(x.shape[0], w.shape[0], x.shape[1], n_sms)
+        if form == "pair":
+            gemm_tcgen05_pair(x, w, out, epilogue, block_rows, n_splits, n_sms)
+        else:
+            gemm_tcgen05_rows(x, w, out, epilogue, block_rows, n_splits, n_sms=n_sms)
+    elif gemm_pair_takes(x.shape[0], w.shape[0], x.shape[1], n_sms):
         gemm_tcgen05_pair(x, w, out, epilogue, 256, 1, n_sms)
     else:
         gemm_tcgen05_rows(x, w, out, epilogue, n_sms=n_sms)
 
 
-def gemm_rows_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):
-    """(rows of W per tile, K splits) for a prompt product that adds into the stream.  Such products (the output and down
-    projections) have few columns, so their tiles alone leave SMs idle: the K range is then shared out over several
-    blocks per tile, which add atomically.  The cost of a plan is its number of rounds of `n_sms` blocks times what a
-    block does per round: its K steps and a fixed part for filling the pipeline and writing the tile out (the
-    constants are fitted to measurements on a B200 at 2,048 tokens: 896 x 896, 896 x 4,864 and 1,536 x 8,960)."""
-    m_tiles = (n_tok + 127) // 128
+# What an adding prompt product costs in microseconds, by form: a launch, per K step a part that grows with the tile's
+# width and one that does not, per tile the write-out, and per megabyte of 16-byte atomic adds what the L2 takes for
+# them.  Fitted (12 % rms) to 600 measurements on a B200: 512, 2,048 and 8,192 tokens, nine weight shapes from
+# 896 x 896 to 4,096 x 11,008, every width and split below; the plan it picks is the fastest measured one in half of
+# the 27 cases and within 4 % of it in all but four (at most 9 %).
+_ADD_COST = {"rows": (128, 1, 2.34, 0.00090, 0.183, 2.19, 0.372),
+             "pair": (256, 2, 3.41, 0.00061, 0.219, 2.24, 0.360)}
+_ADD_WIDTHS = {"rows": (128, 160, 192, 224, 256), "pair": (192, 224, 256)}
+
+
+def _add_plans(form: str, n_tok: int, n_out: int, k: int, n_sms: int):
+    tile_tokens, sms_per_tile, launch, step_w, step_0, write_out, per_mb = _ADD_COST[form]
+    workers = n_sms // sms_per_tile
+    m_tiles = (n_tok + tile_tokens - 1) // tile_tokens
     k_blocks = (k + 63) // 64
-    best, best_cost = (128, 1), None
-    for bn in (128, 160, 192, 224, 256):
-        tiles = m_tiles * ((n_out + bn - 1) // bn)
-        step = 2.6 * bn + 380.0                                               # clocks per K step
-        fixed = 9000.0 + 20.0 * bn                                            # clocks per tile
-        for splits in (1, 2, 3, 4, 6, 8):
+    for bn in _ADD_WIDTHS[form]:
+        n_tiles = (n_out + bn - 1) // bn
+        for splits in (1, 2, 3, 4, 6):
             per = (k_blocks + splits - 1) // splits
-            real = (k_blocks + per - 1) // per
-            if real != splits or (splits > 1 and per < 4):
-                continue
-            rounds = (tiles * splits + n_sms - 1) // n_sms
-            cost = rounds * (per * step + fixed)
-            if best_cost is None or cost < best_cost:
-                best, best_cost = (bn, splits), cost
+            if (k_blocks + per - 1) // per != splits or (splits > 1 and per < 4):
+                continue                                   # an empty split, or splits too short to fill the ring
+            rounds = (m_tiles * n_tiles * splits + workers - 1) // workers
+            products = rounds * per * (step_w * bn + step_0)
+            adds = per_mb * splits * m_tiles * tile_tokens * n_tiles * bn * 4 / 1e6
+            yield launch + (products * products + adds * adds) ** 0.5 + write_out * bn / 256, bn, splits
+
+
+def gemm_rows_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):
+    """(rows of W per tile, K splits) for a prompt product that adds into the stream on the one-SM form.  Such products
+    (the output and down projections) have few columns, so their tiles alone leave SMs idle: the K range is then shared
+    out over several blocks per tile, which all add atomically."""
+    _, bn, splits = min(_add_plans("rows", n_tok, n_out, k, n_sms))
+    return bn, splits
+
+
+def gemm_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):
+    """("rows" or "pair", rows of W per tile, K splits): the cheapest plan of either form by the fitted costs above.
+    The paired form wins from about 1,536 columns at 2,048 tokens on (43 against 47 us for 1,536 x 8,960, 198 against
+    206 us for 3,584 x 18,944) and everywhere at 8,192 tokens; below that the one-SM form has the tiles to fill the GPU."""
+    best = ("rows",) + tuple(gemm_rows_add_plan(n_tok, n_out, k, n_sms))
+    if n_sms >= 2 and n_tok > 64 and n_out % 16 == 0 and k % 8 == 0:
+        rows_cost = min(_add_plans("rows", n_tok, n_out, k, n_sms))[0]
+        cost, bn, splits = min(_add_plans("pair", n_tok, n_out, k, n_sms))
+        if cost < rows_cost:
+            best = ("pair", bn, splits)
     return best
 
 

@@ -131,8 +131,18 @@ def bench_gemm(args) -> None:
                       kv=bindings.KVView(k_pool, v_pool, 0, table, 64, KV, hd))
             out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
         splits = args.splits_given or None       # None: the plan's choice (adding epilogue) or none
-        fn = lambda i: kernels.gemm_tcgen05_rows(x, ws[i % C], out, epi, args.block_tokens, splits, **kw)
-        report(f"tcgen05 product, prompt form T={T} N={N} K={K} epilogue={args.epilogue} tile rows={args.block_tokens} splits={splits}", fn, args, nbytes + out.numel() * out.element_size(), flops)
+        if args.pair:
+            if epi == 2:
+                raise SystemExit("the paired form has no Q/K/V epilogue")
+            fn = lambda i: kernels.gemm_tcgen05_pair(x, ws[i % C], out, epi, args.block_tokens or 256, splits or 1)
+        elif epi != 2 and args.block_tokens is None and splits is None:
+            fn = lambda i: kernels.gemm_prompt(x, ws[i % C], out, epi)          # the form and plan the engine takes
+        else:
+            fn = lambda i: kernels.gemm_tcgen05_rows(x, ws[i % C], out, epi, args.block_tokens, splits, **kw)
+        form = "prompt form with a pair of SMs per tile" if args.pair else "prompt form"
+        if epi == 3 and not args.pair and args.block_tokens is None and splits is None:
+            form += " by plan %s" % (kernels.gemm_add_plan(T, N, K, torch.cuda.get_device_properties(0).multi_processor_count),)
+        report(f"tcgen05 product, {form} T={T} N={N} K={K} epilogue={args.epilogue} tile rows={args.block_tokens} splits={splits}", fn, args, nbytes + out.numel() * out.element_size(), flops)
         return
     if epi == 0:
         out = torch.empty(args.splits, T, N, dtype=torch.float32, device=DEV)
@@ -277,6 +287,7 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--copies", type=int, default=24)
     ap.add_argument("--library", action="store_true")
     ap.add_argument("--rows-form", action="store_true", help="the prompt form of the product (tokens as the M operand)")
+    ap.add_argument("--pair", action="store_true", help="with --rows-form: a pair of SMs on every tile of 256 tokens (cta_group::2)")
     ap.add_argument("--once", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--seqs", type=int, default=8)

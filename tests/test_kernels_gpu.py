@@ -433,8 +433,8 @@ def test_prompt_product_with_bias_rotation_and_cache_write(H, KV, hd, T, bn):
                                               (300, 464, 200, 224, 1), (2048, 896, 896, None, None), (300, 272, 1000, 160, 3),
                                               (129, 48, 4864, 128, 8), (1000, 896, 4864, 224, 5), (70, 144, 520, 128, 2)])
 def test_prompt_product_adding_into_the_stream(T, N, K, bn, splits):
-    """Without a K split plain reads and writes; with one (given, or chosen by the plan when the tiles alone would leave
-    SMs idle) 16-byte atomic adds.  A last split shorter than the others, tiles beyond the matrix's edge in both
+    """16-byte atomic adds into the stream, with and without a K split (given, or chosen by the plan when the tiles
+    alone would leave SMs idle).  A last split shorter than the others, tiles beyond the matrix's edge in both
     directions, more tiles than blocks."""
     g = torch.Generator().manual_seed(N + K)
     x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
@@ -451,6 +451,13 @@ def test_prompt_product_shares_out_the_k_range_when_its_tiles_are_few():
     assert kernels.gemm_rows_add_plan(2048, 896, 4864, 148)[1] > 1            # 64 tiles on 148 SMs
     assert kernels.gemm_rows_add_plan(65536, 896, 4864, 148)[1] == 1          # tiles enough
     assert kernels.gemm_rows_add_plan(128, 64, 176, 148) == (128, 1)          # three K steps: nothing to share
+    assert kernels.gemm_add_plan(2048, 896, 896, 148)[0] == "rows"            # few columns: the one-SM form has the tiles
+    assert kernels.gemm_add_plan(2048, 3584, 18944, 148)[0] == "pair" and kernels.gemm_add_plan(8192, 896, 4864, 148)[0] == "pair"
+    assert kernels.gemm_add_plan(2048, 3584, 18944, 1)[0] == "rows"           # no pair without a second SM
+    for n_tok, n_out, k in ((100, 48, 8), (3000, 1536, 8960), (70000, 160, 72)):  # every plan is one the kernels take
+        form, bn, splits = kernels.gemm_add_plan(n_tok, n_out, k, 148)
+        per = -(-(-(-k // 64)) // splits)
+        assert bn in (128, 160, 192, 224, 256) and (splits - 1) * per < -(-k // 64)
     x = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(kernels.KernelError, match="size"):                     # a K split is for the adding epilogue only
         kernels.gemm_tcgen05_rows(x, torch.zeros(48, 64, dtype=torch.bfloat16, device=DEV), torch.empty(128, 48, device=DEV), 0, 128, 2)
@@ -797,3 +804,18 @@ def test_paired_prompt_product_is_chosen_when_its_tiles_fill_the_gpu_and_refuses
     kernels.gemm_tcgen05_rows(x, w, b, 0, 160)
     kernels.check_gemm_status(DEV)
     assert torch.equal(a, b)
+
+
+def test_adding_prompt_product_through_the_plan_on_either_form():
+    """`gemm_prompt` with the adding epilogue at sizes where the plan takes the paired form with a K split, and at
+    sizes where it takes the one-SM form."""
+    for T, N, K, form in ((2048, 1536, 4480, "pair"), (1100, 896, 896, "rows")):
+        assert kernels.gemm_add_plan(T, N, K, torch.cuda.get_device_properties(0).multi_processor_count)[0] == form
+        g = torch.Generator().manual_seed(T + N)
+        x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+        base = torch.randn(T, N, generator=g)
+        out = base.clone().to(DEV)
+        kernels.gemm_prompt(x.to(DEV), w.to(DEV), out, 3)
+        kernels.check_gemm_status(DEV)
+        close(out, base.double() + x.double() @ w.double().t(), 3 * math.sqrt(K) * 2.0 ** -24)
