@@ -11,14 +11,14 @@
 // (token, query head) pair, and all rows of a block share one kv head, so the G query heads
 // of a group ride on the same key and value tiles (for 14 heads on 2 kv heads: 9 tokens x 7
 // heads per 64-row tile).  Keys come in tiles of 64, one cache page, copied to shared
-// memory with cp.async, two to four tiles ahead.
+// memory with cp.async, two to four tiles ahead (the single-token kernel further down: by TMA at head sizes 64 and 128).
 //   RT = 4: each warp owns 16 rows and walks all 64 keys of a tile (prompts, chunks).
 //   RT = 1: the block has 16 rows (one decoded token's group of heads) and the four warps
 //           split each tile's keys 4 x 16, merging their partial results at the end.
 //   RT = 2: 32 rows, two warps per row tile, 2 x 32 keys.
 // A sequence's key range can also be split over blocks (n_splits); partial (max, sum,
 // weighted values) then go to scratch memory and mlc_attention_combine merges them.
-#include "common.cuh"
+#include "tcgen05.cuh"      // mbarriers with bounded waits, TMA tile loads, tensor maps
 
 #ifndef MLC_HEAD_DIM
 #error "compile with -DMLC_HEAD_DIM=<head size>"
@@ -56,6 +56,7 @@ struct MmaArgs {
     int cluster_merge;        // decode kernel: the blocks of one row tile form a cluster and merge their key splits through
                               // distributed shared memory instead of part_ml / part_o and a second kernel
     unsigned long long* stamps;   // decode kernel: null, or [blocks][12] nanosecond stamps of each block's phases
+    int* status;              // decode kernel with TMA loads: where a wait that ran out leaves its code (31)
 };
 
 __device__ __forceinline__ unsigned long long stamp_ns() {
@@ -75,6 +76,14 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const bf16* p) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_at(unsigned (&r)[4], unsigned s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_at(unsigned (&r)[4], unsigned s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const bf16* p) {
@@ -410,6 +419,7 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
 // sub-tiles of DKT keys (keys and values) into its own three shared-memory stages, computes all 16
 // rows against them, and never meets the other warps until the end, where the warps' partial
 // results are merged.  Warp w of DNW takes sub-tiles w, w + DNW, w + 2 DNW, ... of the block's key range.
+// The copies are TMA loads at head sizes 64 and 128 (below) and cp.async at the others.
 constexpr int DNW = (HD <= 128) ? 8 : 4;                         // warps per block: two per scheduler hide each other's latencies
 constexpr int DKT = (HD <= 64) ? 32 : 16;                        // keys per sub-tile
 constexpr int D_STAGE = DKT * STRIDE;                            // elements per stage and operand
@@ -419,20 +429,40 @@ constexpr int D_TILES_STAGED = 512;                              // page numbers
 constexpr int D_MAX_CLUSTER = 16;                                // the largest cluster there is
 // Cluster merge: what the other blocks of a cluster send this one.  Its share of the 16 x HD outputs (at most a
 // D_MAX_CLUSTER-th of them, rounded up, in four-float pieces) from every block, and every block's (maximum, sum) per row.
+// Head sizes 64 and 128: a sub-tile's keys and values come by TMA (cp.async.bulk.tensor, one thread of the warp asks for a
+// whole sub-tile, an mbarrier per warp and stage says when it has landed).  A row's 128-byte spans lie apart
+// ([span][key][128 bytes]) and the 16-byte pieces of a span are swapped by the key's number modulo 8 (the 128-byte
+// swizzle), which keeps ldmatrix free of bank conflicts without padding.  Other head sizes: cp.async into padded rows.
+constexpr bool D_TMA = (HD == 64 || HD == 128);
+constexpr int D_SPANS = HD / 64;                                 // 128-byte spans per row (TMA form)
+constexpr int D_OPER_BYTES = DKT * HD * 2;                       // keys (or values) of one sub-tile, TMA form
+constexpr int D_STAGE_BYTES = D_TMA ? 2 * D_OPER_BYTES : 2 * D_STAGE * (int)sizeof(bf16);
+constexpr int D_KV_BYTES = DNW * D_NSTAGE * D_STAGE_BYTES;
+constexpr int D_Q_BYTES = 16 * STRIDE * (int)sizeof(bf16);
+constexpr int D_KV_OFF = D_TMA ? ((D_Q_BYTES + 1023) / 1024) * 1024 : D_Q_BYTES;      // swizzled tiles want 1024-byte alignment
 constexpr int D_VPR = HD / 4;                                    // four-float pieces per row
 constexpr int D_RECV_O_BYTES = (16 * D_VPR + D_MAX_CLUSTER) * 16;
 constexpr int D_RECV_BYTES = D_RECV_O_BYTES + D_MAX_CLUSTER * 16 * 8;
-constexpr size_t D_SMEM_BYTES = (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16) + D_RECV_BYTES;
+constexpr int D_BAR_BYTES = DNW * D_NSTAGE * 8;                  // TMA form: an mbarrier per warp and stage
+constexpr size_t D_SMEM_BYTES = (size_t)D_KV_OFF + D_KV_BYTES + D_RECV_BYTES + D_BAR_BYTES + (D_TMA ? 1024 : 0) /* alignment slack */;
 static_assert(D_SMEM_BYTES + D_TILES_STAGED * 4 <= 227 * 1024, "shared memory of a block");
 
+// Shared-memory address of the 16-byte piece `piece` of key `row` in a TMA-form operand tile.
+__device__ __forceinline__ unsigned d_swizzled(unsigned oper, int row, int piece) {
+    return oper + (unsigned)((piece >> 3) * (DKT * 128) + row * 128 + (((piece & 7) ^ (row & 7)) << 4));
+}
+
 __global__ void __launch_bounds__(DNW * 32)
-attention_decode_kernel(MmaArgs a, PagedKV c) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, MmaArgs a, PagedKV c) {
+    extern __shared__ __align__(16) unsigned char smem_dyn[];
+    // the TMA form wants its tiles on 1024-byte boundaries of the shared address space
+    unsigned char* smem_raw = D_TMA ? smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u) : smem_dyn;
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][STRIDE]
-    bf16* KVs = Qs + 16 * STRIDE;                                 // [DNW warps][D_NSTAGE][K | V][DKT][STRIDE]
+    bf16* KVs = reinterpret_cast<bf16*>(smem_raw + D_KV_OFF);     // [DNW warps][D_NSTAGE][K | V]: [DKT][STRIDE], or the TMA form
     __shared__ int tile_pages[D_TILES_STAGED];
     // where the cluster's other blocks write; nothing else of this block lives here, so they may write at any time
-    unsigned char* recv = smem_raw + (size_t)(16 * STRIDE + DNW * D_NSTAGE * 2 * D_STAGE) * sizeof(bf16);
+    unsigned char* recv = smem_raw + D_KV_OFF + D_KV_BYTES;
+    const unsigned bars = smem_u32(recv) + D_RECV_BYTES;          // [DNW][D_NSTAGE] mbarriers (TMA form)
 
     unsigned long long* const stamps = MLC_STAMPS_OR_NULL((a.stamps != nullptr && threadIdx.x == 0)
         ? a.stamps + 12ull * (blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z)) : nullptr);
@@ -453,6 +483,10 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     // queries, and a sub-tile that holds a key of this step, wait for it.
     for (int t = tid; t < c.pages_per_seq && t < D_TILES_STAGED; t += DNW * 32)
         tile_pages[t] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
+    if (D_TMA && tid == 0) {
+        for (int i = 0; i < DNW * D_NSTAGE; ++i) mbar_init(bars + 8u * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     const int start = a.start_pos[b];
     int seq_tok0, q_len;
     if (a.one_token_each) {
@@ -477,10 +511,32 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     const int st_begin = my_begin * SUB, st_end = my_end * SUB;
     const bf16* kp = (const bf16*)c.k_pool;
     const bf16* vp = (const bf16*)c.v_pool;
-    bf16* my_stages = KVs + warp * D_NSTAGE * 2 * D_STAGE;
+    bf16* my_stages = reinterpret_cast<bf16*>(reinterpret_cast<unsigned char*>(KVs) + warp * D_NSTAGE * D_STAGE_BYTES);
+    const unsigned my_stages_s = smem_u32(my_stages);
+    const unsigned my_bars = bars + 8u * (unsigned)(warp * D_NSTAGE);
+    auto page_of = [&](int tile) {
+        return (tile < D_TILES_STAGED) ? tile_pages[tile] : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
+    };
     auto load_sub = [&](int stage, int st) {
         const int tile = st / SUB;
-        const int page = (tile < D_TILES_STAGED) ? tile_pages[tile] : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
+        const int page = page_of(tile);
+        if (D_TMA) {
+            // one thread asks for the sub-tile's keys and values, whole: rows of the pool seen as [pages x kv heads x 64][HD].
+            // Keys outside the row tile's range (beyond the sequence's end as a rule) come along and are dealt with
+            // when the sub-tile is used.
+            if (lane == 0) {
+                const int row0 = (max(page, 0) * c.kv_heads + kvh) * TILE + (st % SUB) * DKT;
+                const unsigned bar = my_bars + 8u * (unsigned)stage;
+                const unsigned kd = my_stages_s + (unsigned)(stage * D_STAGE_BYTES);
+                mbar_expect_tx(bar, 2 * D_OPER_BYTES);
+#pragma unroll
+                for (int h = 0; h < D_SPANS; ++h) {
+                    tma_load_2d(kd + h * (DKT * 128), &map_k, h * 64, row0, bar);
+                    tma_load_2d(kd + D_OPER_BYTES + h * (DKT * 128), &map_v, h * 64, row0, bar);
+                }
+            }
+            return;
+        }
         const long long base = c.entry_offset + (((long long)max(page, 0) * c.kv_heads + kvh) * TILE + (st % SUB) * DKT) * HD;
         bf16* kd = my_stages + stage * 2 * D_STAGE;
         bf16* vd = kd + D_STAGE;
@@ -505,7 +561,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         const int sp = st + DNW * p;
         if (early == p && (sp >= st_end || sp * DKT + DKT - 1 < start)) {
             if (sp < st_end) load_sub(p, sp);
-            cp_async_commit();
+            if (!D_TMA) cp_async_commit();
             early = p + 1;
         }
     }
@@ -530,7 +586,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
     for (int p = 0; p < D_NSTAGE; ++p) {
         if (p >= early) {
             if (st + DNW * p < st_end) load_sub(p, st + DNW * p);
-            cp_async_commit();
+            if (!D_TMA) cp_async_commit();
         }
     }
 
@@ -573,12 +629,32 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         if (it > 0) {
             // every stage was filled before the loop; the stage read out in the last round takes the sub-tile two on
             if (st + DNW * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + DNW * (D_NSTAGE - 1));
-            cp_async_commit();
+            if (!D_TMA) cp_async_commit();
         }
-        cp_async_wait<D_NSTAGE - 1>();
+        const int key0 = st * DKT;
+        const unsigned kt_s = my_stages_s + (unsigned)(stage * D_STAGE_BYTES), vt_s = kt_s + D_OPER_BYTES;     // TMA form
+        if (D_TMA) {
+            if (!mbar_wait(my_bars + 8u * (unsigned)stage, (unsigned)(it / D_NSTAGE) & 1u, a.status, 31)) break;
+            // keys outside the row tile's range, or of a page the sequence does not hold, count as zeros (their scores
+            // are masked below, but a value row that is not a number would spoil 0 · v)
+            const int page = page_of(st / SUB);
+            if (page < 0 || key0 < lo_block || key0 + DKT - 1 > p_last) {
+                for (int idx = lane; idx < DKT * CPR; idx += 32) {
+                    const int j = idx / CPR, ch = idx % CPR;
+                    const int kpos = key0 + j;
+                    if (page < 0 || kpos < lo_block || kpos > p_last) {
+                        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d_swizzled(kt_s, j, ch)), "r"(z.x), "r"(z.y), "r"(z.z), "r"(z.w) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d_swizzled(vt_s, j, ch)), "r"(z.x), "r"(z.y), "r"(z.z), "r"(z.w) : "memory");
+                    }
+                }
+                fence_async_shared();              // before a later TMA load writes the stage again
+            }
+        } else {
+            cp_async_wait<D_NSTAGE - 1>();
+        }
         __syncwarp();
 
-        const int key0 = st * DKT;
         if (key0 <= p_last && key0 + DKT - 1 >= lo_block) {
             const bf16* kt = my_stages + stage * 2 * D_STAGE;
             const bf16* vt = kt + D_STAGE;
@@ -597,7 +673,8 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
 #pragma unroll
                 for (int jp = 0; jp < D_NT_S / 2; ++jp) {
                     unsigned bfr[4];
-                    ldmatrix_x4(bfr, kt + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+                    if (D_TMA) ldmatrix_x4_at(bfr, d_swizzled(kt_s, jp * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 2 + ((lane >> 3) & 1)));
+                    else ldmatrix_x4(bfr, kt + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
                     mma_bf16(sc[2 * jp], af, bfr[0], bfr[1]);
                     mma_bf16(sc[2 * jp + 1], af, bfr[2], bfr[3]);
                 }
@@ -666,7 +743,8 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
 #pragma unroll
                 for (int jp = 0; jp < NT_O / 2; ++jp) {
                     unsigned bfr[4];
-                    ldmatrix_x4_trans(bfr, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + jp * 16 + (lane >> 4) * 8);
+                    if (D_TMA) ldmatrix_x4_trans_at(bfr, d_swizzled(vt_s, kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 2 + (lane >> 4)));
+                    else ldmatrix_x4_trans(bfr, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + jp * 16 + (lane >> 4) * 8);
                     mma_bf16(o[2 * jp], pf, bfr[0], bfr[1]);
                     mma_bf16(o[2 * jp + 1], pf, bfr[2], bfr[3]);
                 }
@@ -674,7 +752,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
         }
         __syncwarp();                      // the stage is read out before the next copy into it is issued
     }
-    cp_async_wait<0>();
+    if (!D_TMA) cp_async_wait<0>();
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
@@ -690,7 +768,7 @@ attention_decode_kernel(MmaArgs a, PagedKV c) {
                                                                     // start on the same one)
     float* Oc = reinterpret_cast<float*>(KVs);                      // [DNW warps][16][OS]
     float* MLc = Oc + DNW * 16 * OS;                                // [DNW warps][16][2]
-    static_assert(DNW * D_NSTAGE * 2 * D_STAGE * sizeof(bf16) >= (DNW * 16 * OS + DNW * 16 * 2 + 32 + DNW * 16) * sizeof(float), "merge buffer");
+    static_assert(D_KV_BYTES >= (DNW * 16 * OS + DNW * 16 * 2 + 32 + DNW * 16) * sizeof(float), "merge buffer");
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         const int r16 = (lane >> 2) + 8 * rr;
@@ -833,8 +911,21 @@ static int decode_clusters_resident(int size) {
     return cached[size];
 }
 
-static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStream_t s) {
+static int launch_decode(const MmaArgs& a, const PagedKV& c, int pool_pages, dim3 grid, cudaStream_t s) {
     const size_t smem = D_SMEM_BYTES;
+    // the cache entry's keys and values as matrices [pages x kv heads x 64 keys][HD], read in boxes of DKT keys x 64 columns
+    CUtensorMap map_k, map_v;
+    if (D_TMA) {
+        if (pool_pages < 1 || a.status == nullptr) return MLC_ERR_BAD_SIZE;
+        const long long rows = (long long)pool_pages * c.kv_heads * TILE;
+        int rc = cached_map_2d(&map_k, (const bf16*)c.k_pool + c.entry_offset, rows, HD, 64, DKT);
+        if (rc) return rc;
+        rc = cached_map_2d(&map_v, (const bf16*)c.v_pool + c.entry_offset, rows, HD, 64, DKT);
+        if (rc) return rc;
+    } else {
+        memset(&map_k, 0, sizeof(map_k));
+        memset(&map_v, 0, sizeof(map_v));
+    }
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -842,7 +933,7 @@ static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStre
         configured = true;
     }
     if (!a.cluster_merge) {
-        cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(DNW * 32), smem, s, a, c);
+        cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(DNW * 32), smem, s, map_k, map_v, a, c);
         return e == cudaSuccess ? 0 : (int)e;
     }
     if (decode_clusters_resident(a.n_splits) < 1) return MLC_ERR_UNSUPPORTED;
@@ -860,7 +951,7 @@ static int launch_decode(const MmaArgs& a, const PagedKV& c, dim3 grid, cudaStre
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel, a, c);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel, map_k, map_v, a, c);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
@@ -905,13 +996,15 @@ extern "C" int mlc_attention_decode_stamps(unsigned long long* p) {
 
 // q, out: bfloat16 [n_tokens][q_heads][HD]; the cache pools hold bfloat16 in pages of 64 tokens.
 // row_tiles: 1, 2 or 4 (16, 32 or 64 rows per block); with row_tiles 1, warp_private != 0 picks the
-// kernel whose warps each stream their own sub-tiles (the decode form).  n_splits > 1 writes partial results to
+// kernel whose warps each stream their own sub-tiles (the decode form; at head sizes 64 and 128 by TMA, for which it
+// needs pool_pages, the pages of a cache entry, and status, one int on the device that is 0 before the call and holds
+// 31 afterwards if a bounded wait for a sub-tile ran out).  n_splits > 1 writes partial results to
 // part_ml / part_o (sizes as for mlc_attention_simt) and leaves `out` to the combine kernel.
 extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
                                  int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
                                  int window, int row_tiles, int warp_private, int n_splits, float* part_ml, float* part_o,
                                  void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
-                                 int pages_per_seq, int page_size, void* stream) {
+                                 int pages_per_seq, int page_size, int pool_pages, int* status, void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd != HD || page_size != TILE) return MLC_ERR_BAD_SIZE;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
@@ -941,6 +1034,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     a.cluster_merge = cluster_merge ? 1 : 0;
     a.one_token_each = (max_q_len == 1 && n_tokens == n_seqs) ? 1 : 0;
     a.stamps = g_decode_stamps;
+    a.status = status;
     const long long gy = (long long)kv_heads * a.head_chunks * n_splits;
     if (gy > 65535) return MLC_ERR_BAD_SIZE;
     PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, kv_heads, hd};
@@ -948,6 +1042,6 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     cudaStream_t s = (cudaStream_t)stream;
     if (row_tiles == 4) return launch_mma<4>(a, c, grid, s);
     if (row_tiles == 2) return launch_mma<2>(a, c, grid, s);
-    if (warp_private) return launch_decode(a, c, grid, s);
+    if (warp_private) return launch_decode(a, c, pool_pages, grid, s);
     return launch_mma<1>(a, c, grid, s);
 }

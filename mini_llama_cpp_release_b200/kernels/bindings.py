@@ -349,7 +349,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     if lib is None:
         lib = _build.attention_library(head_dim)
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
-        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, P]
+        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, I, P, P]
         lib.mlc_attention_mma.restype = c_int
         lib.mlc_attention_mma_head_dim.restype = c_int
         lib.mlc_attention_decode_clusters_resident.argtypes = [I]
@@ -467,7 +467,8 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
                                  n_tokens, max_q_len, q_heads, kv.kv_heads, hd, float(scale), int(window), row_tiles,
                                  1 if warp_private else 0, n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(),
                                  kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq,
-                                 kv.page_size, _stream()), "tensor-core attention")
+                                 kv.page_size, int(kv.k_pool.shape[1]), gemm_status(q.device).data_ptr(), _stream()),
+           "tensor-core attention")
     if n_splits > 1 and not in_cluster:
         _check(core().mlc_attention_combine(part_ml.data_ptr(), part_o.data_ptr(), n_tokens * q_heads, n_splits, hd,
                                             out.data_ptr(), dtype_code(out.dtype), _stream()), "attention combine")
@@ -516,7 +517,7 @@ def check_gemm_status(device: torch.device) -> None:
                    3: "the matrix product's epilogue", 11: "the attention kernel's TMA loader",
                    12: "the attention kernel's tensor-core issuer", 13: "the attention kernel's softmax rows",
                    21: "the prompt product's TMA loader", 22: "the prompt product's tensor-core issuer",
-                   23: "the prompt product's epilogue", 41: "the paired prompt product's TMA loader",
+                   23: "the prompt product's epilogue", 31: "the single-token attention kernel's wait for keys and values", 41: "the paired prompt product's TMA loader",
                    42: "the paired prompt product's tensor-core issuer or relay", 43: "the paired prompt product's epilogue"}.get(code, str(code))
             raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier ({who}); its output is not valid")
 
