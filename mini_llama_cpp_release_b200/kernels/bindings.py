@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from dataclasses import dataclass
 from typing import Optional
@@ -532,6 +533,7 @@ def _sm_count(device: torch.device) -> int:
     return _sm_counts[key]
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_block_tokens(n_tok: int, row_tiles: int, n_sms: int) -> int:
     for bn in (16, 32, 64, 128):
         if n_tok <= bn:
@@ -544,6 +546,7 @@ def gemm_rows_takes(n_tok: int, n_out: int, k: int) -> bool:
     return n_tok > 64 and n_out % 16 == 0 and k % 8 == 0
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_rows_block(n_tok: int, n_out: int, n_sms: int) -> int:
     """Rows of W per tile for the prompt form: the persistent blocks walk the tiles in rounds of `n_sms`, and a last
     round with a few tiles costs a whole round, so the width is the one whose rounds x width is smallest (wider
@@ -639,6 +642,7 @@ def _add_plans(form: str, n_tok: int, n_out: int, k: int, n_sms: int):
             yield launch + (products * products + adds * adds) ** 0.5 + write_out * bn / 256, bn, splits
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_rows_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):
     """(rows of W per tile, K splits) for a prompt product that adds into the stream on the one-SM form.  Such products
     (the output and down projections) have few columns, so their tiles alone leave SMs idle: the K range is then shared
@@ -647,6 +651,7 @@ def gemm_rows_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):
     return bn, splits
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_add_plan(n_tok: int, n_out: int, k: int, n_sms: int):
     """("rows" or "pair", rows of W per tile, K splits): the cheapest plan of either form by the fitted costs above.
     The paired form wins from about 1,536 columns at 2,048 tokens on (43 against 47 us for 1,536 x 8,960, 198 against
