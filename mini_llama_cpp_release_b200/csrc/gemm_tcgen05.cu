@@ -26,6 +26,12 @@
 //
 //   ADD       adds y into a float32 [token][row] tensor (the residual stream) with atomic adds,
 //             so that any number of K splits can feed it (src/forward.cpp:772, 779).
+// The Q/K/V product of a few tokens has few tiles (nine at 1,152 rows), and a block alone draws its 128 rows of W
+// at one SM's pace.  Its K range can therefore be shared out over a thread-block cluster of 2 or 4 blocks, one tile
+// and one K range per block: every block fills an accumulator with its part, each of its four epilogue warps
+// stores its 32 rows' partial sums into the shared memory of the block that owns those rows (rank = rows' quarter
+// · blocks / 4) and arrives on that block's barrier; the owner's warp adds the parts up in a fixed order and
+// runs the epilogue (bias, rotation, cache write) on its rows.
 // Blocks are persistent: at most one per SM, each walks output tiles t, t + blocks, ...; a block keeps two
 // accumulators in tensor memory, so the epilogue of one tile runs while the tensor cores fill the next.
 // Tiles of 64 tokens and more have two groups of four epilogue warps that share out the tokens.
@@ -40,7 +46,11 @@ constexpr int G_BM = 128;
 constexpr int G_BK = 64;
 constexpr int G_A_BYTES = G_BM * G_BK * 2;                 // 16 KiB per stage
 
-enum { EPI_STORE = 0, EPI_SILU_MUL = 1, EPI_QKV = 2, EPI_ADD = 3 };
+enum { EPI_STORE = 0, EPI_SILU_MUL = 1, EPI_QKV = 2, EPI_ADD = 3,
+       EPI_QKV_CLUSTER = 4 };      // QKV whose tiles' K range is shared out over a cluster: a kernel of its own, so that the
+                                   // plain form keeps its registers (166 against 157 with the exchange compiled in, and a
+                                   // decode step of the 0.5B sizes 0.02 ms longer)
+__host__ __device__ constexpr bool qkv_epilogue(int epi) { return epi == EPI_QKV || epi == EPI_QKV_CLUSTER; }
 
 struct GemmArgs {
     void* out;                 // STORE / SILU_MUL: [splits][tokens][n_out or n_out/2]; QKV: q [tokens][q_heads*hd]
@@ -52,6 +62,7 @@ struct GemmArgs {
     long long split_stride;    // elements between the output slices of two splits
     int* status;
     int m_tiles, n_tiles, n_splits;   // the grid of output tiles the persistent blocks walk
+    int cluster_split;         // QKV epilogue: the n_splits blocks of a tile are a cluster and merge their parts (one tile per block)
     unsigned long long* timing;  // [blocks][8] nanosecond stamps of a block's phases, or null; read only in builds with -DMLC_PHASE_STAMPS
     // QKV epilogue
     const float* bias;         // [n_out] in the stored row order, or null
@@ -77,10 +88,18 @@ template <int BN, int EPI> struct GemmShape {
     static constexpr int TMEM_COLS = 2 * ISSUERS * ACC_COLS;          // per issuer two accumulators: one is read out while the other fills
     static constexpr int META_BYTES = BN * 16;                        // per token: position, cache offset (QKV epilogue)
     // SILU_MUL: [8 or 4 warps][tokens][16 outputs] bfloat16; QKV: [8 or 4 warps][2 buffers][16 tokens][32 outputs] bfloat16
-    static constexpr int STAGING_BYTES = (EPI == EPI_SILU_MUL) ? 128 * BN : (EPI == EPI_QKV ? EPI_GROUPS * 4 * 2048 : 0);
+    static constexpr int STAGING_BYTES = (EPI == EPI_SILU_MUL) ? 128 * BN : (qkv_epilogue(EPI) ? EPI_GROUPS * 4 * 2048 : 0);
     // QKV: cos and sin of each warp's 16 rotation pairs for the tokens of its group, [warps][tokens][16] float2
-    static constexpr int ROPE_BYTES = (EPI == EPI_QKV && BN <= 128) ? 4 * BN * 128 : 0;
-    static constexpr int BAR_BYTES = 512;                           // up to 16 stages: full 0-15, empty 16-31, accumulators 32-35, slot 36
+    static constexpr int ROPE_BYTES = (qkv_epilogue(EPI) && BN <= 128) ? 4 * BN * 128 : 0;
+    // QKV with 16-token tiles: what the blocks of a cluster send this one, [source block][warp of this block's rows][lane][16 tokens]
+    // float32: 2 blocks x 2 warps or 4 blocks x 1 warp, 8 KiB.  It lies over the staging tiles: a warp that owns rows
+    // reads the parts sent to it (slots source x warps + its number among the owner's warps) before it stages
+    // anything, its staging tile (2 KiB at its quarter's number) is one of its own slots, and warps that own no rows
+    // stage nothing.  (With 8 KiB of its own the block passed 164 KiB, the SM's next smaller split between L1 and
+    // shared memory, and the whole decode step took 4 % longer.)
+    static constexpr int RECV_BYTES = (EPI == EPI_QKV_CLUSTER && BN == 16) ? 4 * 32 * 16 * 4 : 0;
+    static_assert(RECV_BYTES <= STAGING_BYTES, "the received parts lie over the staging tiles");
+    static constexpr int BAR_BYTES = 512;                           // up to 16 stages: full 0-15, empty 16-31, accumulators 32-35, slot 36, parts received 37
     static constexpr int FIXED_BYTES = STAGING_BYTES + ROPE_BYTES + BAR_BYTES + META_BYTES + 1024 /* alignment slack */;
     static constexpr int STAGES_FIT = (227 * 1024 - FIXED_BYTES) / STAGE_BYTES;
     // Few tokens: the whole K range of a 896-wide layer (14 steps) fits the ring, so that all of a tile's weights are
@@ -100,10 +119,20 @@ template <typename T> __device__ __forceinline__ void store_out(void* base, long
 struct TileCoord {
     int m0, n0, split, kb_begin, n_kb;
 };
+// CLUSTERS: the kernel variant can run as clusters that share a tile's K range (the others are spared the test and
+// the divisions: every role of every block works a tile's place out before it can ask for anything).
+template <bool CLUSTERS>
 __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& g, int t, int bn) {
     TileCoord c;
-    const int m_tile = t % g.m_tiles;
-    const int r = t / g.m_tiles;
+    int m_tile, r;
+    if (CLUSTERS && g.cluster_split) {         // the blocks of a cluster are neighbours: the splits of a tile run fastest
+        const int tile = t / g.n_splits;
+        m_tile = tile % g.m_tiles;
+        r = (tile / g.m_tiles) + g.n_tiles * (t % g.n_splits);
+    } else {
+        m_tile = t % g.m_tiles;
+        r = t / g.m_tiles;
+    }
     c.m0 = m_tile * G_BM;
     c.n0 = (r % g.n_tiles) * bn;
     c.split = r / g.n_tiles;
@@ -124,12 +153,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const unsigned b_base = base + S::STAGES * G_A_BYTES;
     constexpr unsigned staging_off = S::STAGES * S::STAGE_BYTES;
     constexpr unsigned rope_off = staging_off + S::STAGING_BYTES;
+    constexpr unsigned recv_off = staging_off;
     constexpr unsigned bar_off = rope_off + S::ROPE_BYTES;
     const unsigned bar_base = base + bar_off;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (16 + s); };
     auto acc_full_bar = [&](int b) { return bar_base + 8u * (32 + b); };
     auto acc_empty_bar = [&](int b) { return bar_base + 8u * (34 + b); };
+    const unsigned recv_bar = bar_base + 8u * 37;
+    const bool clustered = S::RECV_BYTES > 0 && g.cluster_split;
     const unsigned tmem_slot = bar_base + 8u * 36;
     volatile unsigned* tmem_slot_ptr = reinterpret_cast<volatile unsigned*>(smem_generic + bar_off + 8 * 36);
     int* tok_pos = reinterpret_cast<int*>(smem_generic + bar_off + S::BAR_BYTES);                         // [BN]
@@ -149,6 +181,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_init(acc_full_bar(b), S::ISSUERS);
             mbar_init(acc_empty_bar(b), 128 * EG);
         }
+        if (S::RECV_BYTES > 0) mbar_init(recv_bar, 128);             // every lane of the four warps that hold this block's rows, in whichever block
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -169,19 +202,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // The first ring of the first tile is requested by one lane per stage, so that the requests go out together
         // (a single thread needs some hundred clocks per request, and the activations' requests sit on the critical path
         // right after the wait).
-        const TileCoord c0 = tile_coord(g, blockIdx.x, BN);
+        const TileCoord c0 = tile_coord<(S::RECV_BYTES > 0)>(g, blockIdx.x, BN);
         const int early = (blockIdx.x < n_tiles_total) ? min(c0.n_kb, S::STAGES) : 0;
         if (lane < early) {
             mbar_expect_tx(full_bar(lane), S::STAGE_BYTES);
             tma_load_2d(a_base + lane * G_A_BYTES, &map_w, (c0.kb_begin + lane) * G_BK, c0.m0, full_bar(lane));
         }
+        if (clustered) cluster_sync_all();       // every block's barriers exist before any block arrives on another's
         grid_dependency_wait();
         if (lane < early) tma_load_2d(b_base + lane * S::B_BYTES, &map_x, (c0.kb_begin + lane) * G_BK, c0.n0, full_bar(lane));
         if (lane == 0) {
             int it = 0;
             bool alive = true;
             for (int t = blockIdx.x; t < n_tiles_total && alive; t += gridDim.x) {
-                const TileCoord c = tile_coord(g, t, BN);
+                const TileCoord c = tile_coord<(S::RECV_BYTES > 0)>(g, t, BN);
                 int i = 0;
                 if (it == 0) {
                     i = early;
@@ -201,15 +235,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (warp <= S::ISSUERS) {
         // ---------------- MMA issuers: tile j accumulates in buffer j % 2 (of each issuer) once the epilogue has emptied
         // it; issuer u takes the tile's K steps u, u + ISSUERS, ...
+        if (clustered) cluster_sync_all();
         if (lane == 0) {
             constexpr unsigned idesc = umma_idesc(BN);
             const int u = warp - 1;
             int it = 0, j = 0;
             bool ok = true;
             int total_it = 0;                  // K steps of all of this block's tiles: a stage is handed back only if needed again
-            for (int t = blockIdx.x; t < n_tiles_total; t += gridDim.x) total_it += tile_coord(g, t, BN).n_kb;
+            for (int t = blockIdx.x; t < n_tiles_total; t += gridDim.x) total_it += tile_coord<(S::RECV_BYTES > 0)>(g, t, BN).n_kb;
             for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
-                const TileCoord c = tile_coord(g, t, BN);
+                const TileCoord c = tile_coord<(S::RECV_BYTES > 0)>(g, t, BN);
                 const int buf = j & 1;
                 ok = mbar_wait(acc_empty_bar(buf), (((unsigned)j >> 1) & 1u) ^ 1u, g.status, 2);
                 if (!ok) break;
@@ -251,19 +286,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int eg = (warp - 1 - S::ISSUERS) >> 2;
         const int et = threadIdx.x - 32 * (1 + S::ISSUERS);            // 0 .. 128*EG-1
         constexpr int COLS_PER_GROUP = BN / EG;
+        if (clustered) cluster_sync_all();
         grid_dependency_wait();                // positions, page lists and the output buffers may come from earlier kernels
         // QKV through shared memory: when a warp's 32 rows are 16 rotation pairs of one head (head sizes in steps of 32)
         // and everything is bfloat16 and 16-byte aligned, results leave in 16-byte stores
-        const bool qkv_fast = EPI == EPI_QKV && g.out_dtype == MLC_DTYPE_BF16 && (g.hd & 31) == 0 &&
+        const bool qkv_fast = qkv_epilogue(EPI) && g.out_dtype == MLC_DTYPE_BF16 && (g.hd & 31) == 0 &&
                               ((((uintptr_t)g.out) | ((uintptr_t)g.cache.k_pool) | ((uintptr_t)g.cache.v_pool)) & 15) == 0 &&
                               (g.cache.entry_offset & 7) == 0;
         int j = 0, it_done = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
-            const TileCoord c = tile_coord(g, t, BN);
+            const TileCoord c = tile_coord<(S::RECV_BYTES > 0)>(g, t, BN);
             const int m0 = c.m0, n0 = c.n0, split = c.split;
             const int buf = j & 1;
-            if (EPI == EPI_QKV) {
+            if (qkv_epilogue(EPI)) {
                 for (int tt = et; tt < BN; tt += 128 * EG) {
                     int p = 0;
                     long long off = 0;
@@ -310,12 +346,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int it0 = it_done;
             it_done += c.n_kb;
             const int row = m0 + q * 32 + lane;
-            const float bias_row = (EPI == EPI_QKV && g.bias != nullptr && row < g.n_out) ? __ldg(g.bias + row) : 0.0f;
+            const float bias_row = (qkv_epilogue(EPI) && g.bias != nullptr && row < g.n_out) ? __ldg(g.bias + row) : 0.0f;
             // SiLU epilogue through shared memory: bfloat16 output, a full 16-output group inside the matrix, aligned rows
             const bool silu_staged = EPI == EPI_SILU_MUL && g.out_dtype == MLC_DTYPE_BF16 && ((g.n_out >> 1) & 7) == 0 &&
                                      (m0 + q * 32 + 32 <= g.n_out) && ((((uintptr_t)g.out) & 15) == 0);
             bf16* stage = reinterpret_cast<bf16*>(smem_generic + staging_off) + (eg * 4 + q) * COLS_PER_GROUP * 16;
-#pragma unroll (EPI == EPI_QKV ? 2 : 1)
+#pragma unroll (qkv_epilogue(EPI) ? 2 : 1)
             for (int c0 = eg * COLS_PER_GROUP; c0 < (eg + 1) * COLS_PER_GROUP; c0 += 16) {
                 float v[16];
                 if (S::ISSUERS == 1) tmem_load16(d_tmem + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
@@ -331,6 +367,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             for (int e = 0; e < 16; ++e) v[e] = have ? v[e] + w[e] : w[e];
                             have = true;
                         }
+                    }
+                }
+                if (S::RECV_BYTES > 0 && clustered) {
+                    // this warp's 32 rows x 16 tokens of partial sums go to the block that owns the rows; that block's
+                    // warp adds up what the cluster's blocks sent, in the order of their ranks
+                    const unsigned n_blocks = (unsigned)g.n_splits, rank = cluster_rank();
+                    const unsigned per_owner = 4u / n_blocks;                      // warps (quarters of the tile's rows) a block owns
+                    const unsigned owner = (unsigned)q / per_owner, mine_q = (unsigned)q % per_owner;
+                    const unsigned recv_local = base + recv_off;
+                    const unsigned dst = cluster_map(recv_local + (((rank * per_owner + mine_q) * 32u + (unsigned)lane) << 6), owner);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 16u * u), "f"(v[4 * u]), "f"(v[4 * u + 1]),
+                                     "f"(v[4 * u + 2]), "f"(v[4 * u + 3]) : "memory");
+                    mbar_arrive_remote(cluster_map(recv_bar, owner));
+                    if (owner != rank) continue;                    // another block finishes these rows
+                    ok = mbar_wait_cluster(recv_bar, 0u, g.status, 3);
+                    if (!ok) break;
+                    const float4* mine = reinterpret_cast<const float4*>(smem_generic + recv_off) + ((mine_q * 32 + lane) << 2);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        float4 sum = mine[u];
+                        for (unsigned r = 1; r < n_blocks; ++r) {
+                            const float4 x = mine[(r * per_owner * 32 << 2) + u];
+                            sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
+                        }
+                        v[4 * u] = sum.x; v[4 * u + 1] = sum.y; v[4 * u + 2] = sum.z; v[4 * u + 3] = sum.w;
                     }
                 }
                 if (EPI == EPI_ADD) {
@@ -493,7 +556,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
                 __syncwarp();                  // the staging tile is free for the warp's next tile
             }
-            if (EPI == EPI_QKV) asm volatile("bar.sync 1, %0;" ::"n"(128 * EG) : "memory");   // before the next tile's positions
+            if (qkv_epilogue(EPI)) asm volatile("bar.sync 1, %0;" ::"n"(128 * EG) : "memory");   // before the next tile's positions
         }
         if (stamps != nullptr && et == 0) stamps[5] = global_ns();                       // epilogues done
     }
@@ -523,6 +586,26 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmA
     }
     // persistent blocks: one per SM at most, each walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
     const long long tiles = (long long)g.m_tiles * g.n_tiles * g.n_splits;
+    if (g.cluster_split) {
+        // one tile and one K range per block; the n_splits blocks of a tile are neighbours and form a cluster
+        if (S::RECV_BYTES == 0 || tiles > 0x7fffffffll) return MLC_ERR_BAD_SIZE;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)tiles);
+        cfg.blockDim = dim3(S::THREADS);
+        cfg.dynamicSmemBytes = (size_t)S::SMEM_BYTES;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)g.n_splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, EPI>, mw, mx, g);
+        return e == cudaSuccess ? 0 : (int)e;
+    }
     const unsigned blocks = (unsigned)(tiles < n_sms ? tiles : n_sms);
     cudaError_t e = launch_pdl(gemm_tcgen05_kernel<BN, EPI>, dim3(blocks), dim3(S::THREADS), (size_t)S::SMEM_BYTES, s, mw, mx, g);
     return e == cudaSuccess ? 0 : (int)e;
@@ -544,11 +627,42 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 
 using namespace mlc;
 
+// How many clusters of `size` (2 or 4) blocks of the few-token Q/K/V product the GPU holds at once; 0 if such clusters
+// cannot be launched.  A tile count above this number runs in rounds.
+extern "C" int mlc_gemm_qkv_clusters_resident(int size) {
+    static int cached[5] = {0, 0, 0, 0, 0};
+    static bool known[5] = {false, false, false, false, false};
+    if (size != 2 && size != 4) return 0;
+    if (!known[size]) {
+        using S = GemmShape<16, EPI_QKV_CLUSTER>;
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<16, EPI_QKV_CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)size);
+            cfg.blockDim = dim3(S::THREADS);
+            cfg.dynamicSmemBytes = (size_t)S::SMEM_BYTES;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = (unsigned)size;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_kernel<16, EPI_QKV_CLUSTER>, &cfg) != cudaSuccess) n = 0;
+        }
+        (void)cudaGetLastError();
+        cached[size] = n;
+        known[size] = true;
+    }
+    return cached[size];
+}
+
 // x: bfloat16 [n_tok][K]; w: bfloat16 [n_out][K] (K a multiple of 8, both 16-byte aligned).
 // epilogue 0: out [n_splits][n_tok][n_out] (float32 or bfloat16): with n_splits > 1 the K range is shared out over
 // blocks and each leaves its partial sums in its own slice for the consumer to add; 1: out [n_tok][n_out/2],
 // n_splits must be 1;
-// 2: out = q [n_tok][q_heads*hd], k and v go to the cache, n_splits must be 1; 3: adds into out (float32
+// 2: out = q [n_tok][q_heads*hd], k and v go to the cache, n_splits 1, or 2 or 4 with block_tokens 16 (the K range
+// shared out over the blocks of a cluster, which merge before the epilogue); 3: adds into out (float32
 // [n_tok][n_out]) atomically, any n_splits.
 // block_tokens: 16, 32, 64, 128 or 256.  status: one int on the device, 0 before the call; a bounded
 // wait that ran out leaves 1 (loader), 2 (tensor cores) or 3 (epilogue) there.  timing: null, or
@@ -562,7 +676,10 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     if (n_tok <= 0 || n_out <= 0) return 0;
     if (K <= 0 || (K & 7) || (((uintptr_t)x | (uintptr_t)w) & 15)) return MLC_ERR_BAD_SIZE;
     if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
-    if (n_splits < 1 || (epilogue != EPI_STORE && epilogue != EPI_ADD && n_splits != 1) || status == nullptr) return MLC_ERR_BAD_SIZE;
+    // Q/K/V: 2 or 4 blocks of a cluster may share a tile's K range (16-token tiles only)
+    const bool cluster_split = epilogue == EPI_QKV && n_splits > 1;
+    if (cluster_split && !((n_splits == 2 || n_splits == 4) && block_tokens == 16)) return MLC_ERR_BAD_SIZE;
+    if (n_splits < 1 || (epilogue != EPI_STORE && epilogue != EPI_ADD && !cluster_split && n_splits != 1) || status == nullptr) return MLC_ERR_BAD_SIZE;
     if (epilogue == EPI_ADD && out_dtype != MLC_DTYPE_F32) return MLC_ERR_BAD_DTYPE;
     if (n_sms < 1) return MLC_ERR_BAD_SIZE;
     GemmArgs g{};
@@ -579,6 +696,7 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     g.m_tiles = (n_out + G_BM - 1) / G_BM;
     g.n_tiles = (n_tok + block_tokens - 1) / block_tokens;
     g.n_splits = n_splits;
+    g.cluster_split = cluster_split ? 1 : 0;
     if (epilogue == EPI_SILU_MUL && (n_out & 1)) return MLC_ERR_BAD_SIZE;
     if (epilogue == EPI_QKV) {
         if (hd <= 0 || (hd & 1) || n_out != (q_heads + 2 * kv_heads) * hd || positions == nullptr) return MLC_ERR_BAD_SIZE;
@@ -601,6 +719,7 @@ extern "C" int mlc_gemm_tcgen05(const void* x, const void* w, void* out, int out
     cudaStream_t s = (cudaStream_t)stream;
     if (epilogue == EPI_STORE) return dispatch_bn<EPI_STORE>(block_tokens, mw, mx, g, n_sms, s);
     if (epilogue == EPI_SILU_MUL) return dispatch_bn<EPI_SILU_MUL>(block_tokens, mw, mx, g, n_sms, s);
+    if (epilogue == EPI_QKV && cluster_split) return launch_gemm<16, EPI_QKV_CLUSTER>(mw, mx, g, n_sms, s);
     if (epilogue == EPI_QKV) return dispatch_bn<EPI_QKV>(block_tokens, mw, mx, g, n_sms, s);
     if (epilogue == EPI_ADD) return dispatch_bn<EPI_ADD>(block_tokens, mw, mx, g, n_sms, s);
     return MLC_ERR_UNSUPPORTED;

@@ -34,43 +34,10 @@ template <int BN> struct PairShape {
     static_assert(STAGES >= 3 && STAGES <= 8, "stage ring");
 };
 
-__device__ __forceinline__ unsigned cluster_rank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// The address, in the cluster's shared window, of this block's shared-memory address `local` in block `rank`.
-__device__ __forceinline__ unsigned cluster_address(unsigned local, unsigned rank) {
-    unsigned a;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local), "r"(rank));
-    return a;
-}
-__device__ __forceinline__ void mbar_arrive_remote(unsigned cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// The same without ordering of this thread's own earlier writes (it has none to publish): what the arrival reports was
+// A remote arrival (mbar_arrive_remote) without ordering of this thread's own earlier writes (it has none to publish): what the arrival reports was
 // written by the TMA unit and was complete before the local barrier said so.
 __device__ __forceinline__ void mbar_arrive_remote_relaxed(unsigned cluster_addr) {
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// mbar_wait for a barrier that a thread of the other block arrives on: the wait acquires at cluster scope.
-__device__ __forceinline__ bool mbar_wait_cluster(unsigned bar, unsigned parity, int* status, int code) {
-    unsigned long long deadline = 0;
-    for (unsigned spin = 0;; ++spin) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((spin & 1023u) == 1023u) {
-            if (spin > 65536u && *reinterpret_cast<volatile int*>(status) != 0) return false;
-            const unsigned long long now = global_ns();
-            if (deadline == 0) deadline = now + TC_WAIT_NS;
-            else if (now > deadline) {
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
 }
 __device__ __forceinline__ void tcgen05_mma_f16_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
                                                      unsigned idesc, unsigned accumulate) {
@@ -175,7 +142,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             bool ok = true;
             unsigned remote[S::STAGES];
 #pragma unroll
-            for (int s = 0; s < S::STAGES; ++s) remote[s] = cluster_address(full_bar(s), 0);
+            for (int s = 0; s < S::STAGES; ++s) remote[s] = cluster_map(full_bar(s), 0);
             for (int t = pair; t < n_tiles_total && ok; t += n_pairs) {
                 const int n_kb = tile_nkb(t);
                 for (int i = 0; i < n_kb; ++i, ++it) {
@@ -254,7 +221,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             asm volatile("bar.sync 1, 256;" ::: "memory");                   // the epilogue warps only
             if (threadIdx.x == 64) {
                 if (rank == 0) mbar_arrive(acc_empty_bar(buf));
-                else mbar_arrive_remote(cluster_address(acc_empty_bar(buf), 0));
+                else mbar_arrive_remote(cluster_map(acc_empty_bar(buf), 0));
             }
         }
     }

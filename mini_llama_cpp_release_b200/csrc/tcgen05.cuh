@@ -78,6 +78,25 @@ __device__ __forceinline__ bool mbar_wait_polling(unsigned bar, unsigned parity,
         }
     }
 }
+// mbar_wait for a barrier that threads of other blocks of the cluster arrive on: the wait acquires at cluster scope.
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned bar, unsigned parity, int* status, int code) {
+    unsigned long long deadline = 0;
+    for (unsigned spin = 0;; ++spin) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spin & 1023u) == 1023u) {
+            if (spin > 65536u && *reinterpret_cast<volatile int*>(status) != 0) return false;
+            const unsigned long long now = global_ns();
+            if (deadline == 0) deadline = now + TC_WAIT_NS;
+            else if (now > deadline) {
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
@@ -122,6 +141,26 @@ __host__ __device__ constexpr unsigned umma_idesc(int n, bool b_mn_major = false
            ((unsigned)(128 >> 4) << 24);
 }
 
+// This block's shared-memory address `addr` as an address in the shared memory of block `rank` of the cluster.
+__device__ __forceinline__ unsigned cluster_map(unsigned addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Arrive on an mbarrier of another block of the cluster (address from cluster_map); this thread's earlier writes to
+// that block's shared memory are visible to whoever acquires the barrier's phase.
+__device__ __forceinline__ void mbar_arrive_remote(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// All threads of all blocks of the cluster meet (every thread of a warp together).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }

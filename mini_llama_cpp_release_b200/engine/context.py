@@ -16,7 +16,7 @@ import torch
 from .. import kernels
 from ..cache.paged import PAGE_SIZE, PagedCache
 from .batch import MiniBatch, SequenceChunk
-from .decode_runner import DecodeRunner, padded_batch
+from .decode_runner import DecodeRunner, capturing, padded_batch
 from .model import Model
 from .step_info import StepInfo
 
@@ -248,7 +248,7 @@ class Context:
         torch.cuda.current_stream(dev).wait_stream(stream)
         torch.cuda.synchronize(dev)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
+        with capturing(graph, stream):
             logits = self.model.forward(self._step_over(own, layout), self.cache)
         torch.cuda.synchronize(dev)
         while len(graphs) >= self.STEP_GRAPHS:

@@ -14,6 +14,8 @@ after each attention kernel (src/cuda_attention.cu:29-32).
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -28,6 +30,22 @@ def _round_up_pow2(n: int) -> int:
     while p < n:
         p <<= 1
     return p
+
+
+@contextlib.contextmanager
+def capturing(graph: "torch.cuda.CUDAGraph", stream: "torch.cuda.Stream"):
+    """`torch.cuda.graph` with Python's cyclic garbage collector held off: a collection that ran in the middle of a
+    capture could free a graph of an earlier context or runner, and destroying a graph while this thread captures
+    invalidates the capture."""
+    was_on = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, stream=stream):
+            yield
+    finally:
+        if was_on:
+            gc.enable()
 
 
 BATCH_SIZES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -138,7 +156,7 @@ class DecodeRunner:
         torch.cuda.synchronize(dev)
         before, lib_before = kernels.launch_count(), kernels.library_launch_count()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, stream=stream):
+        with capturing(self.graph, stream):
             self._body()
         self.launches_per_step = kernels.launch_count() - before
         self.library_launches_per_step = kernels.library_launch_count() - lib_before

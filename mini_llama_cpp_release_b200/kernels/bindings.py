@@ -14,7 +14,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
 ]
 
 
@@ -712,6 +712,32 @@ def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
                                         kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product (prompt form)")
 
 
+@functools.lru_cache(maxsize=None)
+def gemm_qkv_clusters_resident(size: int) -> int:
+    """Clusters of `size` blocks of the few-token Q/K/V product that the GPU holds at once (0: none can be launched)."""
+    fn = core().mlc_gemm_qkv_clusters_resident
+    fn.argtypes, fn.restype = [c_int], c_int
+    return int(fn(size))
+
+
+@functools.lru_cache(maxsize=1024)
+def gemm_qkv_cluster_splits(n_tok: int, n_out: int, k: int, resident: tuple = None) -> int:
+    """Blocks (1, 2 or 4) that share the K range of a tile of the few-token Q/K/V product and merge inside a cluster
+    (csrc/gemm_tcgen05.cu).  A block alone draws its 128 rows of W at one SM's pace, which costs where the rows are
+    long: 14.4 against 11.1 us with two blocks at 4,608 x 3,584 (Qwen2-7B), 7.4 against 6.6 us at 2,048 x 1,536; at
+    1,152 x 896 the product is a chain of latencies either way and the cluster's meeting only adds to it (5.0
+    against 5.2 us).  So: the most blocks that leave each at least 768 columns of W and whose clusters the GPU
+    holds all at once (`resident`: clusters of 2 and of 4 that fit; asked of the device if not given)."""
+    tiles = ((n_out + 127) // 128) * ((n_tok + 15) // 16)
+    k_blocks = (k + 63) // 64
+    for i, splits in enumerate((4, 2)):
+        per = (k_blocks + splits - 1) // splits
+        fit = resident[i] if resident is not None else gemm_qkv_clusters_resident(splits)
+        if per >= 12 and (splits - 1) * per < k_blocks and tiles <= fit:
+            return splits
+    return 1
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, n_splits: int = 1,
                  block_tokens: Optional[int] = None, bias: Optional[torch.Tensor] = None,
                  positions: Optional[torch.Tensor] = None, tok_seq: Optional[torch.Tensor] = None,
@@ -740,7 +766,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
     elif epilogue == EPI_SILU_MUL:
         assert out.numel() == n_tok * (n_out // 2) and n_splits == 1
     else:
-        assert out.numel() == n_tok * q_heads * head_dim and n_splits == 1
+        assert out.numel() == n_tok * q_heads * head_dim
+        if n_splits != 1 and not (n_splits in (2, 4) and block_tokens == 16):
+            raise KernelError(f"the Q/K/V product shares its K range out over 2 or 4 blocks of 16-token tiles, not {n_splits} "
+                              f"blocks of {block_tokens}-token tiles (bad size)")
     if kv is not None:
         assert kv.k_pool.dtype == out.dtype
         cache = (kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset,

@@ -170,7 +170,7 @@ def bench_gemm(args) -> None:
         rope = kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), max(T, 64))
         bias = torch.randn(N, device=DEV)
         out = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
-        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 2, 1, args.block_tokens, bias=bias, positions=positions,
+        fn = lambda i: kernels.gemm_tcgen05(x, ws[i % C], out, 2, args.splits, args.block_tokens, bias=bias, positions=positions,
                                             tok_seq=tok_seq, rope=rope, q_heads=H, kv_heads=KV, head_dim=hd, kv=kv)
         nbytes += T * N * 2
     report(f"tcgen05 product T={T} N={N} K={K} epilogue={args.epilogue} splits={args.splits}", fn, args, nbytes, flops)

@@ -127,10 +127,12 @@ class GQAttention(Part):
                                       tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
                                       kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms)
         elif self.fused:
-            kernels.gemm_tcgen05(h, proj.weight, q, kernels.bindings.EPI_QKV, bias=bias, positions=step.positions,
+            # short epilogues in more blocks beat one long one; the few tiles' K range shared out over clusters of blocks
+            splits = kernels.gemm_qkv_cluster_splits(n, proj.weight.shape[0], self.hidden) if n <= 64 else 1
+            kernels.gemm_tcgen05(h, proj.weight, q, kernels.bindings.EPI_QKV, splits, bias=bias, positions=step.positions,
                                  tok_seq=step.tok_seq, rope=table, q_heads=self.H, kv_heads=kv_heads, head_dim=self.hd,
                                  kv=memory.kv if memory.writes_cache else None, n_sms=rt.n_sms,
-                                 block_tokens=16 if n <= 64 else None)     # short epilogues in more blocks beat one long one
+                                 block_tokens=16 if n <= 64 else None)
         elif getattr(self.position, "fusable", False):
             kernels.qkv_post(proj(h, torch.float32), bias, step.positions, step.tok_seq, table, self.H, kv_heads,
                              self.hd, q, memory.kv if memory.writes_cache else None)

@@ -310,6 +310,28 @@ def test_a_batch_between_two_captured_sizes_is_padded_with_copies_that_change_no
     assert ctx.cache.slots.n_held == 0
 
 
+def test_a_graph_that_the_garbage_collector_frees_does_not_spoil_a_capture():
+    """An engine that is no longer used lies in reference cycles (context, runners, their graphs), so its graphs die
+    whenever Python's cyclic collector next runs; destroying a graph while this thread captures one invalidates the
+    capture.  `decode_runner.capturing` collects before it captures and holds the collector off meanwhile: with the
+    collector set to run at every allocation, a new engine still captures its steps."""
+    import gc
+    folder = model_folder("A")
+    old = helpers.engine(folder, "bfloat16")
+    assert len(old.generate([[1, 2, 3]], n_predict=3, stop_token_ids=[])[0]) == 3
+    cycle = [old]
+    cycle.append(cycle)
+    del old, cycle
+    thresholds = gc.get_threshold()
+    gc.set_threshold(1, 1, 1)
+    try:
+        llm = helpers.engine(folder, "bfloat16")
+        out = llm.generate([[4, 5, 6], [7]], n_predict=4, stop_token_ids=[])
+    finally:
+        gc.set_threshold(*thresholds)
+    assert [len(o) for o in out] == [4, 4]
+
+
 def test_the_seed_is_data_of_the_captured_step_not_part_of_it():
     folder = model_folder("B", std=0.1)
     llm = helpers.engine(folder, "float32")

@@ -342,6 +342,61 @@ def test_tcgen05_product_with_qkv_epilogue(H, KV, hd, T):
     assert torch.isnan(kv.k_pool[0].float()).all()
 
 
+@pytest.mark.parametrize("H,KV,hd,T,K,splits", [(14, 2, 64, 8, 896, 4), (6, 3, 32, 9, 200, 2), (2, 1, 256, 3, 136, 2), (28, 4, 128, 1, 3584, 4),
+                                                (4, 2, 64, 40, 1152, 4), (3, 1, 16, 16, 448, 4)])
+def test_tcgen05_product_with_qkv_epilogue_shares_its_k_range_out_over_a_cluster(H, KV, hd, T, K, splits):
+    """The few-token Q/K/V product with 2 or 4 blocks of a cluster per tile: each block's accumulator holds a part of the
+    K range, the parts travel to the block that owns the rows through distributed shared memory, and the owner adds them
+    and runs bias, rotation and cache write.  A last part shorter than the others, K no multiple of 64, row counts that
+    are no multiple of 128 (a last tile whose upper warps have no rows), several token tiles, a head size whose
+    rotation pairs span several warps.  Against the plain formula and, bit for bit in the queries, against one block
+    per tile when the parts are as many as the threads that issue products (the sums then run in the same order)."""
+    g = torch.Generator().manual_seed(hd + T + K)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((H + 2 * KV) * hd, K, generator=g) * 0.3).to(torch.bfloat16)
+    bias = torch.randn((H + 2 * KV) * hd, generator=g)
+    half = hd // 2
+    within = torch.stack([torch.arange(half), torch.arange(half) + half], dim=1).reshape(-1)
+    order = (torch.arange(H + 2 * KV)[:, None] * hd + within[None, :]).reshape(-1)
+    lens = [T - T // 3 + 66, T // 3] if T >= 3 else [T + 66]
+    q_lens = [T - T // 3, T // 3] if T >= 3 else [T]
+    positions = torch.cat([torch.arange(n - m, n) for n, m in zip(lens, q_lens)]).to(torch.int32)
+    tok_seq = torch.cat([torch.full((m,), b) for b, m in enumerate(q_lens)]).to(torch.int32)
+    kv = make_paged([torch.zeros(n, KV, hd) for n in lens], [torch.zeros(n, KV, hd) for n in lens], torch.bfloat16)
+    table = kernels.rope_table(neox_inv_freq(hd, 1e6).to(DEV), 512)
+    q_out = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05(x.to(DEV), w[order].contiguous().to(DEV), q_out, 2, splits, 16, bias=bias[order].contiguous().to(DEV),
+                         positions=positions.to(DEV), tok_seq=tok_seq.to(DEV), rope=table, q_heads=H, kv_heads=KV,
+                         head_dim=hd, kv=kv)
+    kernels.check_gemm_status(DEV)
+    full = x.float() @ w.float().t() + bias
+    q_want = plain_impl.rope_neox(full[:, :H * hd].reshape(T, H, hd), positions, 1e6)
+    k_want = plain_impl.rope_neox(full[:, H * hd:(H + KV) * hd].reshape(T, KV, hd), positions, 1e6)
+    v_want = full[:, (H + KV) * hd:].reshape(T, KV, hd)
+    close(q_out.float().view(T, H, hd), q_want, 8e-3)
+    pages = kv.page_table.cpu()
+    k_got = torch.stack([kv.k_pool[1, int(pages[tok_seq[n], positions[n] // 64]), :, positions[n] % 64].float().cpu() for n in range(T)])
+    v_got = torch.stack([kv.v_pool[1, int(pages[tok_seq[n], positions[n] // 64]), :, positions[n] % 64].float().cpu() for n in range(T)])
+    close(k_got, k_want, 8e-3)
+    close(v_got, v_want, 8e-3)
+    assert torch.isnan(kv.k_pool[0].float()).all()
+
+
+def test_qkv_cluster_splits_are_chosen_for_long_rows_and_refused_for_other_tile_widths():
+    fit = (32, 70)                                                             # clusters of 4 and of 2 that a GPU might hold
+    assert kernels.gemm_qkv_cluster_splits(8, 4608, 3584, fit) == 2            # 36 tiles: more than the clusters of 4 that fit
+    assert kernels.gemm_qkv_cluster_splits(8, 2048, 3584, fit) == 4
+    assert kernels.gemm_qkv_cluster_splits(16, 2048, 1536, fit) == 2           # 768 columns a block
+    assert kernels.gemm_qkv_cluster_splits(8, 1152, 896, fit) == 1             # short rows: a chain of latencies either way
+    assert kernels.gemm_qkv_cluster_splits(64, 4608, 3584, fit) == 1           # 144 tiles fill the GPU as they are
+    assert kernels.gemm_qkv_clusters_resident(2) >= 1 and kernels.gemm_qkv_clusters_resident(3) == 0
+    x = torch.zeros(8, 128, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)
+    pos = torch.zeros(8, dtype=torch.int32, device=DEV)
+    with pytest.raises(kernels.KernelError, match="size"):                     # three blocks are no cluster this kernel forms
+        kernels.gemm_tcgen05(x, w, torch.empty(8, 128, dtype=torch.bfloat16, device=DEV), 2, 3, 16, positions=pos, q_heads=2, head_dim=64)
+
+
 @pytest.mark.parametrize("T,N,K,splits", [(8, 896, 4864, 19), (64, 896, 896, 7), (3, 200, 128, 1), (16, 130, 1000, 4)])
 def test_tcgen05_product_adding_into_the_stream(T, N, K, splits):
     g = torch.Generator().manual_seed(N + K)
