@@ -95,8 +95,7 @@ template <int BN, int EPI> struct GemmShape {
     // float32: 2 blocks x 2 warps or 4 blocks x 1 warp, 8 KiB.  It lies over the staging tiles: a warp that owns rows
     // reads the parts sent to it (slots source x warps + its number among the owner's warps) before it stages
     // anything, its staging tile (2 KiB at its quarter's number) is one of its own slots, and warps that own no rows
-    // stage nothing.  (With 8 KiB of its own the block passed 164 KiB, the SM's next smaller split between L1 and
-    // shared memory, and the whole decode step took 4 % longer.)
+    // stage nothing.
     static constexpr int RECV_BYTES = (EPI == EPI_QKV_CLUSTER && BN == 16) ? 4 * 32 * 16 * 4 : 0;
     static_assert(RECV_BYTES <= STAGING_BYTES, "the received parts lie over the staging tiles");
     static constexpr int BAR_BYTES = 512;                           // up to 16 stages: full 0-15, empty 16-31, accumulators 32-35, slot 36, parts received 37
