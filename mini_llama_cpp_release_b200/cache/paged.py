@@ -137,7 +137,10 @@ class SlotBook:
         self._require(slot)
         new_len = self.length[slot] + n_new
         n_needed = (new_len + self.page_size - 1) // self.page_size
-        want = [max(0, n_needed - len(pl)) for pl in self.page_lists[slot]]
+        lists = self.page_lists[slot]
+        if all(len(pl) >= n_needed for pl in lists):         # the step of a decoded token, 63 times in 64
+            return
+        want = [max(0, n_needed - len(pl)) for pl in lists]
         for g, k in enumerate(want):
             if k > self.pages[g].n_free:
                 raise CacheFull(

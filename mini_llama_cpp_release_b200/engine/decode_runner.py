@@ -18,6 +18,7 @@ import contextlib
 import gc
 from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -104,6 +105,12 @@ class DecodeRunner:
         for g in range(n_groups):
             h(f"pages{g}")[:] = -1
         self.chosen_dev = self.view("chosen")
+        self.chosen_np = self.chosen_host.numpy()
+        # the per-step inputs as views made once: slicing a tensor costs microseconds that every step would pay
+        end = self.offsets["sample_pos"][0] + B                     # tokens, positions, start_pos, sample_pos lie first
+        self._step_dev, self._step_host = self.dev_buf[:end], self.host_buf[:end]
+        self._np_step = {n: self.host_np[self.offsets[n][0]:self.offsets[n][0] + B]
+                         for n in ("tokens", "positions", "start_pos", "sample_pos")}
         self.sync_stream = torch.cuda.current_stream(dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
@@ -225,16 +232,13 @@ class DecodeRunner:
         pad = B - self.n_live
         if pad:
             tokens, lengths = list(tokens) + [tokens[-1]] * pad, list(lengths) + [lengths[-1]] * pad
-        np_buf = self.host_np
-        o_tok, o_pos, o_start, o_samp = (self.offsets[n][0] for n in ("tokens", "positions", "start_pos", "sample_pos"))
-        np_buf[o_tok:o_tok + B] = tokens
-        np_buf[o_pos:o_pos + B] = lengths
-        np_buf[o_start:o_start + B] = lengths
-        np_buf[o_samp:o_samp + B] = lengths
-        np_buf[o_samp:o_samp + B] += 1
-        end = o_samp + B                                          # the four segments lie first, in this order
-        self.dev_buf[:end].copy_(self.host_buf[:end], non_blocking=True)
-        return 4 * end
+        v = self._np_step
+        v["tokens"][:] = tokens
+        v["positions"][:] = lengths
+        np.copyto(v["start_pos"], v["positions"])
+        np.add(v["positions"], 1, out=v["sample_pos"])
+        self._step_dev.copy_(self._step_host, non_blocking=True)
+        return 4 * self._step_host.numel()
 
     def replay(self) -> None:
         self.graph.replay()
@@ -247,4 +251,4 @@ class DecodeRunner:
         self.reads = getattr(self, "reads", 0) + 1
         if self.reads % 64 == 1:
             kernels.check_gemm_status(self.model.runtime.device)
-        return self.chosen_host[:self.n_live].tolist()
+        return self.chosen_np[:self.n_live].tolist()

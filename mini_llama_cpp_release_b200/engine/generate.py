@@ -97,12 +97,13 @@ def generate_batch(ctx, sampler, prompts: Sequence[Sequence[int]], seq_ids: Sequ
         lengths = [len(p) for p in prompts]
         logits = ctx.forward_batch(MiniBatch.prefill([slots[i] for i in live], [prompts[i] for i in live]))
         fused = bool(getattr(ctx, "use_graphs", False)) and hasattr(ctx, "decode_and_sample")
+        live_slots, live_ids = [slots[i] for i in live], [seq_ids[i] for i in live]
         chosen_next = None
         while True:
             if chosen_next is not None:
                 chosen, chosen_next = chosen_next, None
             else:
-                chosen = sampler.sample(logits, [seq_ids[i] for i in live], [lengths[i] for i in live])
+                chosen = sampler.sample(logits, live_ids, [lengths[i] for i in live])
             if on_step is not None:
                 on_step(live, chosen, logits)
             still: List[int] = []
@@ -117,21 +118,22 @@ def generate_batch(ctx, sampler, prompts: Sequence[Sequence[int]], seq_ids: Sequ
                 else:
                     still.append(i)
                     feed.append(tok)
-            for i in live:
-                if i not in still:
-                    ctx.release(slots[i])          # a finished sequence gives its slot and pages back at once
-                    slots[i] = -1
-            live = still
+            if len(still) != len(live):
+                for i in live:
+                    if i not in still:
+                        ctx.release(slots[i])      # a finished sequence gives its slot and pages back at once
+                        slots[i] = -1
+                live = still
+                live_slots, live_ids = [slots[i] for i in live], [seq_ids[i] for i in live]
             if not live:
                 break
             for i in live:
                 lengths[i] += 1
             if fused:
                 # forward, choice and the move to the next position are one captured graph
-                chosen_next, logits = ctx.decode_and_sample([slots[i] for i in live], feed, sampler,
-                                                            [seq_ids[i] for i in live])
+                chosen_next, logits = ctx.decode_and_sample(live_slots, feed, sampler, live_ids)
             else:
-                logits = ctx.forward_batch(MiniBatch.decode([slots[i] for i in live], feed))
+                logits = ctx.forward_batch(MiniBatch.decode(live_slots, feed))
     finally:
         for s in slots:
             if s >= 0:
