@@ -704,6 +704,41 @@ def test_tensor_core_attention_window_edge_and_far_key(window, row_tiles):
     assert float((got - 7.0).abs().max()) < 0.2
 
 
+@pytest.mark.parametrize("H,KV,hd", [(14, 2, 64), (8, 2, 128), (3, 1, 64)])
+@pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 4), (24, 1), (64, 2), (130, 1), (130, 3)])
+def test_single_token_attention_by_tma_with_windows_given_back_pages_and_key_splits(H, KV, hd, window, n_splits):
+    """The single-token kernel at the head sizes whose keys and values come by TMA (whole sub-tiles of 32 or 16 keys in
+    swizzled tiles): a sub-tile brings along keys beyond the sequence's end and before the window's start, which hold
+    NaN here and must count as nothing; pages wholly before the window are given back (page number -1, their contents
+    NaN), as the cache's window groups do; key splits merged inside a cluster; sequences whose last sub-tile holds one
+    key, a full sub-tile, a full page."""
+    lens = [300, 66, 25, 700, 64, 97, 1, 33]
+    g = torch.Generator().manual_seed(hd + window + n_splits)
+    ks = [torch.randn(n, KV, hd, generator=g).bfloat16().float() for n in lens]
+    vs = [torch.randn(n, KV, hd, generator=g).bfloat16().float() for n in lens]
+    qs = [torch.randn(n, H, hd, generator=g).bfloat16().float() for n in lens]
+    kv = make_paged(ks, vs, torch.bfloat16, seed=window)
+    if window:
+        table = kv.page_table.cpu()
+        for b, n in enumerate(lens):
+            for p in range(max(0, n - window) // 64):                          # no key of these pages is inside the window
+                kv.k_pool[1, int(table[b, p])] = float("nan")
+                kv.v_pool[1, int(table[b, p])] = float("nan")
+                table[b, p] = -1
+        kv.page_table.copy_(table)
+    q = torch.cat([qq[-1:] for qq in qs]).bfloat16().to(DEV)
+    out = torch.full_like(q, float("nan"))
+    B = len(lens)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    start = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    kernels.attention_mma(q.view(B, H * hd), out.view(B, H * hd), cu, start, B, 1, H, kv, 1.0 / math.sqrt(hd), window, 1, n_splits,
+                          None, None, True)
+    kernels.check_gemm_status(DEV)
+    want = torch.cat([plain_impl.attention(qq, k, v, window or None)[-1:] for qq, k, v in zip(qs, ks, vs)])
+    assert torch.isfinite(out.float()).all()
+    close(out.float().cpu(), want, 1e-2)
+
+
 def test_tensor_core_attention_ignores_what_lies_beyond_a_sequences_end():
     """Pages are handed out dirty: whatever bit patterns follow a sequence's last token in its
     last page (NaN here) must not reach the result."""
