@@ -317,13 +317,14 @@ class Context:
             h2d += runner.load_step(tokens, lengths)
             h2d += runner.refresh_pages(slots)
         runner.replay()
-        chosen = runner.read_chosen()
-        logits = runner.logits[:len(slots)]
+        # the host's bookkeeping of this step while the device runs it
         history = self.token_history
         for s, t in zip(slots, tokens):
             cache.commit(s, 1)
             history[s].append(int(t))
         self.n_steps += 1
+        chosen = runner.read_chosen()
+        logits = runner.logits[:len(slots)]
         self.last_copy_bytes = (h2d, 4 * len(slots))
         return chosen, logits
 

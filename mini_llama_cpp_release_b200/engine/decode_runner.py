@@ -108,7 +108,8 @@ class DecodeRunner:
         self.chosen_np = self.chosen_host.numpy()
         # the per-step inputs as views made once: slicing a tensor costs microseconds that every step would pay
         end = self.offsets["sample_pos"][0] + B                     # tokens, positions, start_pos, sample_pos lie first
-        self._step_dev, self._step_host = self.dev_buf[:end], self.host_buf[:end]
+        self._copy_step_in = kernels.PinnedCopy(self.dev_buf[:end], self.host_buf[:end])
+        self._copy_chosen_out = kernels.PinnedCopy(self.chosen_host, self.chosen_dev)
         self._np_step = {n: self.host_np[self.offsets[n][0]:self.offsets[n][0] + B]
                          for n in ("tokens", "positions", "start_pos", "sample_pos")}
         self.sync_stream = torch.cuda.current_stream(dev)
@@ -237,8 +238,8 @@ class DecodeRunner:
         v["positions"][:] = lengths
         np.copyto(v["start_pos"], v["positions"])
         np.add(v["positions"], 1, out=v["sample_pos"])
-        self._step_dev.copy_(self._step_host, non_blocking=True)
-        return 4 * self._step_host.numel()
+        self._copy_step_in()
+        return self._copy_step_in.nbytes
 
     def replay(self) -> None:
         self.graph.replay()
@@ -246,7 +247,7 @@ class DecodeRunner:
         kernels.count_library_launches(self.library_launches_per_step)
 
     def read_chosen(self) -> List[int]:
-        self.chosen_host.copy_(self.chosen_dev, non_blocking=True)
+        self._copy_chosen_out()
         self.sync_stream.synchronize()
         self.reads = getattr(self, "reads", 0) + 1
         if self.reads % 64 == 1:

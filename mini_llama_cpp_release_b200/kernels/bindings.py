@@ -14,7 +14,7 @@ from ..csrc import build as _build
 __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
-    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "decode_advance",
+    "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "PinnedCopy", "decode_advance",
 ]
 
 
@@ -98,6 +98,7 @@ def core() -> ctypes.CDLL:
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_pair": [P, P, P, I, I, I, I, I, I, I, P, I, P],
+            "mlc_copy_async": [P, P, LL, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
             "mlc_sample": [P, I, I, F, I, c_ulonglong, P, P, P, P, P],
@@ -323,6 +324,27 @@ def decode_advance(chosen: torch.Tensor, tokens: torch.Tensor, positions: torch.
     _check(core().mlc_decode_advance(chosen.data_ptr(), n, tokens.data_ptr(), positions.data_ptr(), start_pos.data_ptr(),
                                      sample_pos.data_ptr(), _ptr(history), counter.data_ptr(), max_steps, _stream()),
            "decode advance")
+
+
+class PinnedCopy:
+    """dst ← src on the current stream, one of them in pinned host memory and the other on the device, both dense and of
+    one type and size: the few hundred bytes a decode step brings and takes.  Checked once, when it is made; a call
+    costs the host a third of a tensor library's copy.  Not counted as a kernel launch.  The tensors are kept alive."""
+
+    def __init__(self, dst: torch.Tensor, src: torch.Tensor):
+        if dst.dtype != src.dtype or dst.numel() != src.numel() or not dst.is_contiguous() or not src.is_contiguous():
+            raise KernelError("a pinned copy takes two dense tensors of one type and size")
+        if src.is_cuda == dst.is_cuda or not (src.is_cuda or src.is_pinned()) or not (dst.is_cuda or dst.is_pinned()):
+            raise KernelError("a pinned copy runs between pinned host memory and the device")
+        self.dst, self.src = dst, src
+        self._fn = core().mlc_copy_async
+        self._args = (dst.data_ptr(), src.data_ptr(), src.numel() * src.element_size(), 0 if dst.is_cuda else 1)
+        self.nbytes = self._args[2]
+
+    def __call__(self) -> None:
+        rc = self._fn(*self._args, _stream())
+        if rc:
+            raise KernelError(f"copy between host and device: CUDA error {rc}")
 
 
 def set_pdl(enabled: bool) -> None:
