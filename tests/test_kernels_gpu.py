@@ -232,6 +232,20 @@ def test_silu_mul(dtype):
     close(out.float(), g * (1 / (1 + torch.exp(-g))) * u, 2e-6 if dtype == "float32" else 5e-3)
 
 
+def test_pinned_copy_brings_and_takes_and_refuses_pageable_memory():
+    host = torch.arange(37, dtype=torch.int32).pin_memory()
+    dev = torch.zeros(37, dtype=torch.int32, device=DEV)
+    back = torch.zeros(37, dtype=torch.int32).pin_memory()
+    kernels.PinnedCopy(dev, host)()
+    kernels.PinnedCopy(back, dev)()
+    torch.cuda.synchronize()
+    assert torch.equal(back, host)
+    with pytest.raises(kernels.KernelError, match="pinned"):
+        kernels.PinnedCopy(dev, torch.zeros(37, dtype=torch.int32))
+    with pytest.raises(kernels.KernelError, match="one type and size"):
+        kernels.PinnedCopy(dev, host[:36])
+
+
 def test_gather_rows():
     x, d = torch.randn(11, 72, device=DEV), torch.randn(11, 72, device=DEV)
     rows = torch.tensor([10, 0, 3, 3], dtype=torch.int32, device=DEV)
