@@ -43,7 +43,7 @@ CONFIGS = {
     "qwen2-7b": dict(preset="qwen2-7b", prompt_len=2048, ctx_len=8192, ragged=None, max_steps=1000),
 }
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
-REF_SOURCE = "/root/reference"
+REF_SOURCE = os.environ.get("MLC_REFERENCE_SOURCE", "/root/reference")     # where the reference's checkout lies, if baseline/_ref is empty
 REF_PREFILL_TOKENS = 32
 
 
