@@ -694,7 +694,8 @@ def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
                       kv: Optional[KVView] = None, n_sms: int = 0) -> None:
     """The tcgen05 product for prompts (csrc/gemm_tcgen05_rows.cu): bfloat16 x [n, K] times bfloat16 w [rows, K]
     transposed, tiles of 128 tokens x `block_rows` (128 to 256 in steps of 32) rows of w, the same epilogues as `gemm_tcgen05`;
-    EPI_ADD adds into `out` (float32 [n, rows]) with plain reads and writes."""
+    EPI_ADD adds into `out` (float32 [n, rows]) with 16-byte atomic adds, the K range shared out over `n_splits` blocks per
+    tile (the plan's choice if neither tile width nor splits are given)."""
     require_cuda(x, w, out, bias, positions, tok_seq, rope)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("the tcgen05 matrix product takes bfloat16 operands")
