@@ -189,7 +189,8 @@ def cmd_bench(argv: Sequence[str]) -> int:
             ctx.release(s)
         return logits, (t1 - t0) * 1e3, (t3 - t2) * 1e3
 
-    run()                                                       # warm-up: kernels compiled, graphs captured
+    run()                                                       # warm-up: kernels compiled and loaded
+    run()                                                       # the shape's second coming: its steps are captured as graphs
     logits, prefill_ms, decode_ms = run()
     generated, decode_tokens = args.batch * n_predict, args.batch * (n_predict - 1)
     if args.verbose:
