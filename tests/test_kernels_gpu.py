@@ -753,6 +753,38 @@ def test_single_token_attention_by_tma_with_windows_given_back_pages_and_key_spl
     close(out.float().cpu(), want, 1e-2)
 
 
+@pytest.mark.parametrize("H,KV,hd", [(14, 2, 64), (8, 2, 128), (6, 3, 32)])
+@pytest.mark.parametrize("n_splits", [1, 8])
+def test_single_token_attention_over_more_pages_than_a_block_keeps_in_shared_memory(H, KV, hd, n_splits):
+    """40,000 cached tokens are 625 pages; a block keeps the numbers of the first 512 in shared memory and looks the
+    others up.  One early key and one late key are made to dominate one head each, so that a page read from the wrong
+    place shows; the other heads against softmax(q·k/sqrt(hd))·v computed here in float64 (src/ops.cpp:43-70)."""
+    n = 40000
+    g = torch.Generator().manual_seed(hd + n_splits)
+    k = torch.randn(n, KV, hd, generator=g).bfloat16().float()
+    v = torch.randn(n, KV, hd, generator=g).bfloat16().float()
+    q = torch.randn(1, H, hd, generator=g).bfloat16().float()
+    group = H // KV
+    k[7, 0] = 0; k[7, 0, 5] = 16.0; v[7, 0] = 3.0                  # kv head 0, an early page
+    q[0, 0] = 0; q[0, 0, 5] = 16.0
+    k[39000, KV - 1] = 0; k[39000, KV - 1, 2] = 16.0; v[39000, KV - 1] = -2.0     # the last kv head, a page beyond the 512th
+    q[0, H - 1] = 0; q[0, H - 1, 2] = 16.0
+    kv = make_paged([k], [v], torch.bfloat16, seed=3)
+    out = torch.full((1, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    start = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    kernels.attention_mma(q.bfloat16().view(1, H * hd).to(DEV), out, cu, start, 1, 1, H, kv, 1.0 / math.sqrt(hd), 0, 1, n_splits,
+                          None, None, True)
+    kernels.check_gemm_status(DEV)
+    kh = k.double().repeat_interleave(group, dim=1)                 # [n, H, hd]: query head h reads kv head h // group
+    vh = v.double().repeat_interleave(group, dim=1)
+    p = torch.softmax((kh * q.double()).sum(-1) / math.sqrt(hd), dim=0)          # [n, H]
+    want = (p[:, :, None] * vh).sum(0)                                          # [H, hd]
+    got = out.float().cpu().view(H, hd)
+    assert float((got[0] - 3.0).abs().max()) < 0.1 and float((got[H - 1] + 2.0).abs().max()) < 0.1
+    close(got, want.float(), 1e-2)
+
+
 def test_tensor_core_attention_ignores_what_lies_beyond_a_sequences_end():
     """Pages are handed out dirty: whatever bit patterns follow a sequence's last token in its
     last page (NaN here) must not reach the result."""
