@@ -847,6 +847,36 @@ def test_tcgen05_attention_window_edge_and_far_key(window):
     assert float((got[-1] - 7.0).abs().max()) < 0.2
 
 
+@pytest.mark.parametrize("H,KV,hd", [(14, 2, 64), (4, 1, 128)])
+def test_tcgen05_attention_of_a_chunk_over_a_long_cache(H, KV, hd):
+    """The last 130 tokens of a 40,000-token sequence as one step (a chunk of a long prompt): 625 key tiles a row,
+    pages in shuffled order.  Against softmax(q·k/sqrt(hd))·v of those rows computed here in float64, causal
+    (src/forward.cpp:585-611); one early key that only the last row prefers."""
+    n, m = 40000, 130
+    g = torch.Generator().manual_seed(hd)
+    k = torch.randn(n, KV, hd, generator=g).bfloat16().float()
+    v = torch.randn(n, KV, hd, generator=g).bfloat16().float()
+    q = torch.randn(m, H, hd, generator=g).bfloat16().float()
+    k[11] = 0; k[11, :, 3] = 16.0; v[11] = 5.0
+    q[-1] = 0; q[-1, :, 3] = 16.0
+    kv = make_paged([k], [v], torch.bfloat16, seed=5)
+    out = torch.full((m, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor([0, m], dtype=torch.int32, device=DEV)
+    start = torch.tensor([n - m], dtype=torch.int32, device=DEV)
+    kernels.attention_tcgen05(q.bfloat16().view(m, H * hd).to(DEV), out, cu, start, 1, m, H, kv, 1.0 / math.sqrt(hd), 0)
+    torch.cuda.synchronize()
+    kernels.check_gemm_status(DEV)
+    got = out.float().cpu().view(m, H, hd)
+    group = H // KV
+    pos = torch.arange(n - m, n)[:, None]
+    mask = torch.arange(n)[None, :] <= pos                                        # [m, n]
+    for h in range(H):
+        sc = q[:, h].double() @ k[:, h // group].double().t() / math.sqrt(hd)     # [m, n]
+        p = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=1)
+        close(got[:, h], (p @ v[:, h // group].double()).float(), 1e-2)
+    assert float((got[-1] - 5.0).abs().max()) < 0.2
+
+
 def test_tcgen05_attention_rescales_when_the_maximum_keeps_rising():
     """One key per page scores far above everything before it, so every row's running maximum jumps by more than
     the lazy-rescaling threshold page after page; the value at that key is the page's number."""
