@@ -11,6 +11,10 @@ from mini_llama_cpp_release_b200.engine import MiniBatch
 pytestmark = pytest.mark.gpu
 
 
+def ml_engine(folder, dtype):
+    return helpers.ml.load(folder, dtype=dtype, max_tokens=70 * 64, max_seqs=70)
+
+
 def confident_greedy(pm, prompt, n, margin=1e-3):
     """Greedy ids of the plain model with, for each, whether the top two logits are clearly apart."""
     seq, ids, sure = list(prompt), [], []
@@ -308,6 +312,29 @@ def test_a_batch_between_two_captured_sizes_is_padded_with_copies_that_change_no
             assert rel_err(logits[row], refs[i][len(prompts[i]) - 1 + step]) <= TOL[dtype], (step, i)
     ctx.cache.check()
     assert ctx.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_batch_of_more_sequences_than_the_few_token_kernels_take(dtype):
+    """Seventy sequences decode together: above 64 rows the step's products are the prompt kernels' (tiles of 128
+    tokens), the captured step has 96 rows of which 26 repeat the last sequence, and the sequences end at three
+    different steps.  Every step's logits of every sequence against the plain implementation."""
+    folder = model_folder("C")
+    pm = plain_model(folder)
+    llm = ml_engine(folder, dtype)
+    prompts = [random_tokens(1 + (7 * i) % 23, 777, 900 + i) for i in range(70)]
+    counts = [4 + 2 * (i % 3) for i in range(70)]
+    seen = []
+    out = llm.generate(prompts, n_predict=counts, temperature=1.0, seed=5, stop_token_ids=[], max_batch=70,
+                       on_step=lambda live, chosen, logits: seen.append((list(live), logits.float().cpu().clone())))
+    assert [len(o) for o in out] == counts
+    assert [len(live) for live, _ in seen] == [70, 70, 70, 70, 46, 46, 23, 23]
+    refs = [pm.logits(p + o) for p, o in zip(prompts, out)]
+    for step, (live, logits) in enumerate(seen):
+        for row, i in enumerate(live):
+            assert rel_err(logits[row], refs[i][len(prompts[i]) - 1 + step]) <= TOL[dtype], (step, i)
+    llm.context.cache.check()
+    assert llm.context.cache.slots.n_held == 0
 
 
 def test_a_graph_that_the_garbage_collector_frees_does_not_spoil_a_capture():
