@@ -18,10 +18,9 @@
 //   QKV       rows of each head alternate dim i, dim i + hd/2: adds the bias, rotates q and k by the token's
 //             position (src/ops.cpp:125-141), writes q as [token][head][hd] and k, v into the token's place in
 //             the paged cache (src/forward.cpp:553);
-//   ADD       adds y into a float32 [token][row] tensor, the residual stream (src/forward.cpp:772, 779).  Without a K
-//             split every element belongs to one thread and these are plain reads and writes; with one (the K range
-//             shared out over blocks, for products whose tiles alone would leave most SMs idle) they are 16-byte
-//             atomic adds, which also spare the read.
+//   ADD       adds y into a float32 [token][row] tensor, the residual stream (src/forward.cpp:772, 779), with 16-byte
+//             atomic adds: nothing comes back, so a thread does not wait for the stream's old values, and the K
+//             range can be shared out over blocks (for products whose tiles alone would leave most SMs idle).
 //
 // Every wait on an mbarrier is bounded by a clock; a wait that runs out records a code in `status` (21 loader,
 // 22 tensor cores, 23 epilogue), the block skips its stores, frees its tensor memory and returns.
