@@ -31,6 +31,17 @@ from .base import Runtime
 SMALL_BATCH = 64          # up to this many rows a plain product runs on the tcgen05 kernel with split K
 MAX_SPLITS = 8            # partial sums the consumer has to add
 ADD_MAX_SPLITS = 24       # splits of a product that adds into the stream atomically (nobody has to add them up)
+ADD_MAX_SPLITS_SOME = 10  # the same for 2 to 16 rows
+
+
+def add_split_cap(n_tok: int) -> int:
+    """The most blocks that share the K range of a few-row product that adds into the stream.  More blocks stream the
+    weights faster, but every block adds its part with one atomic per row and column, and its blocks are SMs on which
+    the kernel after it cannot start early to ask for its own weights.  Measured on whole decode steps of 24 and 28
+    layers on a B200, caps of 8 / 10 / 12 / 24: 0.733 / 0.710 / 0.717 / 0.722 ms at 8 rows and 1.271 against 1.300 ms
+    (10 against 24) at 16 rows of the Qwen2-1.5B sizes, but 0.735 / 0.703 / 0.704 / 0.683 ms at one row and
+    1.039 / 1.044 / 1.016 / 1.009 ms at 64 rows; at the 7B sizes the cap does not bind."""
+    return ADD_MAX_SPLITS_SOME if 2 <= n_tok <= 16 else ADD_MAX_SPLITS
 
 
 def split_count(n_out: int, k: int, n_tok: int, n_sms: int, max_splits: int = 0) -> int:
@@ -75,7 +86,7 @@ class Linear:
         if m > SMALL_BATCH:
             kernels.library_gemm(x, self.weight, stream, accumulate=True)
             return
-        splits = split_count(self.out_features, self.in_features, m, self.runtime.n_sms, max_splits=ADD_MAX_SPLITS)
+        splits = split_count(self.out_features, self.in_features, m, self.runtime.n_sms, max_splits=add_split_cap(m))
         kernels.gemm_tcgen05(x, self.weight, stream, kernels.bindings.EPI_ADD, splits, n_sms=self.runtime.n_sms)
 
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype = torch.float32, partial_ok: bool = False) -> torch.Tensor:
