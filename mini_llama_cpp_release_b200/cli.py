@@ -53,6 +53,8 @@ def add_model_options(ap: argparse.ArgumentParser, positional: bool = False) -> 
 
 def add_engine_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
+    ap.add_argument("--backend", default="cuda", choices=["cuda", "cpu"],
+                    help="execution backend, as the reference's option (src/main.cpp:291): only cuda exists here")
     ap.add_argument("--device", type=int, default=0, help="CUDA device id (default: 0)")
     ap.add_argument("--max-tokens", "--ctx", type=int, default=None, dest="max_tokens",
                     help="tokens the cache holds (default: what the request needs)")
@@ -80,6 +82,8 @@ def resolve_model(args) -> Tuple[str, Optional[str]]:
 
 def engine_config(args, need_tokens: int):
     from mini_llama_cpp_release_b200 import EngineConfig
+    if getattr(args, "backend", "cuda") != "cuda":
+        raise SystemExit("--backend cpu: this engine runs on a CUDA device only (there is no CPU path)")
     kw = {} if args.max_batch_tokens is None else {"max_batch_tokens": args.max_batch_tokens}
     try:
         return EngineConfig(dtype=args.dtype, device=f"cuda:{args.device}", max_tokens=args.max_tokens or need_tokens,
@@ -292,7 +296,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if not argv or argv[0] in ("-h", "--help"):
         print(__doc__)
         return 0
-    if argv[0] == "--device-info":
+    if argv[0] in ("--device-info", "--cuda-info"):                                        # src/main.cpp: --cuda-info
         import torch
         for i in range(torch.cuda.device_count()):
             p = torch.cuda.get_device_properties(i)

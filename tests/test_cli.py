@@ -129,11 +129,19 @@ def test_engine_configuration_is_checked():
             EngineConfig(**bad)
 
 
+def test_the_references_backend_option_is_taken_and_cpu_is_refused():
+    """`--backend cpu|cuda` is the reference's option (src/main.cpp:291); here only cuda exists, and cpu says so before
+    anything is loaded."""
+    p = subprocess.run([sys.executable, "-m", "mini_llama_cpp_release_b200", "generate", "--random", "tiny-a", "--tokens", "1,2",
+                        "--backend", "cpu"], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert p.returncode != 0 and "CUDA device only" in p.stderr
+
+
 @pytest.mark.gpu
 def test_generate_from_random_weights_of_a_preset_with_no_model_on_disk(tmp_path):
     env_tmp = str(tmp_path)
     p = subprocess.run([sys.executable, "-m", "mini_llama_cpp_release_b200", "generate", "--random", "tiny-b", "--tokens", "1,2,3;7",
-                        "-n", "8", "--slots", "2"], cwd=ROOT, capture_output=True, text=True, timeout=600,
+                        "-n", "8", "--slots", "2", "--backend", "cuda"], cwd=ROOT, capture_output=True, text=True, timeout=600,
                        env=dict(os.environ, TMPDIR=env_tmp))
     assert p.returncode == 0, p.stderr[-2000:]
     lines = [l for l in p.stdout.splitlines() if l.startswith("generated ids:")]
