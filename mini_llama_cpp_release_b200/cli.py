@@ -103,8 +103,13 @@ def cmd_generate(argv: Sequence[str]) -> int:
     ap.add_argument("--seed", type=int, default=0, help="random seed for reproducible sampling (default: 0 = random)")
     ap.add_argument("--stop-ids", default=None, help="comma-separated stop token ids (default: the model's eos_token_id)")
     ap.add_argument("--dump-logits", default=None, help="dump the logits of every step to this directory")
+    ap.add_argument("--prompt", default=None, help=argparse.SUPPRESS)        # the reference's text options: answered, not taken
+    ap.add_argument("--tokenizer", default=None, help=argparse.SUPPRESS)
     add_engine_options(ap)
     args = ap.parse_args(argv)
+    if args.prompt is not None or args.tokenizer is not None:
+        raise SystemExit("--prompt/--tokenizer: this library works on token ids and has no tokenizer; give --tokens \"5,17,3\" "
+                         "or --tokens-file")
     if not 0 <= args.n_predict <= 1_000_000:
         raise SystemExit("--n-predict must be in 0..1000000")                            # src/main.cpp:66-79
     if args.tokens_file:

@@ -135,6 +135,8 @@ def test_the_references_backend_option_is_taken_and_cpu_is_refused():
     p = subprocess.run([sys.executable, "-m", "mini_llama_cpp_release_b200", "generate", "--random", "tiny-a", "--tokens", "1,2",
                         "--backend", "cpu"], cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert p.returncode != 0 and "CUDA device only" in p.stderr
+    p = run("generate", "--random", "tiny-a", "--prompt", "hello")
+    assert p.returncode != 0 and "no tokenizer" in p.stderr
 
 
 @pytest.mark.gpu
