@@ -94,7 +94,7 @@ def reference_line(args, raw, work) -> dict:
     r = json.loads(p.stdout.strip().splitlines()[-1])
     return {
         "impl": "reference",
-        "metric": f"decode tok/s at batch {args.batch} (Qwen2-0.5B shape, 2,048-token prompts, context 4,096)",
+        "metric": metric_name(args.batch, work),
         "value": round(r["decode_tokens_per_s"], 3), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(r["decode_ms_per_step"], 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32", "data": "synthetic: seeded uniform token ids, seeded N(0, 0.02) weights",
@@ -109,6 +109,12 @@ def reference_line(args, raw, work) -> dict:
         "prefill": {"value": round(r["prefill_tokens_per_s"], 3), "tokens": r["prefill_tokens"], "ms": round(r["prefill_ms"], 1)},
         "clocks": clock_info,
     }
+
+
+def metric_name(batch, work) -> str:
+    """The same words in both arms' lines: the metric and the work it is measured on."""
+    what = "2,048-token prompts" if not work["ragged"] else f"{batch} prompts of 1 to 2,048 tokens"
+    return f"decode tok/s at batch {batch} ({work['preset']} shape, {what}, context {work['ctx_len']:,})"
 
 
 def describe(raw, layers, batch, work) -> dict:
@@ -219,9 +225,8 @@ def main() -> int:
               f"of {same['of']} sequences; the timed path is not the product's", file=sys.stderr)
         return 1
 
-    work_name = "2,048-token prompts" if not work["ragged"] else f"{args.batch} prompts of 1 to 2,048 tokens"
     line = {
-        "metric": f"decode tok/s at batch {args.batch} ({work['preset']} shape, {work_name}, context {ctx_len:,})",
+        "metric": metric_name(args.batch, work),
         "value": round(d["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(d["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
